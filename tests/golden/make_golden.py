@@ -1,0 +1,184 @@
+#!/usr/bin/env python3
+"""Generate the golden fixtures in this directory by RUNNING THE REFERENCE.
+
+Usage (only where the reference checkout is available):
+
+    python tests/golden/make_golden.py --reference /path/to/LLM_KVCache_Quantization
+
+The reference's own classes and functions are imported unmodified
+(`INT8KVCache`, `INT4KVCache`, `quantize_asymmetric`, `pack_int4`,
+`_decode_attn_int8_torch_ref`) and driven on seeded inputs on CPU; inputs and
+outputs are stored as small `.npz` files.  The fixtures travel with the
+repository, the reference does not.
+"""
+import argparse
+import os
+import sys
+import warnings
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _np(t):
+    return t.detach().cpu().numpy()
+
+
+def gen_kv(gen, b, h, s, d, outlier_ch=0, outlier_mag=20.0, chan_std=False):
+    x = torch.randn(b, h, s, d, generator=gen)
+    if chan_std:
+        std = torch.exp(torch.empty(1, h, 1, d).uniform_(np.log(0.3), np.log(3.0), generator=gen))
+        x = x * std
+    if outlier_ch:
+        for hh in range(h):
+            ch = torch.randperm(d, generator=gen)[:outlier_ch]
+            x[:, hh, :, ch] *= outlier_mag
+    return x.to(torch.float16)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    warnings.simplefilter("ignore")
+
+    from src.cache.int8_cache import INT8KVCache
+    from src.cache.int4_cache import INT4KVCache
+    from src.quant.asymmetric_quant import quantize_asymmetric, dequantize_asymmetric
+    from src.quant.int4_basic import pack_int4, unpack_int4
+    from src.engine.patch_model import _decode_attn_int8_torch_ref
+
+    torch.manual_seed(0)
+    gen = torch.Generator().manual_seed(20261125)
+
+    # ------------------------------------------------------------------ quantizers
+    out = {}
+    B, H, S, D = 2, 2, 37, 128
+    for gs in (16, 32, 64, 128):
+        G = D // gs
+        k = gen_kv(gen, B, H, S, D, outlier_ch=4)
+        v = gen_kv(gen, B, H, S, D, chan_std=True)
+        # make some exact ties / clamp cases / tiny values
+        k[0, 0, 0, :8] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, 1e-4, 6e-8, 0.0]).half()
+        calib_k = gen_kv(gen, 4, H, 64, D, outlier_ch=0).float().abs().view(4, H, 64, G, gs).amax(dim=(0, 2, 4))
+        calib_v = gen_kv(gen, 4, H, 64, D, chan_std=True).float().abs().view(4, H, 64, G, gs).amax(dim=(0, 2, 4))
+        out[f"g{gs}_k"] = _np(k)
+        out[f"g{gs}_v"] = _np(v)
+        # --- INT8 static, fp16 calibration scales (generate_loop.py:816-817)
+        ks8 = (calib_k / 127.0).to(torch.float16)
+        vs8 = (calib_v / 127.0).to(torch.float16)
+        ks8[0, 0] = 0.0  # exercises the 1e-5 clamp
+        out[f"g{gs}_int8_static_ks_in"] = _np(ks8)
+        out[f"g{gs}_int8_static_vs_in"] = _np(vs8)
+        c = INT8KVCache(1, device="cpu", group_size=gs, static_k_scale=ks8[None], static_v_scale=vs8[None])
+        c.append(0, k, v)
+        qk, qv, sk, sv = c.get_int8_tensors(0)
+        out[f"g{gs}_int8_static_qk"] = _np(qk); out[f"g{gs}_int8_static_qv"] = _np(qv)
+        out[f"g{gs}_int8_static_sk"] = _np(sk); out[f"g{gs}_int8_static_sv"] = _np(sv)
+        # --- INT8 adaptive static
+        c = INT8KVCache(1, device="cpu", group_size=gs, static_k_scale=ks8[None], static_v_scale=vs8[None],
+                        adaptive_static_scales=True, adaptive_static_margin=0.9)
+        c.append(0, k, v)
+        qk, qv, sk, sv = c.get_int8_tensors(0)
+        out[f"g{gs}_int8_adapt_qk"] = _np(qk); out[f"g{gs}_int8_adapt_qv"] = _np(qv)
+        out[f"g{gs}_int8_adapt_sk"] = _np(sk); out[f"g{gs}_int8_adapt_sv"] = _np(sv)
+        # --- INT8 dynamic
+        for p in (99.9, 100.0, 95.0):
+            c = INT8KVCache(1, device="cpu", group_size=gs, clip_percentile=p)
+            c.append(0, k, v)
+            qk, qv, sk, sv = c.get_int8_tensors(0)
+            out[f"g{gs}_int8_dyn{p}_qk"] = _np(qk); out[f"g{gs}_int8_dyn{p}_qv"] = _np(qv)
+            out[f"g{gs}_int8_dyn{p}_sk"] = _np(sk); out[f"g{gs}_int8_dyn{p}_sv"] = _np(sv)
+        # --- INT4 static (fp32 calibration scales, generate_loop.py:818-820)
+        ks4 = (calib_k / 7.0).float()
+        vs4 = (calib_v / 7.0).float()
+        ks4[0, 0] = 0.0
+        out[f"g{gs}_int4_static_ks_in"] = _np(ks4)
+        out[f"g{gs}_int4_static_vs_in"] = _np(vs4)
+        variants = {
+            "static": dict(),
+            "mixed": dict(mixed_rescue=True),
+            "rescue": dict(outlier_rescue_ratio=0.05),
+            "rescue1": dict(outlier_rescue_ratio=1.0),
+            "adapt": dict(adaptive_static_scales=True, adaptive_static_margin=1.1),
+        }
+        for name, kw in variants.items():
+            c = INT4KVCache(1, device="cpu", group_size=gs, static_k_scale=ks4[None], static_v_scale=vs4[None], **kw)
+            c.append(0, k, v)
+            qk, qv, sk, sv = c.get_int4_tensors(0)
+            out[f"g{gs}_int4_{name}_qk"] = _np(qk); out[f"g{gs}_int4_{name}_qv"] = _np(qv)
+            out[f"g{gs}_int4_{name}_sk"] = _np(sk); out[f"g{gs}_int4_{name}_sv"] = _np(sv)
+        for p in (99.9, 100.0):
+            c = INT4KVCache(1, device="cpu", group_size=gs, clip_percentile=p)
+            c.append(0, k, v)
+            qk, qv, sk, sv = c.get_int4_tensors(0)
+            out[f"g{gs}_int4_dyn{p}_qk"] = _np(qk); out[f"g{gs}_int4_dyn{p}_qv"] = _np(qv)
+            out[f"g{gs}_int4_dyn{p}_sk"] = _np(sk); out[f"g{gs}_int4_dyn{p}_sv"] = _np(sv)
+        # --- group-wise asymmetric INT4 = generic quantize_asymmetric on a grouped view
+        for nm, t in (("k", k), ("v", v)):
+            q, s, z = quantize_asymmetric(t.view(B, H, S, G, gs), axis=-1, quant_bits=4)
+            out[f"g{gs}_asym_q{nm}"] = _np(pack_int4(q.view(B, H, S, D)))
+            out[f"g{gs}_asym_s{nm}"] = _np(s); out[f"g{gs}_asym_z{nm}"] = _np(z)
+            deq = dequantize_asymmetric(q, s.half(), z.half(), axis=-1).view(B, H, S, D)
+            out[f"g{gs}_asym_deq{nm}"] = _np(deq)
+    np.savez_compressed(os.path.join(HERE, "quantizers.npz"), **out)
+
+    # ------------------------------------------------------------------ pack / unpack
+    allv = torch.arange(-8, 8, dtype=torch.int8)
+    pairs = torch.stack(torch.meshgrid(allv, allv, indexing="ij"), -1).reshape(1, 1, 16, 32)
+    packed = pack_int4(pairs)
+    np.savez_compressed(os.path.join(HERE, "pack_int4.npz"), codes=_np(pairs), packed=_np(packed),
+                        unpacked=_np(unpack_int4(packed)))
+
+    # ------------------------------------------------------------------ attention
+    att = {}
+    cases = {
+        # name: (B, Hq, Hkv, S, gs, kind, outlier_ch, ctx)
+        "c1_small": (1, 12, 2, 300, 32, "int8", 4, [300]),
+        "gqa7_ragged": (3, 28, 4, 129, 32, "int8", 0, [129, 1, 64]),
+        "zero_ctx": (2, 8, 2, 40, 64, "int8", 0, [0, 40]),
+        "int4_g32": (2, 12, 2, 200, 32, "int4", 0, [200, 77]),
+        "int4_g16": (1, 40, 8, 96, 16, "int4", 0, [96]),
+        "mha_g128": (2, 4, 4, 65, 128, "int8", 0, [65, 33]),
+    }
+    for name, (b, hq, hkv, s, gs, kind, och, ctx) in cases.items():
+        d = 128
+        q = torch.randn(b, hq, d, generator=gen).half()
+        k = gen_kv(gen, b, hkv, s, d, outlier_ch=och)
+        v = gen_kv(gen, b, hkv, s, d, outlier_ch=och)
+        inv_tau = torch.empty(hq).uniform_(0.8, 1.2, generator=gen)
+        g = d // gs
+        if kind == "int8":
+            sc_k = (k.float().abs().view(b, hkv, s, g, gs).amax(dim=(0, 2, 4)) / 127.0).half()
+            sc_v = (v.float().abs().view(b, hkv, s, g, gs).amax(dim=(0, 2, 4)) / 127.0).half()
+            c = INT8KVCache(1, device="cpu", group_size=gs, static_k_scale=sc_k[None], static_v_scale=sc_v[None])
+            c.append(0, k, v)
+            qk, qv, sk, sv = c.get_int8_tensors(0)
+            k8, v8 = qk, qv
+        else:
+            sc_k = (k.float().abs().view(b, hkv, s, g, gs).amax(dim=(0, 2, 4)) / 7.0).float()
+            sc_v = (v.float().abs().view(b, hkv, s, g, gs).amax(dim=(0, 2, 4)) / 7.0).float()
+            c = INT4KVCache(1, device="cpu", group_size=gs, static_k_scale=sc_k[None], static_v_scale=sc_v[None])
+            c.append(0, k, v)
+            qk, qv, sk, sv = c.get_int4_tensors(0)
+            k8, v8 = unpack_int4(qk), unpack_int4(qv)
+        # inv_tau applied in fp16 before the kernel (patch_model.py:712-746)
+        q_scaled = q * inv_tau.to(torch.float16).view(1, -1, 1)
+        ctx_t = torch.tensor(ctx, dtype=torch.int32)
+        sm = 1.0 / (d ** 0.5)
+        ref = _decode_attn_int8_torch_ref(q_scaled, k8, v8, sk.half(), sv.half(), ctx_t, sm)
+        att[f"{name}_q"] = _np(q); att[f"{name}_inv_tau"] = _np(inv_tau)
+        att[f"{name}_k"] = _np(qk); att[f"{name}_v"] = _np(qv)
+        att[f"{name}_ks"] = _np(sk.half()); att[f"{name}_vs"] = _np(sv.half())
+        att[f"{name}_ctx"] = _np(ctx_t); att[f"{name}_out"] = _np(ref)
+        att[f"{name}_meta"] = np.array([b, hq, hkv, s, gs, 1 if kind == "int4" else 0])
+    np.savez_compressed(os.path.join(HERE, "attention.npz"), **att)
+    for f in ("quantizers.npz", "pack_int4.npz", "attention.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
+
+
+if __name__ == "__main__":
+    main()
