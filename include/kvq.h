@@ -1,0 +1,186 @@
+/*
+ * kvq.h - C ABI of libkvq: quantize-on-append and q_len==1 fused decode
+ * attention over a quantized KV cache, for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer owned by the caller unless stated;
+ *  - every entry point returns 0 (KVQ_OK) or a negative KVQ_E* code, never
+ *    throws, never traps; kvq_strerror() gives the text;
+ *  - `stream` is a cudaStream_t passed as void*; work is enqueued, not waited for;
+ *  - cache layout is the reference project's: payload [B, Hkv, S, Dp] with the
+ *    last dimension contiguous (Dp = D for fp16/int8, D/2 for packed int4),
+ *    scales / zero-points [B, Hkv, S, G] fp16, G = D / group_size
+ *    (reference: src/cache/int8_cache.py:101-106, src/cache/int4_cache.py:651-673).
+ *    All strides are given explicitly so that views into larger preallocated
+ *    buffers (capacity > S) can be passed without copies.
+ *
+ * Each declaration cites the reference interface it stands in for
+ * (paths relative to the reference project root).
+ */
+#ifndef KVQ_H_
+#define KVQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KVQ_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define KVQ_API __attribute__((visibility("default")))
+#else
+#define KVQ_API
+#endif
+
+/* status codes */
+#define KVQ_OK            0
+#define KVQ_EINVAL       -1  /* bad argument (shape, stride, alignment, NULL) */
+#define KVQ_EUNSUPPORTED -2  /* valid request this build has no kernel for */
+#define KVQ_ECUDA        -3  /* a CUDA runtime call failed; see kvq_last_cuda_error() */
+#define KVQ_EWORKSPACE   -4  /* workspace too small */
+#define KVQ_ELIMIT       -5  /* request exceeds a fixed limit of the entry point */
+
+/* payload formats */
+#define KVQ_FMT_FP16  0      /* fp16 [.., D]                                   */
+#define KVQ_FMT_INT8  1      /* int8 codes [.., D] (also unpacked int4 codes)  */
+#define KVQ_FMT_INT4  2      /* two codes per byte [.., D/2]:
+                                byte i = ((c[2i]+8) << 4) | (c[2i+1]+8)
+                                (reference: src/quant/int4_basic.py:260-272)   */
+
+/* how the group scale is obtained when appending */
+#define KVQ_SCALE_STATIC      0  /* calibrated [Hkv, G] table (+ flags below)    */
+#define KVQ_SCALE_DYNAMIC_PCT 1  /* per token-group percentile of |x|            */
+#define KVQ_SCALE_ASYM_MINMAX 2  /* per token-group min/max, scale + zero-point  */
+
+/* flags for KVQ_SCALE_STATIC */
+#define KVQ_F_ADAPTIVE     1  /* s = max(static*margin, absmax/qmax)  (int8_cache.py:392-402, int4_cache.py:451-455) */
+#define KVQ_F_MIXED_RESCUE 2  /* s = max(s, absmax/7)                 (int4_cache.py:456-459)                        */
+#define KVQ_F_RESCUE_THR   4  /* s = dyn >= *thr ? max(s,dyn) : s     (int4_cache.py:360-390)                        */
+
+typedef void* kvq_stream_t;
+
+/* One side (K or V) of an append. */
+typedef struct KvqAppendSide {
+    const void* src;          /* fp16 new tokens [B, Hkv, T, D], D contiguous             */
+    int64_t src_stride_b, src_stride_h, src_stride_t;   /* in elements                  */
+    void*   payload;          /* cache payload base (token 0), see formats above          */
+    int64_t pay_stride_b, pay_stride_h, pay_stride_s;   /* in BYTES                     */
+    void*   scale;            /* fp16 [B,Hkv,cap,G]; NULL for KVQ_FMT_FP16                */
+    void*   zp;               /* fp16 zero-points, same strides; KVQ_SCALE_ASYM_MINMAX only */
+    float*  scale_f32;        /* optional fp32 copy of the scale (same strides) or NULL   */
+    int64_t sc_stride_b, sc_stride_h, sc_stride_s;      /* in elements                  */
+    void*   side;             /* fp16 outlier side buffer [B,Hkv,cap,n_out] or NULL       */
+    int64_t side_stride_b, side_stride_h, side_stride_s; /* in elements                 */
+    const void*  static_scale;      /* [Hkv, G] contiguous; KVQ_SCALE_STATIC              */
+    int32_t      static_scale_is_f32; /* 0: fp16 table, 1: fp32 table                     */
+    const float* rescue_threshold;  /* device scalar, KVQ_F_RESCUE_THR                    */
+} KvqAppendSide;
+
+typedef struct KvqAppendArgs {
+    int32_t format;           /* KVQ_FMT_*                                                */
+    int32_t policy;           /* KVQ_SCALE_*                                              */
+    int32_t flags;            /* KVQ_F_*                                                  */
+    int32_t B, Hkv, T, D;
+    int32_t group_size;       /* divides D; 8..D                                          */
+    float   adaptive_margin;
+    float   quantile;         /* percentile/100 as fp32, KVQ_SCALE_DYNAMIC_PCT; >=1 means absmax */
+    int32_t n_out;            /* fp16 outlier channels per KV head (0 = none)             */
+    const int16_t* outlier_idx;   /* [Hkv, n_out] sorted channel indices                  */
+    int64_t write_pos;        /* first cache slot to write                                */
+    const int32_t* write_pos_dev; /* if not NULL the slot is read on the device instead   */
+    KvqAppendSide k, v;
+} KvqAppendArgs;
+
+/*
+ * Quantize T new tokens of K and V and write payload, scales (zero-points,
+ * outlier side buffer) at cache slots [write_pos, write_pos + T): ONE launch for
+ * both tensors (v.src == NULL quantizes the K side only).
+ * Stands in for INT8KVCache.append / INT4KVCache.append / FP16KVCache.append
+ * (src/cache/int8_cache.py:350-488, src/cache/int4_cache.py:392-589,
+ *  src/cache/fp16_cache.py) and the quantizers they call
+ * (src/quant/int8_basic.py:18-164, src/quant/int4_basic.py:24-159, :230-272,
+ *  src/quant/asymmetric_quant.py:24-141 applied group-wise).
+ * Codes, packed bytes and fp16 scales are bit-identical to those functions.
+ */
+KVQ_API int kvq_quantize_append(const KvqAppendArgs* args, kvq_stream_t stream);
+
+/* One side (K or V) of the cache as the attention kernel reads it. */
+typedef struct KvqCacheSide {
+    const void* payload;
+    int64_t pay_stride_b, pay_stride_h, pay_stride_s;   /* BYTES                         */
+    const void* scale;        /* fp16; strides may be 0 to broadcast a static table       */
+    const void* zp;           /* fp16 or NULL                                             */
+    int64_t sc_stride_b, sc_stride_h, sc_stride_s;      /* elements                      */
+    const void* side;         /* fp16 outlier values [B,Hkv,S,n_out] or NULL              */
+    int64_t side_stride_b, side_stride_h, side_stride_s; /* elements                     */
+} KvqCacheSide;
+
+typedef struct KvqAttnArgs {
+    int32_t format;           /* KVQ_FMT_*                                                */
+    int32_t B, Hq, Hkv, D;
+    int32_t group_size;
+    int32_t max_ctx;          /* upper bound of context_lens (the S extent of the views)  */
+    const void* q;            /* fp16 [B, Hq, D], D contiguous                            */
+    int64_t q_stride_b, q_stride_h;                     /* elements                      */
+    const float* inv_tau;     /* fp32 [Hq] or NULL: q <- RN16(q * RN16(inv_tau[h]))       */
+    float   sm_scale;
+    KvqCacheSide k, v;
+    int32_t n_out;
+    const int16_t* outlier_idx;  /* [Hkv, n_out]                                          */
+    const int32_t* context_lens; /* int32 [B]; values are clamped to [0, max_ctx]         */
+    int32_t splits;           /* KV splits per (batch, kv head); 0 = library heuristic    */
+    void*   workspace;        /* >= kvq_decode_workspace_bytes(...)                       */
+    size_t  workspace_bytes;
+    void*   out;              /* fp16 [B, Hq, D] or NULL                                  */
+    int64_t out_stride_b, out_stride_h;                 /* elements                      */
+    /* optional normalised partial for a cross-GPU merge (all three or none):            */
+    float*  part_o;           /* fp32 [B, Hq, D]  o = sum p v / l                         */
+    float*  part_m;           /* fp32 [B, Hq]     running max of scaled logits (-inf if empty) */
+    float*  part_l;           /* fp32 [B, Hq]     sum exp(logit - m)  (0 if empty)        */
+} KvqAttnArgs;
+
+/*
+ * out[b,h,:] = softmax(sm_scale * q[b,h] . Khat[b, h / n_rep, :ctx_b]^T) Vhat,
+ * Khat = RN16(fp16(code) * scale) (+ zero-point, outlier side values), split-K
+ * flash-decoding over the KV axis followed by a log-sum-exp combine.
+ * Rows with context 0 give zeros (never NaN).
+ * Stands in for decode_attn_int8 / decode_attn_int4
+ * (src/kernels/triton_decode_attn_int8.py:306-519,
+ *  src/kernels/triton_decode_attn_int4.py:62-121) and matches
+ * _decode_attn_int8_torch_ref (src/engine/patch_model.py:281-377) within
+ * |a-b| <= 2e-3 + 1e-2 |b|.
+ */
+KVQ_API int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream);
+
+KVQ_API size_t kvq_decode_workspace_bytes(int32_t B, int32_t Hq, int32_t D, int32_t splits);
+/* split count the library would choose for this shape on the current device */
+KVQ_API int32_t kvq_decode_pick_splits(int32_t B, int32_t Hkv, int32_t max_ctx);
+
+typedef struct KvqCombineArgs {
+    int32_t P, B, Hq, D;      /* P partials (e.g. one per GPU)                            */
+    const float* part_o;      /* fp32 [P, B, Hq, D] normalised partial outputs            */
+    const float* part_m;      /* fp32 [P, B, Hq]                                          */
+    const float* part_l;      /* fp32 [P, B, Hq]                                          */
+    void*   out;              /* fp16 [B, Hq, D]                                          */
+    int64_t out_stride_b, out_stride_h;
+} KvqCombineArgs;
+
+/*
+ * Merge P normalised partials: M = max m_p,
+ * out = sum_p o_p l_p e^(m_p - M) / sum_p l_p e^(m_p - M); all-empty rows give 0.
+ * No counterpart in the reference (it has no sequence sharding); the math is the
+ * online-softmax merge of src/kernels/triton_decode_attn_int8.py:247-283.
+ */
+KVQ_API int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream);
+
+KVQ_API const char* kvq_strerror(int code);
+KVQ_API int  kvq_last_cuda_error(void);     /* cudaError_t of the last KVQ_ECUDA on this thread */
+KVQ_API int  kvq_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVQ_H_ */

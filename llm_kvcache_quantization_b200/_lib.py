@@ -1,0 +1,135 @@
+"""ctypes binding of libkvq.so (the C ABI declared in include/kvq.h).
+
+The library is the only compute path of this package: if it cannot be loaded
+the import of any kernel entry point raises; there is no CPU or torch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+KVQ_OK = 0
+KVQ_EINVAL = -1
+KVQ_EUNSUPPORTED = -2
+KVQ_ECUDA = -3
+KVQ_EWORKSPACE = -4
+KVQ_ELIMIT = -5
+
+FMT_FP16, FMT_INT8, FMT_INT4 = 0, 1, 2
+SCALE_STATIC, SCALE_DYNAMIC_PCT, SCALE_ASYM_MINMAX = 0, 1, 2
+F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR = 1, 2, 4
+
+_i64, _i32, _vp, _f32 = C.c_int64, C.c_int32, C.c_void_p, C.c_float
+
+
+class KvqAppendSide(C.Structure):
+    _fields_ = [
+        ("src", _vp), ("src_stride_b", _i64), ("src_stride_h", _i64), ("src_stride_t", _i64),
+        ("payload", _vp), ("pay_stride_b", _i64), ("pay_stride_h", _i64), ("pay_stride_s", _i64),
+        ("scale", _vp), ("zp", _vp), ("scale_f32", _vp),
+        ("sc_stride_b", _i64), ("sc_stride_h", _i64), ("sc_stride_s", _i64),
+        ("side", _vp), ("side_stride_b", _i64), ("side_stride_h", _i64), ("side_stride_s", _i64),
+        ("static_scale", _vp), ("static_scale_is_f32", _i32), ("rescue_threshold", _vp),
+    ]
+
+
+class KvqAppendArgs(C.Structure):
+    _fields_ = [
+        ("format", _i32), ("policy", _i32), ("flags", _i32),
+        ("B", _i32), ("Hkv", _i32), ("T", _i32), ("D", _i32), ("group_size", _i32),
+        ("adaptive_margin", _f32), ("quantile", _f32),
+        ("n_out", _i32), ("outlier_idx", _vp),
+        ("write_pos", _i64), ("write_pos_dev", _vp),
+        ("k", KvqAppendSide), ("v", KvqAppendSide),
+    ]
+
+
+class KvqCacheSide(C.Structure):
+    _fields_ = [
+        ("payload", _vp), ("pay_stride_b", _i64), ("pay_stride_h", _i64), ("pay_stride_s", _i64),
+        ("scale", _vp), ("zp", _vp),
+        ("sc_stride_b", _i64), ("sc_stride_h", _i64), ("sc_stride_s", _i64),
+        ("side", _vp), ("side_stride_b", _i64), ("side_stride_h", _i64), ("side_stride_s", _i64),
+    ]
+
+
+class KvqAttnArgs(C.Structure):
+    _fields_ = [
+        ("format", _i32), ("B", _i32), ("Hq", _i32), ("Hkv", _i32), ("D", _i32),
+        ("group_size", _i32), ("max_ctx", _i32),
+        ("q", _vp), ("q_stride_b", _i64), ("q_stride_h", _i64),
+        ("inv_tau", _vp), ("sm_scale", _f32),
+        ("k", KvqCacheSide), ("v", KvqCacheSide),
+        ("n_out", _i32), ("outlier_idx", _vp),
+        ("context_lens", _vp),
+        ("splits", _i32),
+        ("workspace", _vp), ("workspace_bytes", C.c_size_t),
+        ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
+        ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),
+    ]
+
+
+class KvqCombineArgs(C.Structure):
+    _fields_ = [
+        ("P", _i32), ("B", _i32), ("Hq", _i32), ("D", _i32),
+        ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),
+        ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
+    ]
+
+
+# every symbol include/kvq.h declares: (name, restype, argtypes)
+EXPORTS = (
+    ("kvq_quantize_append", C.c_int, (C.POINTER(KvqAppendArgs), _vp)),
+    ("kvq_decode_attn", C.c_int, (C.POINTER(KvqAttnArgs), _vp)),
+    ("kvq_decode_workspace_bytes", C.c_size_t, (_i32, _i32, _i32, _i32)),
+    ("kvq_decode_pick_splits", _i32, (_i32, _i32, _i32)),
+    ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
+    ("kvq_strerror", C.c_char_p, (C.c_int,)),
+    ("kvq_last_cuda_error", C.c_int, ()),
+    ("kvq_abi_version", C.c_int, ()),
+)
+
+_LIB = None
+
+
+class KvqError(RuntimeError):
+    """A libkvq entry point returned a non-zero status."""
+
+    def __init__(self, fn: str, code: int, text: str):
+        super().__init__(f"{fn} failed: {text} (code {code})")
+        self.code = code
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load():
+    """Load libkvq.so (once).  Raises if the library is missing: there is no fallback."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = lib_path()
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing. Build it with `python -m llm_kvcache_quantization_b200.build` "
+            "(needs nvcc); this package has no CPU or pure-torch fallback.")
+    lib = C.CDLL(path)
+    for name, restype, argtypes in EXPORTS:
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = list(argtypes)
+    _LIB = lib
+    return lib
+
+
+def check(fn: str, code: int) -> None:
+    if code == KVQ_OK:
+        return
+    lib = load()
+    text = lib.kvq_strerror(code).decode()
+    if code == KVQ_ECUDA:
+        text += f" [cudaError {lib.kvq_last_cuda_error()}]"
+    raise KvqError(fn, code, text)

@@ -1,0 +1,576 @@
+"""KV caches with quantize-on-append, API-compatible with the reference's
+`INT8KVCache`, `INT4KVCache` and `FP16KVCache`
+(src/cache/int8_cache.py:29-682, src/cache/int4_cache.py:32-773,
+ src/cache/fp16_cache.py:26-370, src/cache/protocol.py:30-63).
+
+What is the same: constructor arguments, `append / get_kv / get_int8_tensors /
+get_int4_tensors / get_seq_len / clear / release / get_memory_mb / to_tuple /
+from_tuple`, the decode-stat counters, the growth policy (first allocation
+`max(target, 256)`, then doubling, capped by `max_seq_len`), the exceptions, and
+the stored codes / packed bytes, which are bit-identical.
+
+What is different, on purpose:
+* `append` is ONE kernel launch for K and V (scale policy, quantization, nibble
+  packing and the slot write fused) instead of ~30 eager ops and host syncs.
+* Scales are stored in fp16 - the value the decode kernel and the torch reference
+  consume (`scale.to(float16)`, src/engine/patch_model.py:909-917, 927-933) - so
+  the per-call cast disappears and scale traffic halves.  `keep_fp32_scales=True`
+  keeps the reference's fp32 copy as well (`get_fp32_scales`).
+* The clip-ratio warnings (ENG-040 / KVC-021) and the NaN/Inf guard each need a
+  host sync per append; they run only with `validate_inputs=True` (or `KVQ_VALIDATE=1`).
+* Two formats the reference lacks: group-wise asymmetric INT4 (`asymmetric=True`)
+  and an fp16 outlier-channel side buffer (`outlier_idx=`).
+"""
+from __future__ import annotations
+
+import logging
+import os
+import warnings
+from typing import Dict, List, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import ops, quant
+from ._lib import (FMT_FP16, FMT_INT4, FMT_INT8, F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR,
+                   SCALE_ASYM_MINMAX, SCALE_DYNAMIC_PCT, SCALE_STATIC)
+
+logger = logging.getLogger(__name__)
+_CLIP_WARN_THRESHOLD = 0.01
+
+
+def _new_stats() -> Dict[str, object]:
+    return {"fused_decode_calls": 0, "triton_kernel_calls": 0, "triton_decode_calls": 0,
+            "torch_ref_calls": 0, "layer_hits": {}, "triton_layer_hits": {}}
+
+
+class _CacheBase:
+    """Storage, growth and bookkeeping shared by the three caches."""
+
+    _fmt = FMT_INT8
+    _qmax = 127.0
+
+    def __init__(self, num_layers: int, device="cuda", dtype: torch.dtype = torch.float16,
+                 max_seq_len: Optional[int] = None):
+        if num_layers <= 0:
+            raise ValueError(f"num_layers must be > 0, got {num_layers}")
+        self.num_layers = num_layers
+        self.device = device
+        self.dtype = dtype
+        self.max_seq_len = int(max_seq_len) if max_seq_len is not None else None
+        if self.max_seq_len is not None and self.max_seq_len <= 0:
+            raise ValueError(f"max_seq_len must be > 0, got {self.max_seq_len}")
+        self._min_capacity = 256
+        self._bufs: List[Optional[Dict[str, Tensor]]] = [None] * num_layers
+        self._layer_seq_lens: List[int] = [0] * num_layers
+        self._layer_capacity: List[int] = [0] * num_layers
+        self._seq_len = 0
+        self.decode_stats: Dict[str, object] = _new_stats()
+
+    # ---- decode statistics (key names are read by the reference's callers/tests)
+    def _bump_counter(self, key: str, delta: int = 1) -> None:
+        self.decode_stats[key] = int(self.decode_stats.get(key, 0)) + int(delta)
+
+    def record_fused_decode(self, layer_id: int, decode_impl: str) -> None:
+        self._bump_counter("fused_decode_calls", 1)
+        if decode_impl == "triton_fused":
+            self._bump_counter("triton_decode_calls", 1)
+        elif decode_impl == "torch_ref":
+            self._bump_counter("torch_ref_calls", 1)
+        hits = self.decode_stats.setdefault("layer_hits", {})
+        hits[str(layer_id)] = int(hits.get(str(layer_id), 0)) + 1
+
+    def record_triton_kernel_call(self, layer_id: Optional[int] = None) -> None:
+        self._bump_counter("triton_kernel_calls", 1)
+        if layer_id is None:
+            return
+        hits = self.decode_stats.setdefault("triton_layer_hits", {})
+        hits[str(layer_id)] = int(hits.get(str(layer_id), 0)) + 1
+
+    def reset_decode_stats(self) -> None:
+        self.decode_stats = _new_stats()
+
+    def get_decode_stats(self) -> Dict[str, object]:
+        s = self.decode_stats
+        return {k: (dict(s.get(k, {})) if k.endswith("hits") else int(s.get(k, 0))) for k in _new_stats()}
+
+    # ---- storage
+    def _buffer_specs(self, batch, heads, head_dim) -> Dict[str, Tuple[Tuple[int, ...], torch.dtype]]:
+        raise NotImplementedError
+
+    def _alloc(self, specs, capacity) -> Dict[str, Tensor]:
+        out = {}
+        for name, (tail, dt) in specs.items():
+            b, h, w = tail
+            out[name] = torch.empty((b, h, capacity, w), device=self.device, dtype=dt)
+        return out
+
+    def _ensure_capacity(self, layer_id: int, batch: int, heads: int, head_dim: int, target_len: int) -> None:
+        if self.max_seq_len is not None and target_len > self.max_seq_len:
+            raise ValueError(
+                f"target_len {target_len} exceeds max_seq_len {self.max_seq_len} for layer {layer_id}")
+        specs = self._buffer_specs(batch, heads, head_dim)
+        bufs = self._bufs[layer_id]
+        capacity = self._layer_capacity[layer_id]
+        if bufs is not None:
+            for name, (tail, _) in specs.items():
+                t = bufs[name]
+                if (t.shape[0], t.shape[1], t.shape[3]) != tail:
+                    raise ValueError(
+                        f"Inconsistent KV shape for layer {layer_id}: existing {name}={tuple(t.shape)}, "
+                        f"incoming=({batch}, {heads}, *, {head_dim})")
+            if target_len <= capacity:
+                return
+            new_capacity = max(target_len, capacity * 2)
+        else:
+            new_capacity = max(target_len, self._min_capacity)
+        if self.max_seq_len is not None:
+            new_capacity = min(new_capacity, self.max_seq_len)
+            if new_capacity < target_len:
+                raise ValueError(
+                    f"target_len {target_len} exceeds capped capacity {new_capacity} for layer {layer_id}")
+        new = self._alloc(specs, new_capacity)     # an OOM here leaves the layer untouched
+        old_len = self._layer_seq_lens[layer_id]
+        if bufs is not None and old_len > 0:
+            for name in new:
+                new[name][:, :, :old_len] = bufs[name][:, :, :old_len]
+        self._bufs[layer_id] = new
+        self._layer_capacity[layer_id] = new_capacity
+
+    def reserve(self, layer_id: int, batch: int, heads: int, head_dim: int, capacity: int) -> None:
+        """Preallocate `capacity` slots so that later appends never reallocate
+        (views handed to the decode kernel stay valid; required for CUDA graphs)."""
+        self._ensure_capacity(layer_id, batch, heads, head_dim, capacity)
+
+    def _check_append(self, layer_id: int, k: Tensor, v: Tensor) -> None:
+        if layer_id < 0 or layer_id >= self.num_layers:
+            raise ValueError(f"layer_id {layer_id} out of range")
+        if k.ndim != 4:
+            raise ValueError(f"k must be 4D [B,H,S,D], got ndim={k.ndim}")
+        if v.ndim != 4:
+            raise ValueError(f"v must be 4D [B,H,S,D], got ndim={v.ndim}")
+        if tuple(k.shape) != tuple(v.shape):
+            raise ValueError(f"k/v shape mismatch: k={tuple(k.shape)} vs v={tuple(v.shape)}")
+        target = torch.device(self.device)
+        if k.device.type != target.type or v.device.type != target.type:
+            raise ValueError(f"Device mismatch: cache_device={target}, k.device={k.device}, v.device={v.device}")
+        if not k.is_cuda:
+            raise ValueError("this cache quantizes with a CUDA kernel; CPU tensors are not supported")
+
+    def _layer_view(self, layer_id: int, names) -> Tuple[Tensor, ...]:
+        if layer_id < 0 or layer_id >= self.num_layers:
+            raise ValueError(f"layer_id {layer_id} out of range [0, {self.num_layers})")
+        bufs = self._bufs[layer_id]
+        if bufs is None:
+            raise ValueError(f"Cache for layer {layer_id} is empty")
+        n = self._layer_seq_lens[layer_id]
+        return tuple(bufs[name][:, :, :n] for name in names)
+
+    def _finish_append(self, layer_id: int, target_len: int) -> None:
+        self._layer_seq_lens[layer_id] = target_len
+        if layer_id == 0:
+            self._seq_len = target_len
+
+    def get_seq_len(self) -> int:
+        return self._seq_len
+
+    def clear(self) -> None:
+        """Reset lengths, keep the buffers."""
+        self._layer_seq_lens = [0] * self.num_layers
+        self._seq_len = 0
+
+    def release(self) -> None:
+        self._bufs = [None] * self.num_layers
+        self._layer_seq_lens = [0] * self.num_layers
+        self._layer_capacity = [0] * self.num_layers
+        self._seq_len = 0
+
+    def get_memory_mb(self) -> float:
+        total = 0
+        for bufs in self._bufs:
+            if bufs is not None:
+                total += sum(t.numel() * t.element_size() for t in bufs.values())
+        return total / (1024 * 1024)
+
+    def to_tuple(self) -> Tuple[Tuple[Tensor, Tensor], ...]:
+        out = []
+        for i in range(self.num_layers):
+            if self._bufs[i] is None:
+                raise ValueError(f"Layer {i} cache is empty")
+            out.append(self.get_kv(i))
+        return tuple(out)
+
+    def __repr__(self) -> str:
+        return (f"{type(self).__name__}(num_layers={self.num_layers}, seq_len={self._seq_len}, "
+                f"memory={self.get_memory_mb():.2f}MB)")
+
+
+class FP16KVCache(_CacheBase):
+    """Unquantized cache (src/cache/fp16_cache.py:26-370) with the same slot-write kernel."""
+
+    _fmt = FMT_FP16
+
+    def __init__(self, num_layers: int, device="cuda", dtype: torch.dtype = torch.float16,
+                 max_seq_len: Optional[int] = None):
+        super().__init__(num_layers, device, dtype, max_seq_len)
+
+    def _buffer_specs(self, batch, heads, head_dim):
+        return {"k": ((batch, heads, head_dim), torch.float16), "v": ((batch, heads, head_dim), torch.float16)}
+
+    def append(self, layer_id: int, k: Tensor, v: Tensor) -> None:
+        self._check_append(layer_id, k, v)
+        B, H, T, D = k.shape
+        old = self._layer_seq_lens[layer_id]
+        self._ensure_capacity(layer_id, B, H, D, old + T)
+        bufs = self._bufs[layer_id]
+        ops.quantize_append(FMT_FP16, SCALE_STATIC, k.to(torch.float16), v.to(torch.float16),
+                            bufs["k"], bufs["v"], None, None, old, D)
+        self._finish_append(layer_id, old + T)
+
+    def get_kv(self, layer_id: int) -> Tuple[Tensor, Tensor]:
+        k, v = self._layer_view(layer_id, ("k", "v"))
+        return k.to(self.dtype), v.to(self.dtype)
+
+    def get_fp16_tensors(self, layer_id: int) -> Tuple[Tensor, Tensor]:
+        return self._layer_view(layer_id, ("k", "v"))
+
+    @classmethod
+    def from_tuple(cls, past_key_values, device="cuda") -> "FP16KVCache":
+        cache = cls(num_layers=len(past_key_values), device=device)
+        for i, item in enumerate(past_key_values):
+            cache.append(i, item[0].to(device), item[1].to(device))
+        return cache
+
+
+class _QuantCache(_CacheBase):
+    """Common part of the INT8 and INT4 caches: scale policy selection and the fused append."""
+
+    def __init__(self, num_layers, device, clip_percentile, group_size, dtype, max_seq_len,
+                 decode_attn_impl, static_k_scale, static_v_scale, inv_tau, use_attn_temperature,
+                 adaptive_static_scales, adaptive_static_margin, adaptive_static_k, adaptive_static_v,
+                 keep_fp32_scales, validate_inputs):
+        super().__init__(num_layers, device, dtype, max_seq_len)
+        if adaptive_static_margin <= 0:
+            raise ValueError(f"adaptive_static_margin must be > 0, got {adaptive_static_margin}")
+        self.clip_percentile = clip_percentile
+        self.group_size = group_size
+        self.decode_attn_impl = decode_attn_impl
+        self.static_k_scale = static_k_scale
+        self.static_v_scale = static_v_scale
+        self.inv_tau = inv_tau
+        self.use_attn_temperature = use_attn_temperature
+        self.adaptive_static_scales = adaptive_static_scales
+        self.adaptive_static_margin = adaptive_static_margin
+        self.adaptive_static_k = adaptive_static_k
+        self.adaptive_static_v = adaptive_static_v
+        self.keep_fp32_scales = bool(keep_fp32_scales)
+        self.validate_inputs = bool(validate_inputs) or os.environ.get("KVQ_VALIDATE", "0") == "1"
+        self.asymmetric = False
+        self.outlier_idx = None          # int16 [L, Hkv, n_out] or None
+        self._scale_dtype = torch.float16
+        self._static_tables: Dict[Tuple[str, int], Tensor] = {}
+
+    # payload width in bytes for head_dim D
+    def _payload_dim(self, head_dim: int) -> int:
+        return head_dim
+
+    def _num_groups(self, head_dim: int) -> int:
+        gs = head_dim if self.group_size == -1 else self.group_size
+        if gs <= 0 or head_dim % gs != 0:
+            raise ValueError(f"head_dim {head_dim} must be divisible by group_size {self.group_size}")
+        return head_dim // gs
+
+    def _buffer_specs(self, batch, heads, head_dim):
+        G = self._num_groups(head_dim)
+        dp = self._payload_dim(head_dim)
+        specs = {"k": ((batch, heads, dp), torch.int8), "v": ((batch, heads, dp), torch.int8),
+                 "ks": ((batch, heads, G), torch.float16), "vs": ((batch, heads, G), torch.float16)}
+        if self.keep_fp32_scales:
+            specs["ks32"] = ((batch, heads, G), torch.float32)
+            specs["vs32"] = ((batch, heads, G), torch.float32)
+        if self.asymmetric:
+            specs["kz"] = ((batch, heads, G), torch.float16)
+            specs["vz"] = ((batch, heads, G), torch.float16)
+        if self.outlier_idx is not None:
+            n_out = int(self.outlier_idx.shape[-1])
+            specs["kside"] = ((batch, heads, n_out), torch.float16)
+            specs["vside"] = ((batch, heads, n_out), torch.float16)
+        return specs
+
+    def _static_table(self, which: str, layer_id: int, heads: int, G: int, device) -> Tensor:
+        """The calibrated [Hkv, G] table of one layer on the right device, validated once."""
+        key = (which, layer_id)
+        tab = self._static_tables.get(key)
+        if tab is None:
+            src = self.static_k_scale if which == "k" else self.static_v_scale
+            tab = src[layer_id]
+            if not isinstance(tab, Tensor):
+                tab = torch.as_tensor(tab)
+            if tab.ndim == 5 and tab.shape[-1] == 1:
+                tab = tab[..., 0]
+            if tab.ndim == 3 and tab.shape[1] == 1:          # legacy [H,1,G]
+                tab = tab[:, 0, :]
+            elif tab.ndim == 3 and tab.shape[2] == 1:        # legacy [H,G,1]
+                tab = tab[..., 0]
+            elif tab.ndim == 3 and tab.shape[0] == 1:        # [1,H,G]
+                tab = tab[0]
+            elif tab.ndim == 4 and tab.shape[0] == 1 and tab.shape[2] == 1:   # [1,H,1,G]
+                tab = tab[0, :, 0, :]
+            if tab.ndim != 2:
+                raise ValueError(f"Unsupported static scale shape: {tuple(tab.shape)}")
+            if tab.shape[0] != heads:
+                raise ValueError(
+                    "_normalize_static_scale: calibration vs model heads mismatch "
+                    "(fail-fast; wrong calibration file was loaded).\n"
+                    f"  expected heads: {heads} (from model/cache config)\n"
+                    f"  scale heads:    {tab.shape[0]} (from scale.shape={tuple(tab.shape)})\n"
+                    f"  num_groups:     {G}\n  layer_id:       {layer_id}")
+            if tab.shape[1] != G:
+                raise ValueError(
+                    f"static scale has {tab.shape[1]} groups but head_dim/group_size gives {G}")
+            if tab.dtype not in (torch.float16, torch.float32):
+                tab = tab.float()
+            tab = tab.to(device).contiguous()
+            self._static_tables[key] = tab
+        return tab
+
+    def _rescue_threshold(self, x: Tensor, G: int) -> Optional[Tensor]:
+        return None
+
+    def _append_impl(self, layer_id: int, k: Tensor, v: Tensor, extra_flags: int = 0) -> None:
+        self._check_append(layer_id, k, v)
+        for nm, sc in (("static_k_scale", self.static_k_scale), ("static_v_scale", self.static_v_scale)):
+            if sc is not None and layer_id >= len(sc):
+                raise IndexError(f"layer_id {layer_id} exceeds calibration layers {len(sc)} for {nm}")
+        if (self.static_k_scale is None) != (self.static_v_scale is None) and not self.asymmetric:
+            raise ValueError("static_k_scale and static_v_scale must be given together "
+                             "(K and V are quantized by one fused launch)")
+        if k.dtype != torch.float16:
+            k, v = k.to(torch.float16), v.to(torch.float16)
+        if self.validate_inputs:
+            quant._check_quantize_input(k, "append(k)")
+            quant._check_quantize_input(v, "append(v)")
+        B, H, T, D = k.shape
+        G = self._num_groups(D)
+        gs = D // G
+        old = self._layer_seq_lens[layer_id]
+        self._ensure_capacity(layer_id, B, H, D, old + T)
+        bufs = self._bufs[layer_id]
+        kw = dict(k_scale_f32=bufs.get("ks32"), v_scale_f32=bufs.get("vs32"))
+        oidx = None
+        if self.outlier_idx is not None:
+            oidx = self.outlier_idx[layer_id].to(device=k.device, dtype=torch.int16).contiguous()
+            kw.update(outlier_idx=oidx, k_side=bufs["kside"], v_side=bufs["vside"])
+        flags = 0
+        if self.asymmetric:
+            policy = SCALE_ASYM_MINMAX
+            kw.update(k_zp=bufs["kz"], v_zp=bufs["vz"])
+        elif self.static_k_scale is not None:
+            policy = SCALE_STATIC
+            kw.update(k_static=self._static_table("k", layer_id, H, G, k.device),
+                      v_static=self._static_table("v", layer_id, H, G, k.device))
+            if self.adaptive_static_scales:
+                if self.adaptive_static_k != self.adaptive_static_v:
+                    raise ValueError("adaptive_static_k and adaptive_static_v must agree in the fused append")
+                if self.adaptive_static_k:
+                    flags |= F_ADAPTIVE
+            flags |= extra_flags
+            if flags & F_RESCUE_THR:
+                kw.update(k_rescue_thr=self._rescue_threshold(k, G), v_rescue_thr=self._rescue_threshold(v, G))
+        else:
+            policy = SCALE_DYNAMIC_PCT
+            p = float(self.clip_percentile)
+            kw.update(quantile=(max(min(p / 100.0, 1.0), 0.0) if p < 100.0 else 1.0))
+        ops.quantize_append(self._fmt, policy, k, v, bufs["k"], bufs["v"], bufs["ks"], bufs["vs"], old, gs,
+                            flags=flags, adaptive_margin=float(self.adaptive_static_margin), **kw)
+        self._finish_append(layer_id, old + T)
+        if self.validate_inputs and policy == SCALE_STATIC:
+            self._warn_if_clipped(layer_id, k, v, old, T)
+
+    def _warn_if_clipped(self, layer_id, k, v, old, T) -> None:
+        bufs = self._bufs[layer_id]
+        for nm, x, code, sc in (("K", k, bufs["k"], bufs["ks"]), ("V", v, bufs["v"], bufs["vs"])):
+            B, H, _, D = x.shape
+            G = sc.shape[-1]
+            bound = (sc[:, :, old:old + T].float() * self._qmax).unsqueeze(-1)
+            ratio = float((x.float().view(B, H, T, G, D // G).abs() > bound * (1 + 2 ** -10)).float().mean())
+            if ratio > _CLIP_WARN_THRESHOLD:
+                warnings.warn(
+                    f"Static {nm} scale overflow at layer {layer_id}: {ratio:.1%} of values exceed scale "
+                    f"capacity (threshold={_CLIP_WARN_THRESHOLD:.0%}). Consider re-calibrating or enabling "
+                    "adaptive_static_scales.", RuntimeWarning)
+
+    def get_fp32_scales(self, layer_id: int) -> Tuple[Tensor, Tensor]:
+        if not self.keep_fp32_scales:
+            raise ValueError("construct the cache with keep_fp32_scales=True to keep fp32 scale copies")
+        return self._layer_view(layer_id, ("ks32", "vs32"))
+
+    def get_decode_tensors(self, layer_id: int) -> Dict[str, Optional[Tensor]]:
+        """Everything the fused decode kernel reads for this layer, as views."""
+        names = ["k", "v", "ks", "vs"]
+        if self.asymmetric:
+            names += ["kz", "vz"]
+        if self.outlier_idx is not None:
+            names += ["kside", "vside"]
+        vals = dict(zip(names, self._layer_view(layer_id, names)))
+        vals["outlier_idx"] = None if self.outlier_idx is None else self.outlier_idx[layer_id]
+        return vals
+
+    def release(self) -> None:
+        super().release()
+        self.static_k_scale = None
+        self.static_v_scale = None
+        self.inv_tau = None
+        self._static_tables.clear()
+
+
+class INT8KVCache(_QuantCache):
+    """INT8 symmetric group-wise cache (src/cache/int8_cache.py:29-682)."""
+
+    _fmt = FMT_INT8
+    _qmax = 127.0
+
+    def __init__(self, num_layers: int, device="cuda", clip_percentile: float = 99.9, group_size: int = 128,
+                 dtype: torch.dtype = torch.float16, max_seq_len: Optional[int] = None,
+                 decode_attn_impl: str = "triton_fused", static_k_scale=None, static_v_scale=None,
+                 inv_tau: Optional[Tensor] = None, use_attn_temperature: bool = True,
+                 adaptive_static_scales: bool = False, adaptive_static_margin: float = 1.0,
+                 adaptive_static_k: bool = True, adaptive_static_v: bool = True, *,
+                 keep_fp32_scales: bool = False, validate_inputs: bool = False):
+        super().__init__(num_layers, device, clip_percentile, group_size, dtype, max_seq_len, decode_attn_impl,
+                         static_k_scale, static_v_scale, inv_tau, use_attn_temperature, adaptive_static_scales,
+                         adaptive_static_margin, adaptive_static_k, adaptive_static_v, keep_fp32_scales,
+                         validate_inputs)
+
+    def append(self, layer_id: int, k: Tensor, v: Tensor) -> None:
+        """Quantize and append (src/cache/int8_cache.py:350-488)."""
+        self._append_impl(layer_id, k, v)
+
+    def get_int8_tensors(self, layer_id: int) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+        """(k_int8, v_int8, k_scale, v_scale) views of the valid tokens; scales are fp16."""
+        return self._layer_view(layer_id, ("k", "v", "ks", "vs"))
+
+    def get_kv(self, layer_id: int) -> Tuple[Tensor, Tensor]:
+        k, v, ks, vs = self.get_int8_tensors(layer_id)
+        if k.shape[2] == 0:
+            logger.warning("get_kv(layer_id=%d) returning zero-length tensors.", layer_id)
+        # fp32 product then one rounding, as the reference's fp32-scale dequant (int8_cache.py:536-542)
+        return (quant.dequantize_symmetric_int8(k, ks.float()).to(self.dtype),
+                quant.dequantize_symmetric_int8(v, vs.float()).to(self.dtype))
+
+    @classmethod
+    def from_tuple(cls, past_key_values, device="cuda", clip_percentile: float = 99.9,
+                   group_size: int = 128) -> "INT8KVCache":
+        cache = cls(num_layers=len(past_key_values), device=device, clip_percentile=clip_percentile,
+                    group_size=group_size)
+        for i, item in enumerate(past_key_values):
+            cache.append(i, item[0].to(device), item[1].to(device))
+        return cache
+
+
+class INT4KVCache(_QuantCache):
+    """INT4 group-wise cache, nibble-packed by default (src/cache/int4_cache.py:32-773).
+
+    `mixed_rescue` / `outlier_rescue_ratio` keep the reference's meaning (scale
+    adjustments).  `asymmetric=True` stores group-wise min/max quantization with
+    fp16 scale + zero-point; `outlier_idx` (int16 [L, Hkv, n_out]) keeps the listed
+    channels in an fp16 side buffer - both are extensions."""
+
+    _fmt = FMT_INT4
+    _qmax = 7.0
+
+    def __init__(self, num_layers: int, device="cuda", clip_percentile: float = 99.9, group_size: int = 32,
+                 dtype: torch.dtype = torch.float16, max_seq_len: Optional[int] = None,
+                 decode_attn_impl: str = "triton_fused", static_k_scale=None, static_v_scale=None,
+                 inv_tau: Optional[Tensor] = None, use_attn_temperature: bool = True,
+                 adaptive_static_scales: bool = False, adaptive_static_margin: float = 1.0,
+                 adaptive_static_k: bool = True, adaptive_static_v: bool = True,
+                 bit_packed: bool = True, outlier_rescue_ratio: float = 0.0, mixed_rescue: bool = False, *,
+                 asymmetric: bool = False, outlier_idx: Optional[Tensor] = None,
+                 keep_fp32_scales: bool = False, validate_inputs: bool = False):
+        super().__init__(num_layers, device, clip_percentile, group_size, dtype, max_seq_len, decode_attn_impl,
+                         static_k_scale, static_v_scale, inv_tau, use_attn_temperature, adaptive_static_scales,
+                         adaptive_static_margin, adaptive_static_k, adaptive_static_v, keep_fp32_scales,
+                         validate_inputs)
+        if outlier_rescue_ratio < 0:
+            raise ValueError(f"outlier_rescue_ratio must be >= 0, got {outlier_rescue_ratio}")
+        if not bit_packed:
+            raise ValueError("this cache stores INT4 nibble-packed only (bit_packed=True); "
+                             "decode_attn_int4(bit_packed=False) still accepts unpacked tensors")
+        self.bit_packed = True
+        self.outlier_rescue_ratio = float(outlier_rescue_ratio)
+        self.mixed_rescue = bool(mixed_rescue)
+        self.asymmetric = bool(asymmetric)
+        if outlier_idx is not None:
+            if asymmetric:
+                raise ValueError("outlier side buffer is defined for symmetric INT4 only")
+            outlier_idx = torch.as_tensor(outlier_idx).to(torch.int16)
+            if outlier_idx.ndim != 3 or outlier_idx.shape[0] != num_layers:
+                raise ValueError("outlier_idx must be [num_layers, Hkv, n_out]")
+            outlier_idx, _ = torch.sort(outlier_idx, dim=-1)
+        self.outlier_idx = outlier_idx
+
+    def _payload_dim(self, head_dim: int) -> int:
+        if head_dim % 2 != 0:
+            raise ValueError(f"INT4 bit packing requires even head_dim, got {head_dim}")
+        return head_dim // 2
+
+    def _rescue_threshold(self, x: Tensor, G: int) -> Tensor:
+        """Global quantile of the per-group absmax/7 over the whole appended tensor
+        (src/cache/int4_cache.py:360-390).  The order statistic is taken with
+        torch.quantile on the device; no host sync."""
+        B, H, T, D = x.shape
+        dyn = x.reshape(B, H, T, G, D // G).abs().amax(dim=-1).float().clamp(min=1e-5) / 7.0
+        q = max(0.0, min(1.0, 1.0 - self.outlier_rescue_ratio))
+        return torch.quantile(dyn.reshape(-1), q).reshape(1).contiguous()
+
+    def append(self, layer_id: int, k: Tensor, v: Tensor) -> None:
+        """Quantize, pack and append (src/cache/int4_cache.py:392-589)."""
+        if self.static_k_scale is None and not self.asymmetric:
+            if self.outlier_rescue_ratio > 0:
+                warnings.warn(
+                    f"KVC-031: outlier_rescue_ratio={self.outlier_rescue_ratio} has no effect at layer "
+                    f"{layer_id} because no static scale is provided.", RuntimeWarning)
+            if self.mixed_rescue:
+                warnings.warn(
+                    f"KVC-031: mixed_rescue=True has no effect at layer {layer_id} because no static "
+                    "scale is provided.", RuntimeWarning)
+        flags = 0
+        if self.mixed_rescue:
+            flags |= F_MIXED_RESCUE
+        if self.outlier_rescue_ratio >= 1.0:
+            flags |= F_MIXED_RESCUE          # max(static, dynamic) everywhere (int4_cache.py:380-381)
+        elif self.outlier_rescue_ratio > 0.0:
+            flags |= F_RESCUE_THR
+        self._append_impl(layer_id, k, v, extra_flags=flags)
+
+    def get_int4_tensors(self, layer_id: int) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+        """(k_packed, v_packed, k_scale, v_scale) views; payload [B,Hkv,S,D/2], scales fp16."""
+        return self._layer_view(layer_id, ("k", "v", "ks", "vs"))
+
+    def get_kv(self, layer_id: int) -> Tuple[Tensor, Tensor]:
+        t = self.get_decode_tensors(layer_id)
+        k, v = quant.unpack_int4(t["k"]), quant.unpack_int4(t["v"])
+        if self.asymmetric:
+            kd = quant.dequantize_asymmetric_groupwise(k, t["ks"], t["kz"])
+            vd = quant.dequantize_asymmetric_groupwise(v, t["vs"], t["vz"])
+        else:
+            kd = quant.dequantize_symmetric_int4(k, t["ks"].float())
+            vd = quant.dequantize_symmetric_int4(v, t["vs"].float())
+        kd, vd = kd.to(self.dtype), vd.to(self.dtype)
+        if self.outlier_idx is not None:
+            idx = t["outlier_idx"].to(kd.device).long()
+            B, H, S, _ = kd.shape
+            gather = idx[None, :, None, :].expand(B, H, S, idx.shape[-1])
+            kd = kd.scatter(-1, gather, t["kside"].to(self.dtype))
+            vd = vd.scatter(-1, gather, t["vside"].to(self.dtype))
+        return kd, vd
+
+    @classmethod
+    def from_tuple(cls, past_key_values, device="cuda", clip_percentile: float = 99.9,
+                   group_size: int = 32) -> "INT4KVCache":
+        cache = cls(num_layers=len(past_key_values), device=device, clip_percentile=clip_percentile,
+                    group_size=group_size)
+        for i, item in enumerate(past_key_values):
+            cache.append(i, item[0].to(device), item[1].to(device))
+        return cache

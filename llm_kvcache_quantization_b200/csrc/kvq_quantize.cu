@@ -1,0 +1,260 @@
+// Quantize-on-append for the KV cache: one launch quantizes the new tokens of K
+// and V and writes payload, fp16 scales (zero-points, outlier side values)
+// straight into the cache slots.
+//
+// Arithmetic contracts (bit-exact with the reference's torch quantizers):
+//   INT8   s = RN16(max(s_in,1e-5));  c = clamp(rint(RN16(float(x)/float(s))), -127, 127)
+//          (src/quant/int8_basic.py:155-161 - the fp32 quotient is rounded to fp16 first)
+//   INT4   s = max(s_in,1e-5) fp32;   c = clamp(rint(float(x)/s), -7, 7); stored scale RN16(s)
+//          (src/quant/int4_basic.py:150-156; src/engine/patch_model.py:932-933)
+//   asym   rng = max(max-min, 9.1553e-4); s = rng/15; zp = min + 8 s;
+//          c = clamp(rint((x - zp)/s), -8, 7)      (src/quant/asymmetric_quant.py:98-141)
+//   percentile = torch.quantile's sorted lerp, evaluated as one fma.
+// This translation unit must be compiled WITHOUT fast-math: it relies on IEEE
+// fp32 division and fp16 subnormals.
+//
+// Work decomposition: one thread per (side, b, h, t, group).  Append traffic is
+// tiny next to the attention scan (decode: B*Hkv rows of 256 B), so the kernel is
+// launch-latency bound; what matters is that it is ONE launch with no host sync.
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kvq_internal.h"
+
+namespace kvq {
+
+constexpr int kMaxGroup = 256;
+
+struct QuantParams {
+    KvqAppendArgs a;
+    int G;
+    int nsides;   // 2, or 1 when the V side is absent (v.src == NULL)
+};
+
+__device__ __forceinline__ float h2f(__half h) { return __half2float(h); }
+
+// torch.quantile(|x|, q) over n sorted values: rank = q*(n-1) in fp32, fma lerp.
+__device__ float group_quantile(const float* v, int n, float q) {
+    float pos = __fmul_rn(q, (float)(n - 1));
+    int lo = (int)floorf(pos);
+    int hi = min(lo + 1, n - 1);
+    float w = __fsub_rn(pos, (float)lo);
+    float x0 = 0.f, x1 = 0.f;
+    for (int i = 0; i < n; ++i) {
+        float vi = v[i];
+        int rank = 0;
+        for (int j = 0; j < n; ++j) {
+            float vj = v[j];
+            rank += (vj < vi) || (vj == vi && j < i);
+        }
+        if (rank == lo) x0 = vi;
+        if (rank == hi) x1 = vi;
+    }
+    float diff = __fsub_rn(x1, x0);
+    return (w < 0.5f) ? __fmaf_rn(w, diff, x0) : __fmaf_rn(__fsub_rn(w, 1.0f), diff, x1);
+}
+
+template <int FMT, int POLICY>
+__global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams p) {
+    const KvqAppendArgs& a = p.a;
+    const int G = p.G;
+    const int gs = a.group_size;
+    const long long per_side = (long long)a.B * a.Hkv * a.T * G;
+    long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= p.nsides * per_side) return;
+    const int sidx = gid >= per_side;
+    if (sidx) gid -= per_side;
+    const KvqAppendSide& sd = sidx ? a.v : a.k;
+    const int g = (int)(gid % G);
+    long long r = gid / G;
+    const int t = (int)(r % a.T); r /= a.T;
+    const int h = (int)(r % a.Hkv);
+    const int b = (int)(r / a.Hkv);
+    long long pos = a.write_pos_dev ? (long long)(*a.write_pos_dev) : a.write_pos;
+    pos += t;
+
+    const __half* src = (const __half*)sd.src + b * sd.src_stride_b + h * sd.src_stride_h +
+                        t * sd.src_stride_t + g * gs;
+    char* pay = (char*)sd.payload + b * sd.pay_stride_b + h * sd.pay_stride_h + pos * sd.pay_stride_s;
+
+    if (FMT == KVQ_FMT_FP16) {
+        __half* dst = (__half*)pay + g * gs;
+        for (int i = 0; i < gs; ++i) dst[i] = src[i];
+        return;
+    }
+
+    // outlier channels of this head that fall in this group: copy raw, treat as 0
+    const int16_t* oidx = a.n_out ? a.outlier_idx + h * a.n_out : nullptr;
+    if (oidx && sd.side) {
+        __half* side = (__half*)sd.side + b * sd.side_stride_b + h * sd.side_stride_h + pos * sd.side_stride_s;
+        for (int j = 0; j < a.n_out; ++j) {
+            int ch = oidx[j] - g * gs;
+            if (ch >= 0 && ch < gs) side[j] = src[ch];
+        }
+    }
+    auto load = [&](int i) -> float {
+        if (oidx) {
+            for (int j = 0; j < a.n_out; ++j)
+                if (oidx[j] == g * gs + i) return 0.0f;
+        }
+        return h2f(src[i]);
+    };
+
+    const long long sc_off = b * sd.sc_stride_b + h * sd.sc_stride_h + pos * sd.sc_stride_s + g;
+    float s32 = 1.0f, zp32 = 0.0f;   // scale used for the division (fp32 value)
+
+    if (POLICY == KVQ_SCALE_STATIC) {
+        float st = sd.static_scale_is_f32 ? ((const float*)sd.static_scale)[h * G + g]
+                                          : h2f(((const __half*)sd.static_scale)[h * G + g]);
+        s32 = st;
+        if (a.flags & (KVQ_F_ADAPTIVE | KVQ_F_MIXED_RESCUE | KVQ_F_RESCUE_THR)) {
+            float amax = 0.f;   // |x| is exact in fp16, so the fp32 max equals the fp16 amax
+            for (int i = 0; i < gs; ++i) amax = fmaxf(amax, fabsf(load(i)));
+            const float qmax = (FMT == KVQ_FMT_INT8) ? 127.0f : 7.0f;
+            float dyn = __fdiv_rn(fmaxf(amax, 1e-5f), qmax);
+            s32 = fmaxf(s32, 1e-5f);
+            if (a.flags & KVQ_F_ADAPTIVE) s32 = fmaxf(__fmul_rn(s32, a.adaptive_margin), dyn);
+            if (a.flags & KVQ_F_MIXED_RESCUE) s32 = fmaxf(s32, dyn);
+            if (a.flags & KVQ_F_RESCUE_THR) {
+                float thr = *sd.rescue_threshold;
+                if (dyn >= thr) s32 = fmaxf(s32, dyn);
+            }
+        }
+        s32 = fmaxf(s32, 1e-5f);
+    } else if (POLICY == KVQ_SCALE_DYNAMIC_PCT) {
+        float amax;
+        if (a.quantile < 1.0f) {
+            float vals[kMaxGroup];
+            for (int i = 0; i < gs; ++i) vals[i] = fabsf(load(i));
+            amax = fmaxf(group_quantile(vals, gs, a.quantile), 1e-5f);
+            if (FMT == KVQ_FMT_INT8) amax = h2f(__float2half_rn(amax));
+        } else {
+            amax = 0.f;
+            for (int i = 0; i < gs; ++i) amax = fmaxf(amax, fabsf(load(i)));
+            // the reference clamps the fp16 amax in fp16
+            amax = h2f(__float2half_rn(fmaxf(amax, 1e-5f)));
+        }
+        if (FMT == KVQ_FMT_INT8) {
+            s32 = h2f(__float2half_rn(__fdiv_rn(amax, 127.0f)));   // "/127" runs in fp16
+        } else {
+            s32 = __fdiv_rn(fmaxf(amax, 1e-5f), 7.0f);
+        }
+    } else {  // KVQ_SCALE_ASYM_MINMAX
+        float mn = INFINITY, mx = -INFINITY;
+        for (int i = 0; i < gs; ++i) {
+            float x = load(i);
+            mn = fminf(mn, x);
+            mx = fmaxf(mx, x);
+        }
+        const float qspan = (FMT == KVQ_FMT_INT8) ? 255.0f : 15.0f;
+        const float qmin = (FMT == KVQ_FMT_INT8) ? -128.0f : -8.0f;
+        const float floor_rng = fmaxf(1e-5f, __fmul_rn(6.103515625e-05f, qspan));
+        float rng = fmaxf(__fsub_rn(mx, mn), floor_rng);
+        s32 = __fdiv_rn(rng, qspan);
+        zp32 = __fsub_rn(mn, __fmul_rn(qmin, s32));
+    }
+
+    // stored (kernel-facing) scale is fp16
+    __half s16 = __float2half_rn(s32);
+    if (FMT == KVQ_FMT_INT8 && POLICY != KVQ_SCALE_ASYM_MINMAX) s32 = h2f(s16);  // INT8 divides by the fp16 scale
+    ((__half*)sd.scale)[sc_off] = s16;
+    if (sd.scale_f32) sd.scale_f32[sc_off] = s32;
+    if (POLICY == KVQ_SCALE_ASYM_MINMAX) ((__half*)sd.zp)[sc_off] = __float2half_rn(zp32);
+
+    auto code_of = [&](int i) -> int {
+        float x = load(i);
+        float qv;
+        if (POLICY == KVQ_SCALE_ASYM_MINMAX) {
+            qv = rintf(__fdiv_rn(__fsub_rn(x, zp32), s32));
+            return (FMT == KVQ_FMT_INT8) ? (int)fminf(fmaxf(qv, -128.f), 127.f)
+                                         : (int)fminf(fmaxf(qv, -8.f), 7.f);
+        }
+        if (FMT == KVQ_FMT_INT8) {
+            qv = rintf(h2f(__float2half_rn(__fdiv_rn(x, s32))));
+            return (int)fminf(fmaxf(qv, -127.f), 127.f);
+        }
+        qv = rintf(__fdiv_rn(x, s32));
+        return (int)fminf(fmaxf(qv, -7.f), 7.f);
+    };
+
+    if (FMT == KVQ_FMT_INT8) {
+        int8_t* dst = (int8_t*)pay + g * gs;
+        for (int i = 0; i < gs; i += 4) {
+            int c0 = code_of(i), c1 = code_of(i + 1), c2 = code_of(i + 2), c3 = code_of(i + 3);
+            uint32_t w = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) |
+                         ((uint32_t)(c2 & 0xff) << 16) | ((uint32_t)(c3 & 0xff) << 24);
+            *(uint32_t*)(dst + i) = w;
+        }
+    } else {
+        uint8_t* dst = (uint8_t*)pay + (g * gs) / 2;
+        for (int i = 0; i < gs; i += 8) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int c0 = code_of(i + 2 * j) + 8, c1 = code_of(i + 2 * j + 1) + 8;
+                w |= (uint32_t)(((c0 & 0xf) << 4) | (c1 & 0xf)) << (8 * j);
+            }
+            *(uint32_t*)(dst + i / 2) = w;
+        }
+    }
+}
+
+template <int FMT, int POLICY>
+static int launch(const QuantParams& p, cudaStream_t st) {
+    const long long threads = (long long)p.nsides * p.a.B * p.a.Hkv * p.a.T * p.G;
+    if (threads == 0) return KVQ_OK;
+    const int block = 128;
+    const long long grid = (threads + block - 1) / block;
+    if (grid > 0x7fffffffLL) return KVQ_EINVAL;
+    quantize_append_kernel<FMT, POLICY><<<(unsigned)grid, block, 0, st>>>(p);
+    return check_launch();
+}
+
+static bool side_ok(const KvqAppendSide& s, const KvqAppendArgs& a) {
+    if (!s.src || !s.payload) return false;
+    if (a.format != KVQ_FMT_FP16 && !s.scale) return false;
+    if (a.policy == KVQ_SCALE_STATIC && a.format != KVQ_FMT_FP16 && !s.static_scale) return false;
+    if (a.policy == KVQ_SCALE_ASYM_MINMAX && !s.zp) return false;
+    if ((a.flags & KVQ_F_RESCUE_THR) && !s.rescue_threshold) return false;
+    if (a.n_out > 0 && !s.side) return false;
+    // 4-byte stores into the payload
+    if (((uintptr_t)s.payload | (uintptr_t)s.pay_stride_b | (uintptr_t)s.pay_stride_h |
+         (uintptr_t)s.pay_stride_s) & 3) return false;
+    return true;
+}
+
+}  // namespace kvq
+
+extern "C" int kvq_quantize_append(const KvqAppendArgs* args, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!args) return KVQ_EINVAL;
+    const KvqAppendArgs& a = *args;
+    if (a.B < 0 || a.Hkv <= 0 || a.T < 0 || a.D <= 0) return KVQ_EINVAL;
+    if (a.B == 0 || a.T == 0) return KVQ_OK;
+    int gs = a.group_size == -1 ? a.D : a.group_size;
+    if (gs <= 0 || a.D % gs != 0 || gs % 8 != 0 || gs > kMaxGroup) return KVQ_EINVAL;
+    if (a.format != KVQ_FMT_FP16 && a.format != KVQ_FMT_INT8 && a.format != KVQ_FMT_INT4) return KVQ_EINVAL;
+    if (a.policy < 0 || a.policy > 2) return KVQ_EINVAL;
+    if (a.n_out < 0 || (a.n_out > 0 && !a.outlier_idx)) return KVQ_EINVAL;
+    if (a.n_out > 0 && a.policy == KVQ_SCALE_ASYM_MINMAX) return KVQ_EUNSUPPORTED;
+    if (a.write_pos < 0) return KVQ_EINVAL;
+    QuantParams p;
+    p.a = a;
+    p.a.group_size = gs;
+    p.G = a.D / gs;
+    p.nsides = a.v.src ? 2 : 1;
+    if (!side_ok(a.k, p.a) || (p.nsides == 2 && !side_ok(a.v, p.a))) return KVQ_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+#define KVQ_DISPATCH(F, P) if (a.format == F && a.policy == P) return launch<F, P>(p, st);
+    if (a.format == KVQ_FMT_FP16) return launch<KVQ_FMT_FP16, KVQ_SCALE_STATIC>(p, st);
+    KVQ_DISPATCH(KVQ_FMT_INT8, KVQ_SCALE_STATIC)
+    KVQ_DISPATCH(KVQ_FMT_INT8, KVQ_SCALE_DYNAMIC_PCT)
+    KVQ_DISPATCH(KVQ_FMT_INT8, KVQ_SCALE_ASYM_MINMAX)
+    KVQ_DISPATCH(KVQ_FMT_INT4, KVQ_SCALE_STATIC)
+    KVQ_DISPATCH(KVQ_FMT_INT4, KVQ_SCALE_DYNAMIC_PCT)
+    KVQ_DISPATCH(KVQ_FMT_INT4, KVQ_SCALE_ASYM_MINMAX)
+#undef KVQ_DISPATCH
+    return KVQ_EUNSUPPORTED;
+}

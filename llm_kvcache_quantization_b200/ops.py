@@ -1,0 +1,253 @@
+"""Thin tensor-level wrappers over the C ABI (pointers, strides, stream, workspace).
+
+torch is used for device memory, streams and dtype bookkeeping only; all
+arithmetic happens in libkvq.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (FMT_FP16, FMT_INT4, FMT_INT8, F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR,
+                   SCALE_ASYM_MINMAX, SCALE_DYNAMIC_PCT, SCALE_STATIC)
+
+_WORKSPACES = {}
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("libkvq requires CUDA tensors (there is no CPU path).")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"device mismatch: {t.device} vs {dev}")
+    return dev
+
+
+def get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) scratch buffer for split-K partials; grows, never shrinks."""
+    key = (device.index, _stream_ptr(device))
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    _WORKSPACES.clear()
+
+
+def pick_splits(batch: int, kv_heads: int, max_ctx: int) -> int:
+    return int(_lib.load().kvq_decode_pick_splits(batch, kv_heads, max_ctx))
+
+
+# --------------------------------------------------------------------------- append
+def _append_side(src, payload, scale, zp, scale_f32, side, static_scale, rescue_thr) -> _lib.KvqAppendSide:
+    s = _lib.KvqAppendSide()
+    if src.stride(-1) != 1:
+        raise ValueError("new K/V tokens must be contiguous in head_dim")
+    s.src = src.data_ptr()
+    s.src_stride_b, s.src_stride_h, s.src_stride_t = src.stride(0), src.stride(1), src.stride(2)
+    es = payload.element_size()
+    if payload.stride(-1) != 1:
+        raise ValueError("cache payload must be contiguous in its last dimension")
+    s.payload = payload.data_ptr()
+    s.pay_stride_b, s.pay_stride_h, s.pay_stride_s = (payload.stride(0) * es, payload.stride(1) * es,
+                                                      payload.stride(2) * es)
+    if scale is not None:
+        if scale.dtype != torch.float16 or scale.stride(-1) != 1:
+            raise ValueError("cache scale buffer must be fp16, contiguous in groups")
+        s.scale = scale.data_ptr()
+        s.sc_stride_b, s.sc_stride_h, s.sc_stride_s = scale.stride(0), scale.stride(1), scale.stride(2)
+    if zp is not None:
+        if zp.dtype != torch.float16 or zp.stride() != scale.stride():
+            raise ValueError("zero-point buffer must be fp16 with the strides of the scale buffer")
+        s.zp = zp.data_ptr()
+    if scale_f32 is not None:
+        if scale_f32.dtype != torch.float32 or scale_f32.stride() != scale.stride():
+            raise ValueError("fp32 scale copy must share the strides of the fp16 scale buffer")
+        s.scale_f32 = scale_f32.data_ptr()
+    if side is not None:
+        if side.dtype != torch.float16 or side.stride(-1) != 1:
+            raise ValueError("outlier side buffer must be fp16, contiguous in its last dimension")
+        s.side = side.data_ptr()
+        s.side_stride_b, s.side_stride_h, s.side_stride_s = side.stride(0), side.stride(1), side.stride(2)
+    if static_scale is not None:
+        if static_scale.dtype not in (torch.float16, torch.float32) or not static_scale.is_contiguous():
+            raise ValueError("static scale table must be a contiguous fp16/fp32 [Hkv, G] tensor")
+        s.static_scale = static_scale.data_ptr()
+        s.static_scale_is_f32 = 1 if static_scale.dtype == torch.float32 else 0
+    if rescue_thr is not None:
+        s.rescue_threshold = rescue_thr.data_ptr()
+    return s
+
+
+def quantize_append(fmt: int, policy: int, k_new: torch.Tensor, v_new: torch.Tensor,
+                    k_payload: torch.Tensor, v_payload: torch.Tensor,
+                    k_scale: Optional[torch.Tensor], v_scale: Optional[torch.Tensor],
+                    write_pos, group_size: int, *,
+                    k_zp=None, v_zp=None, k_scale_f32=None, v_scale_f32=None,
+                    k_static=None, v_static=None, flags: int = 0, adaptive_margin: float = 1.0,
+                    quantile: float = 1.0, k_rescue_thr=None, v_rescue_thr=None,
+                    outlier_idx=None, k_side=None, v_side=None) -> None:
+    """Quantize `k_new`, `v_new` ([B,Hkv,T,D] fp16) into cache slots
+    [write_pos, write_pos+T) of the given payload / scale buffers in one launch (`v_new=None`: K side only).
+    `write_pos` is an int or an int32 device tensor (read on the device)."""
+    dev = _require_cuda(k_new, v_new, k_payload, v_payload, k_scale, v_scale)
+    if k_new.dtype != torch.float16 or (v_new is not None and v_new.dtype != torch.float16):
+        raise ValueError("quantize_append expects fp16 K/V")
+    if k_new.ndim != 4 or (v_new is not None and k_new.shape != v_new.shape):
+        raise ValueError(f"k/v shape mismatch or not 4D: {tuple(k_new.shape)}")
+    B, H, T, D = k_new.shape
+    a = _lib.KvqAppendArgs()
+    a.format, a.policy, a.flags = fmt, policy, flags
+    a.B, a.Hkv, a.T, a.D = B, H, T, D
+    a.group_size = group_size
+    a.adaptive_margin = float(adaptive_margin)
+    a.quantile = float(quantile)
+    if outlier_idx is not None:
+        if outlier_idx.dtype != torch.int16 or not outlier_idx.is_contiguous() or outlier_idx.shape[0] != H:
+            raise ValueError("outlier_idx must be a contiguous int16 [Hkv, n_out] tensor")
+        a.n_out = outlier_idx.shape[1]
+        a.outlier_idx = outlier_idx.data_ptr()
+    if isinstance(write_pos, torch.Tensor):
+        if write_pos.dtype != torch.int32 or not write_pos.is_cuda:
+            raise ValueError("device write_pos must be an int32 CUDA tensor")
+        a.write_pos_dev = write_pos.data_ptr()
+    else:
+        a.write_pos = int(write_pos)
+        cap = k_payload.shape[2]
+        if a.write_pos < 0 or a.write_pos + T > cap:
+            raise ValueError(f"append of {T} tokens at {a.write_pos} exceeds capacity {cap}")
+    a.k = _append_side(k_new, k_payload, k_scale, k_zp, k_scale_f32, k_side, k_static, k_rescue_thr)
+    if v_new is not None:
+        a.v = _append_side(v_new, v_payload, v_scale, v_zp, v_scale_f32, v_side, v_static, v_rescue_thr)
+    with torch.cuda.device(dev):
+        rc = _lib.load().kvq_quantize_append(C.byref(a), _stream_ptr(dev))
+    _lib.check("kvq_quantize_append", rc)
+
+
+# --------------------------------------------------------------------------- attention
+def _cache_side(payload, scale, zp, side) -> _lib.KvqCacheSide:
+    s = _lib.KvqCacheSide()
+    es = payload.element_size()
+    s.payload = payload.data_ptr()
+    s.pay_stride_b, s.pay_stride_h, s.pay_stride_s = (payload.stride(0) * es, payload.stride(1) * es,
+                                                      payload.stride(2) * es)
+    if scale is not None:
+        s.scale = scale.data_ptr()
+        s.sc_stride_b, s.sc_stride_h, s.sc_stride_s = scale.stride(0), scale.stride(1), scale.stride(2)
+    if zp is not None:
+        if zp.stride() != scale.stride():
+            raise ValueError("zero-points must share the strides of the scales")
+        s.zp = zp.data_ptr()
+    if side is not None:
+        s.side = side.data_ptr()
+        s.side_stride_b, s.side_stride_h, s.side_stride_s = side.stride(0), side.stride(1), side.stride(2)
+    return s
+
+
+def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: torch.Tensor,
+                k_scale: Optional[torch.Tensor], v_scale: Optional[torch.Tensor],
+                context_lens: torch.Tensor, sm_scale: float, *, head_dim: int,
+                k_zp=None, v_zp=None, inv_tau: Optional[torch.Tensor] = None,
+                outlier_idx=None, k_side=None, v_side=None,
+                splits: int = 0, out: Optional[torch.Tensor] = None,
+                return_partial: bool = False, max_ctx: Optional[int] = None):
+    """Fused q_len==1 attention over a (quantized) cache.  q fp16 [B,Hq,D].
+
+    Returns `out` fp16 [B,Hq,D]; with `return_partial` also the normalised
+    partial `(o fp32 [B,Hq,D], m fp32 [B,Hq], l fp32 [B,Hq])` used by the
+    sequence-sharded merge.  No host synchronisation happens here.
+    """
+    dev = _require_cuda(q, k_payload, v_payload, k_scale, v_scale, context_lens)
+    if q.dtype != torch.float16:
+        raise ValueError("decode_attn expects an fp16 query")
+    B, Hq, D = q.shape
+    if D != head_dim:
+        raise ValueError(f"Head dim mismatch: q={D}, expected {head_dim}")
+    Hkv = k_payload.shape[1]
+    S = k_payload.shape[2]
+    a = _lib.KvqAttnArgs()
+    a.format = fmt
+    a.B, a.Hq, a.Hkv, a.D = B, Hq, Hkv, D
+    G = 1 if k_scale is None else k_scale.shape[-1]
+    a.group_size = D // G
+    a.max_ctx = S if max_ctx is None else min(int(max_ctx), S)
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    a.q = q.data_ptr()
+    a.q_stride_b, a.q_stride_h = q.stride(0), q.stride(1)
+    if inv_tau is not None:
+        if inv_tau.dtype != torch.float32 or not inv_tau.is_contiguous() or inv_tau.numel() != Hq:
+            raise ValueError("inv_tau must be a contiguous fp32 [Hq] tensor")
+        a.inv_tau = inv_tau.data_ptr()
+    a.sm_scale = float(sm_scale)
+    a.k = _cache_side(k_payload, k_scale, k_zp, k_side)
+    a.v = _cache_side(v_payload, v_scale, v_zp, v_side)
+    if outlier_idx is not None:
+        a.n_out = outlier_idx.shape[1]
+        a.outlier_idx = outlier_idx.data_ptr()
+    if context_lens.dtype != torch.int32 or not context_lens.is_contiguous():
+        context_lens = context_lens.to(torch.int32).contiguous()
+    a.context_lens = context_lens.data_ptr()
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        a.splits = int(splits) if splits else int(lib.kvq_decode_pick_splits(B, Hkv, a.max_ctx))
+        need = int(lib.kvq_decode_workspace_bytes(B, Hq, D, a.splits))
+        ws = get_workspace(dev, need)
+        a.workspace = ws.data_ptr()
+        a.workspace_bytes = ws.numel()
+        if out is None:
+            out = torch.empty((B, Hq, D), dtype=torch.float16, device=dev)
+        a.out = out.data_ptr()
+        a.out_stride_b, a.out_stride_h = out.stride(0), out.stride(1)
+        part = None
+        if return_partial:
+            po = torch.empty((B, Hq, D), dtype=torch.float32, device=dev)
+            pm = torch.empty((B, Hq), dtype=torch.float32, device=dev)
+            pl = torch.empty((B, Hq), dtype=torch.float32, device=dev)
+            a.part_o, a.part_m, a.part_l = po.data_ptr(), pm.data_ptr(), pl.data_ptr()
+            part = (po, pm, pl)
+        rc = lib.kvq_decode_attn(C.byref(a), _stream_ptr(dev)) if B > 0 else 0
+    _lib.check("kvq_decode_attn", rc)
+    if return_partial:
+        return out, part
+    return out
+
+
+def lse_combine(part_o: torch.Tensor, part_m: torch.Tensor, part_l: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Merge P normalised partials ([P,B,Hq,D], [P,B,Hq], [P,B,Hq] fp32) -> fp16 [B,Hq,D]."""
+    dev = _require_cuda(part_o, part_m, part_l)
+    P, B, Hq, D = part_o.shape
+    for t in (part_o, part_m, part_l):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError("partials must be contiguous fp32 tensors")
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=torch.float16, device=dev)
+    c = _lib.KvqCombineArgs()
+    c.P, c.B, c.Hq, c.D = P, B, Hq, D
+    c.part_o, c.part_m, c.part_l = part_o.data_ptr(), part_m.data_ptr(), part_l.data_ptr()
+    c.out = out.data_ptr()
+    c.out_stride_b, c.out_stride_h = out.stride(0), out.stride(1)
+    with torch.cuda.device(dev):
+        rc = _lib.load().kvq_lse_combine(C.byref(c), _stream_ptr(dev))
+    _lib.check("kvq_lse_combine", rc)
+    return out
