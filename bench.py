@@ -1,0 +1,481 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-KV decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
+
+One "step" = one decode step over the whole KV stack of the workload: for every
+layer, quantize-on-append of the new token (one launch for K and V) followed by
+the fused decode attention (split-K kernel + combine) over the cached context.
+Default workload is configuration 2 of BASELINE.json (Qwen2.5-1.5B geometry, 28
+layers, batch 16, context 8192, INT4 asymmetric group-32 with fp16 scale and
+zero-point).  With N > 1 the batch is sharded by sequence: every rank owns its own
+batch of sequences and its own cache, no collective on the data path (weak scaling).
+
+Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: layers, B, Hq, Hkv, S, kind, n_out
+    "c1": dict(layers=1, B=1, Hq=12, Hkv=2, S=4096, kind="int8_static", n_out=0,
+               desc="C1: 1 layer, Qwen2.5-1.5B geometry, batch 1, ctx 4096, INT8 static group-32"),
+    "c2": dict(layers=28, B=16, Hq=12, Hkv=2, S=8192, kind="int4_asym", n_out=0,
+               desc="C2: 28-layer KV stack, Qwen2.5-1.5B geometry (12q/2kv heads, d128), batch 16, ctx 8192, "
+                    "INT4 asymmetric group-32 (fp16 scale+zero-point), decode step incl. quantize-on-append"),
+    "c3": dict(layers=4, B=32, Hq=12, Hkv=2, S=16384, kind="int4_outlier", n_out=3,
+               desc="C3: Qwen2.5-1.5B geometry, batch 32, ctx 16384, INT4 group-32 + 3 fp16 outlier channels (4 layers)"),
+    "c4": dict(layers=2, B=64, Hq=28, Hkv=4, S=32768, kind="int8_dyn", n_out=0,
+               desc="C4: Qwen2.5-7B geometry, batch 64, ctx 32768, INT8 group-32 (2 layers)"),
+    "c5": dict(layers=4, B=1, Hq=40, Hkv=8, S=131072, kind="int4_outlier", n_out=1,
+               desc="C5: Qwen2.5-14B geometry, batch 1, ctx 131072, INT4 group-32 + 1 fp16 outlier channel (4 layers)"),
+}
+D = 128
+GS = 32
+G = D // GS
+
+
+def bytes_per_token_head(kind: str, n_out: int) -> int:
+    """Algorithmic HBM bytes per cached token per KV head (K and V): payload + per-token
+    fp16 scales (+ zero-points) (+ fp16 outlier side values), each counted once."""
+    if kind in ("int8_static", "int8_dyn"):
+        return 2 * (D + 2 * G)
+    if kind == "int4_asym":
+        return 2 * (D // 2 + 2 * G + 2 * G)
+    if kind == "int4_outlier":
+        return 2 * (D // 2 + 2 * G + 2 * n_out)
+    raise ValueError(kind)
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- workload
+def build_workload(wl: dict, dev, seed: int, extra_slots: int):
+    """Synthetic KV of the configuration's shape and value distribution, generated on the
+    GPU layer by layer and quantized with the library's own quantizer into a preallocated cache."""
+    import numpy as np
+    import torch
+    import llm_kvcache_quantization_b200 as kvq
+
+    L, B, Hq, Hkv, S, kind, n_out = (wl[k] for k in ("layers", "B", "Hq", "Hkv", "S", "kind", "n_out"))
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    cap = S + extra_slots
+    kw = dict(device=dev, group_size=GS, max_seq_len=cap)
+    outlier_idx = None
+    if kind == "int8_static":
+        tab = torch.full((L, Hkv, G), 4.5 / 127, dtype=torch.float16, device=dev)
+        cache = kvq.INT8KVCache(L, static_k_scale=tab, static_v_scale=tab, **kw)
+    elif kind == "int8_dyn":
+        cache = kvq.INT8KVCache(L, clip_percentile=100.0, **kw)
+    elif kind == "int4_asym":
+        cache = kvq.INT4KVCache(L, asymmetric=True, **kw)
+    else:
+        cpu_gen = torch.Generator().manual_seed(seed)
+        outlier_idx = torch.stack([torch.stack([torch.randperm(D, generator=cpu_gen)[:n_out].sort().values
+                                                for _ in range(Hkv)]) for _ in range(L)]).to(torch.int16)
+        tab = torch.full((L, Hkv, G), 4.5 / 7, dtype=torch.float32, device=dev)
+        cache = kvq.INT4KVCache(L, static_k_scale=tab, static_v_scale=tab, outlier_idx=outlier_idx.to(dev), **kw)
+    chunk = max(1, min(S, (1 << 26) // (B * Hkv * D)))       # <= 128 MB fp16 per generated chunk
+    for l in range(L):
+        cache.reserve(l, B, Hkv, D, cap)
+        if kind == "int4_asym":
+            std = torch.exp(torch.empty(1, Hkv, 1, D, device=dev).uniform_(np.log(0.3), np.log(3.0), generator=gen))
+        else:
+            std = torch.ones(1, Hkv, 1, D, device=dev)
+            if outlier_idx is not None:
+                for h in range(Hkv):
+                    std[0, h, 0, outlier_idx[l, h].long().to(dev)] = 30.0
+        for s0 in range(0, S, chunk):
+            n = min(chunk, S - s0)
+            k = (torch.randn(B, Hkv, n, D, device=dev, generator=gen) * std).half()
+            v = (torch.randn(B, Hkv, n, D, device=dev, generator=gen) * std).half()
+            cache.append(l, k, v)
+            del k, v
+    q = torch.randn(L, B, Hq, D, device=dev, generator=gen).half()
+    k_new = torch.randn(L, B, Hkv, 1, D, device=dev, generator=gen).half()
+    v_new = torch.randn(L, B, Hkv, 1, D, device=dev, generator=gen).half()
+    inv_tau = torch.empty(L, Hq, device=dev).uniform_(0.8, 1.2, generator=gen)
+    return cache, q, k_new, v_new, inv_tau
+
+
+def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=True):
+    """Returns a callable running one decode step with device-resident inputs.  The new
+    token is written at slot S every step (steady state at the nominal context)."""
+    import torch
+    from llm_kvcache_quantization_b200 import ops, _lib
+
+    L, B, Hkv, S, kind = wl["layers"], wl["B"], wl["Hkv"], wl["S"], wl["kind"]
+    dev = q.device
+    ctx = torch.full((B,), S + 1, dtype=torch.int32, device=dev)
+    fmt = _lib.FMT_INT8 if kind.startswith("int8") else _lib.FMT_INT4
+    splits = ops.pick_splits(B, Hkv, S + 1)
+    layers = []
+    for l in range(L):
+        b = cache._bufs[l]
+        view = {n: t[:, :, :S + 1] for n, t in b.items()}
+        app = dict(k_zp=b.get("kz"), v_zp=b.get("vz"))
+        if kind == "int4_asym":
+            policy = _lib.SCALE_ASYM_MINMAX
+        elif kind == "int8_dyn":
+            policy = _lib.SCALE_DYNAMIC_PCT
+            app.update(quantile=1.0)
+        else:
+            policy = _lib.SCALE_STATIC
+            app.update(k_static=cache._static_table("k", l, Hkv, G, dev), v_static=cache._static_table("v", l, Hkv, G, dev))
+        att = dict(k_zp=view.get("kz"), v_zp=view.get("vz"))
+        if kind == "int4_outlier":
+            oidx = cache.outlier_idx[l].contiguous()
+            app.update(outlier_idx=oidx, k_side=b["kside"], v_side=b["vside"])
+            att.update(outlier_idx=oidx, k_side=view["kside"], v_side=view["vside"])
+        layers.append((b, view, policy, app, att))
+
+    def step():
+        for l, (b, view, policy, app, att) in enumerate(layers):
+            if with_append:
+                ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], S, GS, **app)
+            ops.decode_attn(fmt, q[l], view["k"], view["v"], view["ks"], view["vs"], ctx, 1.0 / D ** 0.5,
+                            head_dim=D, inv_tau=inv_tau[l], splits=splits, out=out[l], max_ctx=S + 1,
+                            stages=stages, **att)
+    return step, splits
+
+
+def capture(step):
+    import torch
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        step()                      # warm (workspace allocation happens outside capture)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    return g
+
+
+def time_graph(g, iters, dist=None):
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    return e0.elapsed_time(e1)
+
+
+# --------------------------------------------------------------------------- CPU baseline / reference arm
+def cpu_sample(wl, seed=1234, target_s=12.0, max_rows=4):
+    """Times the CPU oracle (C restatement, OpenMP, all host threads) on a bounded sample of
+    the workload: ONE layer, `rows` batch rows at the full context, quantize-on-append of the
+    new token plus decode attention.  Returns (seconds per sample pass, rows, threads)."""
+    import numpy as np
+    from oracle import c_oracle as CO
+    from oracle import kvq_oracle as O
+
+    Hq, Hkv, S, kind, n_out = wl["Hq"], wl["Hkv"], wl["S"], wl["kind"], wl["n_out"]
+    rows = min(max_rows, wl["B"])
+    rng = np.random.default_rng(seed)
+    k = rng.standard_normal((rows, Hkv, S + 1, D), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((rows, Hkv, S + 1, D), dtype=np.float32).astype(np.float16)
+    q = rng.standard_normal((rows, Hq, D), dtype=np.float32).astype(np.float16)
+    tau = rng.uniform(0.8, 1.2, Hq).astype(np.float32)
+    ctx = np.full(rows, S + 1, np.int32)
+    sm = 1.0 / np.sqrt(D)
+    extra = {}
+    if kind == "int4_asym":
+        pk, sk, zk = CO.quant_int4_asym(k, GS)
+        pv, sv, zv = CO.quant_int4_asym(v, GS)
+        fmt, extra = 2, dict(kz=zk, vz=zv)
+        append = lambda: (CO.quant_int4_asym(k[:, :, -1:], GS), CO.quant_int4_asym(v[:, :, -1:], GS))
+    elif kind.startswith("int8"):
+        tab = np.full((Hkv, G), 4.5 / 127, np.float16)
+        pk, sk = CO.quant_int8_static(k, tab, GS)
+        pv, sv = CO.quant_int8_static(v, tab, GS)
+        fmt = 1
+        append = lambda: (CO.quant_int8_static(k[:, :, -1:], tab, GS), CO.quant_int8_static(v[:, :, -1:], tab, GS))
+    else:
+        idx = np.stack([np.sort(rng.permutation(D)[:n_out]) for _ in range(Hkv)]).astype(np.int16)
+        tab = np.full((Hkv, G), 4.5 / 7, np.float32)
+        bk, sidek = O.split_outliers(k, idx)
+        bv, sidev = O.split_outliers(v, idx)
+        pk, sk = CO.quant_int4_static(bk, tab, GS)
+        pv, sv = CO.quant_int4_static(bv, tab, GS)
+        fmt, extra = 2, dict(kside=sidek, vside=sidev, outlier_idx=idx)
+        append = lambda: (CO.quant_int4_static(bk[:, :, -1:], tab, GS), CO.quant_int4_static(bv[:, :, -1:], tab, GS))
+
+    def one_pass():
+        append()
+        return CO.decode_attn(fmt, q, pk, pv, sk, sv, ctx, sm, inv_tau=tau, **extra)
+
+    one_pass()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        one_pass()
+        n += 1
+        el = time.perf_counter() - t0
+        if el >= target_s or n >= 50:
+            break
+    return el / n, rows, CO.num_threads()
+
+
+def run_reference_arm(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_pass, rows, threads = cpu_sample(wl, target_s=2.0)          # warm-up + calibration
+    times = []
+    for _ in range(max(args.warmup, 0)):
+        cpu_sample(wl, target_s=0.0)
+    for _ in range(args.steps):
+        t, rows, threads = cpu_sample(wl, target_s=0.0)
+        times.append(t)
+    per_pass = statistics.mean(times) if times else per_pass
+    # extrapolate the sample (1 layer x rows sequences) linearly to the full step
+    step_s = per_pass * wl["layers"] * (wl["B"] / rows)
+    value = wl["B"] * args.gpus / step_s if False else wl["B"] / step_s
+    sample = (f"1 of {wl['layers']} layers x {rows} of {wl['B']} sequences at full context, "
+              f"quantize-append + decode attention; extrapolated linearly to the full step")
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": workload_config(wl, args.workload),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(wl, name):
+    return {"workload": wl["desc"], "name": name, "layers": wl["layers"], "batch_per_gpu": wl["B"],
+            "context": wl["S"], "group_size": GS, "l2": "inputs larger than L2 (KV stack cycles through all layers)"
+            if wl["layers"] * wl["B"] * wl["Hkv"] * wl["S"] * bytes_per_token_head(wl["kind"], wl["n_out"]) > 126e6
+            else "L2 flushed between timed iterations by a 256 MB write"}
+
+
+# --------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args, wl)
+        return
+
+    import torch
+    import llm_kvcache_quantization_b200 as kvq
+    from llm_kvcache_quantization_b200 import ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist_mod.init_process_group("nccl", device_id=dev)
+        dist = dist_mod
+
+    L, B, Hq, Hkv, S = wl["layers"], wl["B"], wl["Hq"], wl["Hkv"], wl["S"]
+    e2e_slots = args.steps + args.warmup + 8
+    cache, q, k_new, v_new, inv_tau = build_workload(wl, dev, seed=1234 + rank, extra_slots=e2e_slots)
+    out = torch.empty(L, B, Hq, D, dtype=torch.float16, device=dev)
+    small = L * B * Hkv * S * bytes_per_token_head(wl["kind"], wl["n_out"]) <= 126e6
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
+
+    step, splits = make_step(wl, cache, q, k_new, v_new, inv_tau, out)
+    g_step = capture(step)
+    split_only, _ = make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=1, with_append=False)
+    g_split = capture(split_only)
+
+    def timed(graph, iters):
+        if flush is None:
+            return time_graph(graph, iters, dist)
+        tot = 0.0
+        for _ in range(iters):
+            flush.fill_(1)
+            tot += time_graph(graph, 1, dist)
+        return tot
+
+    timed(g_step, args.warmup)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed(g_step, args.steps)
+    # dominant kernel alone (split-K scan), same clocks window
+    timed(g_split, 3)
+    ms_split = timed(g_split, args.steps)
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([ms, ms_split], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_split = float(t[0]), float(t[1])
+    ms_per_step = ms / args.steps
+    value = world * B / (ms_per_step * 1e-3)
+
+    # roofline of the dominant kernel
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    alg_bytes = B * Hkv * (S + 1) * bytes_per_token_head(wl["kind"], wl["n_out"])
+    split_us = ms_split / (args.steps * L) * 1e3
+    achieved = alg_bytes / (split_us * 1e-6) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": peak_src, "kernel": "decode split-K scan",
+                "us_per_launch": split_us, "algorithmic_bytes_per_launch": alg_bytes,
+                "frac_of_8TBps": achieved / 8000.0}
+
+    # end to end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        os.environ["KVQ_SKIP_CONTEXT_CHECK"] = "1"
+        hq = q.cpu().pin_memory(); hk = k_new.cpu().pin_memory(); hv = v_new.cpu().pin_memory()
+        hout = torch.empty(L, B, Hq, D, dtype=torch.float16).pin_memory()
+        kind = wl["kind"]
+
+        def e2e_step():
+            for l in range(L):
+                dq = hq[l].to(dev, non_blocking=True)
+                dk = hk[l].to(dev, non_blocking=True)
+                dv = hv[l].to(dev, non_blocking=True)
+                cache.append(l, dk, dv)
+                t = cache.get_decode_tensors(l)
+                n = t["k"].shape[2]
+                ctx = torch.full((B,), n, dtype=torch.int32, device=dev)
+                tau = inv_tau[l]
+                if kind == "int4_asym":
+                    o = kvq.decode_attn_int4_asym(dq, t["k"], t["v"], t["ks"], t["kz"], t["vs"], t["vz"], ctx, inv_tau=tau)
+                elif kind == "int4_outlier":
+                    o = kvq.decode_attn_int4_outlier(dq, t["k"], t["v"], t["ks"], t["vs"], t["kside"], t["vside"],
+                                                     t["outlier_idx"].contiguous(), ctx, inv_tau=tau)
+                else:
+                    o = kvq.decode_attn_int8(dq, t["k"], t["v"], t["ks"], t["vs"], ctx, inv_tau=tau)
+                hout[l].copy_(o, non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        ems = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ems], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ems = float(t[0])
+        h2d = L * (B * Hq * D + 2 * B * Hkv * D) * 2
+        d2h = L * B * Hq * D * 2
+        e2e = {"value": world * B / (ems / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ems / args.steps,
+               "api": "cache.append + decode_attn_* per layer, eager (no CUDA graph), pinned host q/k/v in, out to host"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        per_pass, rows, threads = cpu_sample(wl, target_s=12.0)
+        step_s = per_pass * L * (B / rows)
+        cpu = {"value": B / step_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"1 of {L} layers x {rows} of {B} sequences at full context (C oracle, OpenMP), "
+                         f"{per_pass * 1e3:.1f} ms per pass, extrapolated linearly"}
+
+    if rank == 0:
+        line = {
+            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": dict(workload_config(wl, args.workload), parallelism=f"batch-sharded x{world}", splits=splits,
+                           step="CUDA graph of 28x(quantize-append, split-K scan, combine)" if L == 28 else
+                           f"CUDA graph of {L}x(quantize-append, split-K scan, combine)"),
+            "us_per_layer": ms_per_step * 1e3 / L,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": args.steps * L * 3, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

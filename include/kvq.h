@@ -132,6 +132,8 @@ typedef struct KvqAttnArgs {
     const int16_t* outlier_idx;  /* [Hkv, n_out]                                          */
     const int32_t* context_lens; /* int32 [B]; values are clamped to [0, max_ctx]         */
     int32_t splits;           /* KV splits per (batch, kv head); 0 = library heuristic    */
+    int32_t stages;           /* 0 = split kernel + combine; 1 = split kernel only; 2 = combine only
+                                 (for profiling one stage; the workspace carries the partials) */
     void*   workspace;        /* >= kvq_decode_workspace_bytes(...)                       */
     size_t  workspace_bytes;
     void*   out;              /* fp16 [B, Hq, D] or NULL                                  */
@@ -175,6 +177,13 @@ typedef struct KvqCombineArgs {
  * online-softmax merge of src/kernels/triton_decode_attn_int8.py:247-283.
  */
 KVQ_API int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream);
+
+/*
+ * Device-side error flag (synchronises the device): 0 = clean, 1 = a bounded wait on a
+ * copy-completion barrier expired inside the tensor-core decode kernel (results of that
+ * launch are invalid).  `reset` != 0 clears it.  Negative = KVQ_E*.  No reference counterpart.
+ */
+KVQ_API int kvq_debug_error_flag(int reset);
 
 KVQ_API const char* kvq_strerror(int code);
 KVQ_API int  kvq_last_cuda_error(void);     /* cudaError_t of the last KVQ_ECUDA on this thread */

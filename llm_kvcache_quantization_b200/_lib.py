@@ -64,7 +64,7 @@ class KvqAttnArgs(C.Structure):
         ("k", KvqCacheSide), ("v", KvqCacheSide),
         ("n_out", _i32), ("outlier_idx", _vp),
         ("context_lens", _vp),
-        ("splits", _i32),
+        ("splits", _i32), ("stages", _i32),
         ("workspace", _vp), ("workspace_bytes", C.c_size_t),
         ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
         ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),
@@ -86,6 +86,7 @@ EXPORTS = (
     ("kvq_decode_workspace_bytes", C.c_size_t, (_i32, _i32, _i32, _i32)),
     ("kvq_decode_pick_splits", _i32, (_i32, _i32, _i32)),
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
+    ("kvq_debug_error_flag", C.c_int, (C.c_int,)),
     ("kvq_strerror", C.c_char_p, (C.c_int,)),
     ("kvq_last_cuda_error", C.c_int, ()),
     ("kvq_abi_version", C.c_int, ()),

@@ -5,7 +5,10 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <stdlib.h>
+
 #include "kvq_decode_generic.cuh"
+#include "kvq_decode_mma.cuh"
 #include "kvq_internal.h"
 
 namespace kvq {
@@ -113,6 +116,99 @@ static int dispatch_generic(const AttnParams& p, bool asym, cudaStream_t st) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core path: eligibility, TMA descriptors, launch
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+
+// Payload [B, Hkv, S, row_bytes] as a 4-D byte tensor; box = (row_bytes, TS, 1, 1), swizzle = row width.
+// Rows at or beyond `s_extent` are zero-filled by the copy engine.
+static int make_payload_map(CUtensorMap* map, const KvqCacheSide& sd, int row_bytes, int s_extent, int hkv, int b) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return KVQ_EUNSUPPORTED;
+    cuuint64_t dims[4] = {(cuuint64_t)row_bytes, (cuuint64_t)s_extent, (cuuint64_t)hkv, (cuuint64_t)b};
+    cuuint64_t strides[3] = {(cuuint64_t)sd.pay_stride_s, (cuuint64_t)sd.pay_stride_h, (cuuint64_t)sd.pay_stride_b};
+    cuuint32_t box[4] = {(cuuint32_t)row_bytes, (cuuint32_t)kTS, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(sd.payload), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? KVQ_OK : KVQ_EUNSUPPORTED;
+}
+
+static bool mma_side_ok(const KvqCacheSide& s, int row_bytes, int hkv, int b) {
+    if (s.pay_stride_s < row_bytes || (s.pay_stride_s & 15) || (s.pay_stride_h & 15) || (s.pay_stride_b & 15)) return false;
+    if (hkv > 1 && s.pay_stride_h <= 0) return false;
+    if (b > 1 && s.pay_stride_b <= 0) return false;
+    // scales [.., S, 4] with tokens contiguous and 16-byte aligned (b, h) rows
+    if (s.sc_stride_s != 4 || (s.sc_stride_h & 7) || (s.sc_stride_b & 7)) return false;
+    if (((uintptr_t)s.scale & 15) || (s.zp && ((uintptr_t)s.zp & 15))) return false;
+    return true;
+}
+
+static bool mma_eligible(const AttnParams& p, bool asym) {
+    const KvqAttnArgs& a = p.a;
+    if (getenv("KVQ_FORCE_GENERIC")) return false;
+    if (a.D != 128 || a.group_size != 32) return false;
+    if (a.format != KVQ_FMT_INT8 && a.format != KVQ_FMT_INT4) return false;
+    if (a.format == KVQ_FMT_INT8 && asym) return false;
+    if (a.n_out != 0) return false;
+    if (a.max_ctx < 1) return false;
+    const int rb = a.format == KVQ_FMT_INT8 ? 128 : 64;
+    if (!mma_side_ok(a.k, rb, a.Hkv, a.B) || !mma_side_ok(a.v, rb, a.Hkv, a.B)) return false;
+    if (((uintptr_t)a.q & 15) || (a.q_stride_b & 7) || (a.q_stride_h & 7)) return false;
+    return true;
+}
+
+template <int FMT, bool ASYM>
+static int launch_mma(const AttnParams& p, cudaStream_t st) {
+    constexpr int RB = FMT == KVQ_FMT_INT8 ? 128 : 64;
+    MmaParams mp;
+    mp.p = p;
+    mp.nstage = FMT == KVQ_FMT_INT8 ? 3 : 4;
+    mp.stage_bytes = mma_stage_bytes(FMT, ASYM);
+    mp.warp_smem_bytes = mp.nstage * mp.stage_bytes;
+    mp.row_bytes = RB;
+    const size_t dyn = (size_t)kMmaWarps * mp.warp_smem_bytes + 1024;
+    static bool attr_done = false;          // one flag per template instantiation
+    if (!attr_done) {
+        int rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        if (rc) return rc;
+        attr_done = true;
+    }
+    CUtensorMap kmap, vmap;
+    int rc = make_payload_map(&kmap, p.a.k, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
+    if (rc) return rc;
+    rc = make_payload_map(&vmap, p.a.v, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
+    if (rc) return rc;
+    dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
+    decode_split_mma_kernel<FMT, ASYM><<<grid, kMmaWarps * 32, dyn, st>>>(mp, kmap, vmap);
+    return check_launch();
+}
+
+static int dispatch_mma(const AttnParams& p, bool asym, cudaStream_t st) {
+    if (p.a.format == KVQ_FMT_INT8) return launch_mma<KVQ_FMT_INT8, false>(p, st);
+    return asym ? launch_mma<KVQ_FMT_INT4, true>(p, st) : launch_mma<KVQ_FMT_INT4, false>(p, st);
+}
+
 }  // namespace kvq
 
 extern "C" size_t kvq_decode_workspace_bytes(int32_t B, int32_t Hq, int32_t D, int32_t splits) {
@@ -174,10 +270,28 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     p.ws_ml = (float*)((char*)a.workspace + o_bytes);
 
     cudaStream_t st = (cudaStream_t)stream;
-    rc = dispatch_generic(p, asym, st);
-    if (rc) return rc;
-    combine_splits_kernel<<<dim3(a.Hq, a.B), a.D, 0, st>>>(p);
-    return check_launch();
+    if (a.stages < 0 || a.stages > 2) return KVQ_EINVAL;
+    if (a.stages != 2) {
+        rc = KVQ_EUNSUPPORTED;
+        if (mma_eligible(p, asym)) rc = dispatch_mma(p, asym, st);
+        if (rc == KVQ_EUNSUPPORTED) rc = dispatch_generic(p, asym, st);
+        if (rc) return rc;
+    }
+    if (a.stages != 1) {
+        combine_splits_kernel<<<dim3(a.Hq, a.B), a.D, 0, st>>>(p);
+        rc = check_launch();
+    }
+    return rc;
+}
+
+extern "C" int kvq_debug_error_flag(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, kvq::g_kvq_error_flag, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;
+    if (reset && v) {
+        int z = 0;
+        if (cudaMemcpyToSymbol(kvq::g_kvq_error_flag, &z, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;
+    }
+    return v;
 }
 
 extern "C" int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream) {

@@ -57,8 +57,8 @@ __device__ __forceinline__ void load_dequant(const char* row, int d0, __half sc,
         else { *(uint2*)c = *(const uint2*)p; }
 #pragma unroll
         for (int i = 0; i < N; ++i) {
-            __half v = __hmul(__int2half_rn((int)c[i]), sc);
-            if (ASYM) v = __hadd(v, zp);
+            __half v = __hmul_rn(__int2half_rn((int)c[i]), sc);
+            if (ASYM) v = __hadd_rn(v, zp);
             out[i] = __half2float(v);
         }
     } else {
@@ -69,9 +69,9 @@ __device__ __forceinline__ void load_dequant(const char* row, int d0, __half sc,
         else { *(uint32_t*)c = *(const uint32_t*)p; }
 #pragma unroll
         for (int i = 0; i < N / 2; ++i) {
-            __half v0 = __hmul(__int2half_rn((int)(c[i] >> 4) - 8), sc);
-            __half v1 = __hmul(__int2half_rn((int)(c[i] & 15) - 8), sc);
-            if (ASYM) { v0 = __hadd(v0, zp); v1 = __hadd(v1, zp); }
+            __half v0 = __hmul_rn(__int2half_rn((int)(c[i] >> 4) - 8), sc);
+            __half v1 = __hmul_rn(__int2half_rn((int)(c[i] & 15) - 8), sc);
+            if (ASYM) { v0 = __hadd_rn(v0, zp); v1 = __hadd_rn(v1, zp); }
             out[2 * i] = __half2float(v0);
             out[2 * i + 1] = __half2float(v1);
         }

@@ -169,7 +169,7 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
                 k_zp=None, v_zp=None, inv_tau: Optional[torch.Tensor] = None,
                 outlier_idx=None, k_side=None, v_side=None,
                 splits: int = 0, out: Optional[torch.Tensor] = None,
-                return_partial: bool = False, max_ctx: Optional[int] = None):
+                return_partial: bool = False, max_ctx: Optional[int] = None, stages: int = 0):
     """Fused q_len==1 attention over a (quantized) cache.  q fp16 [B,Hq,D].
 
     Returns `out` fp16 [B,Hq,D]; with `return_partial` also the normalised
@@ -199,6 +199,7 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
             raise ValueError("inv_tau must be a contiguous fp32 [Hq] tensor")
         a.inv_tau = inv_tau.data_ptr()
     a.sm_scale = float(sm_scale)
+    a.stages = int(stages)
     a.k = _cache_side(k_payload, k_scale, k_zp, k_side)
     a.v = _cache_side(v_payload, v_scale, v_zp, v_side)
     if outlier_idx is not None:
