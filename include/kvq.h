@@ -157,6 +157,10 @@ typedef struct KvqAttnArgs {
  */
 KVQ_API int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream);
 
+/* Host-side query, no launch: 1 if kvq_decode_attn would take the tensor-core TMA kernel for these
+ * arguments (head_dim 128, group 32, int8 / packed int4, 16-byte aligned rows), 0 for the generic kernel. */
+KVQ_API int kvq_decode_kernel_kind(const KvqAttnArgs* args);
+
 KVQ_API size_t kvq_decode_workspace_bytes(int32_t B, int32_t Hq, int32_t D, int32_t splits);
 /* split count the library would choose for this shape on the current device */
 KVQ_API int32_t kvq_decode_pick_splits(int32_t B, int32_t Hkv, int32_t max_ctx);

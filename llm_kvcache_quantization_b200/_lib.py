@@ -87,6 +87,7 @@ EXPORTS = (
     ("kvq_decode_pick_splits", _i32, (_i32, _i32, _i32)),
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
     ("kvq_debug_error_flag", C.c_int, (C.c_int,)),
+    ("kvq_decode_kernel_kind", C.c_int, (C.POINTER(KvqAttnArgs),)),
     ("kvq_strerror", C.c_char_p, (C.c_int,)),
     ("kvq_last_cuda_error", C.c_int, ()),
     ("kvq_abi_version", C.c_int, ()),

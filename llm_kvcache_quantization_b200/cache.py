@@ -129,7 +129,9 @@ class _CacheBase:
             if new_capacity < target_len:
                 raise ValueError(
                     f"target_len {target_len} exceeds capped capacity {new_capacity} for layer {layer_id}")
-        new = self._alloc(specs, new_capacity)     # an OOM here leaves the layer untouched
+        # physical slots are rounded up to 32 tokens so that every (batch, head) row of every
+        # buffer starts 16-byte aligned (the tensor-core decode kernel copies 16-byte units)
+        new = self._alloc(specs, (new_capacity + 31) // 32 * 32)     # an OOM here leaves the layer untouched
         old_len = self._layer_seq_lens[layer_id]
         if bufs is not None and old_len > 0:
             for name in new:

@@ -284,6 +284,16 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     return rc;
 }
 
+extern "C" int kvq_decode_kernel_kind(const KvqAttnArgs* args) {
+    using namespace kvq;
+    if (!args) return KVQ_EINVAL;
+    AttnParams p;
+    p.a = *args;
+    if (p.a.group_size == -1) p.a.group_size = p.a.D;
+    const bool asym = p.a.k.zp != nullptr || p.a.v.zp != nullptr;
+    return mma_eligible(p, asym) ? 1 : 0;
+}
+
 extern "C" int kvq_debug_error_flag(int reset) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, kvq::g_kvq_error_flag, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;

@@ -226,11 +226,34 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
             pl = torch.empty((B, Hq), dtype=torch.float32, device=dev)
             a.part_o, a.part_m, a.part_l = po.data_ptr(), pm.data_ptr(), pl.data_ptr()
             part = (po, pm, pl)
-        rc = lib.kvq_decode_attn(C.byref(a), _stream_ptr(dev)) if B > 0 else 0
+        if B > 0 and a.max_ctx > 0:
+            rc = lib.kvq_decode_attn(C.byref(a), _stream_ptr(dev))
+        else:
+            # nothing cached (an empty sequence shard): zeros, and the neutral partial (l = 0, m = -inf)
+            rc = 0
+            out.zero_()
+            if part is not None:
+                part[0].zero_(); part[1].fill_(float("-inf")); part[2].zero_()
     _lib.check("kvq_decode_attn", rc)
     if return_partial:
         return out, part
     return out
+
+
+def decode_kernel_kind(fmt: int, q, k_payload, v_payload, k_scale, v_scale, *, k_zp=None, v_zp=None,
+                       n_out: int = 0) -> int:
+    """Which kernel kvq_decode_attn would launch for these tensors: 1 = tensor-core TMA kernel,
+    0 = generic kernel.  Pure host-side query (no launch)."""
+    a = _lib.KvqAttnArgs()
+    B, Hq, D = q.shape
+    a.format, a.B, a.Hq, a.Hkv, a.D = fmt, B, Hq, k_payload.shape[1], D
+    a.group_size = D // (1 if k_scale is None else k_scale.shape[-1])
+    a.max_ctx = k_payload.shape[2]
+    a.q, a.q_stride_b, a.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    a.k = _cache_side(k_payload, k_scale, k_zp, None)
+    a.v = _cache_side(v_payload, v_scale, v_zp, None)
+    a.n_out = n_out
+    return int(_lib.load().kvq_decode_kernel_kind(C.byref(a)))
 
 
 def lse_combine(part_o: torch.Tensor, part_m: torch.Tensor, part_l: torch.Tensor,
