@@ -162,8 +162,10 @@ KVQ_API int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream);
 KVQ_API int kvq_decode_kernel_kind(const KvqAttnArgs* args);
 
 KVQ_API size_t kvq_decode_workspace_bytes(int32_t B, int32_t Hq, int32_t D, int32_t splits);
-/* split count the library would choose for this shape on the current device */
-KVQ_API int32_t kvq_decode_pick_splits(int32_t B, int32_t Hkv, int32_t max_ctx);
+/* Split count the library would choose for these arguments on the current device (host-side query,
+ * no launch): the count whose last wave of CTAs is fullest given the resident CTAs per SM of the
+ * kernel that would run, with at least one 128-token slice per split. */
+KVQ_API int32_t kvq_decode_pick_splits(const KvqAttnArgs* args);
 
 typedef struct KvqCombineArgs {
     int32_t P, B, Hq, D;      /* P partials (e.g. one per GPU)                            */

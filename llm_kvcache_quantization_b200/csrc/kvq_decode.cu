@@ -1,10 +1,9 @@
-// Host side of kvq_decode_attn / kvq_lse_combine: argument validation, split
-// heuristic, kernel selection, and the two combine kernels.
+// Host side of kvq_decode_attn / kvq_lse_combine: argument validation, kernel
+// selection, wave-aware split heuristic, TMA descriptors, and the two combine kernels.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
-
 #include <stdlib.h>
 
 #include "kvq_decode_generic.cuh"
@@ -82,17 +81,13 @@ static int validate_side(const KvqCacheSide& s, const KvqAttnArgs& a, bool asym)
     return KVQ_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Generic kernel dispatch
+// ---------------------------------------------------------------------------
 template <int FMT, bool ASYM, int D>
 static int launch_generic(const AttnParams& p, cudaStream_t st) {
     dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
     size_t dyn = (size_t)4 * kHeadsPerCta * D * sizeof(float);
-    static bool attr_done = false;
-    if (!attr_done && dyn > 48 * 1024) {
-        int rc = check_cuda(cudaFuncSetAttribute(decode_split_generic_kernel<FMT, ASYM, D>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        if (rc) return rc;
-        attr_done = true;
-    }
     decode_split_generic_kernel<FMT, ASYM, D><<<grid, 128, dyn, st>>>(p);
     return check_launch();
 }
@@ -117,7 +112,7 @@ static int dispatch_generic(const AttnParams& p, bool asym, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------
-// Tensor-core path: eligibility, TMA descriptors, launch
+// Tensor-core path: eligibility, TMA descriptors, occupancy, launch
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -153,13 +148,18 @@ static int make_payload_map(CUtensorMap* map, const KvqCacheSide& sd, int row_by
     return r == CUDA_SUCCESS ? KVQ_OK : KVQ_EUNSUPPORTED;
 }
 
-static bool mma_side_ok(const KvqCacheSide& s, int row_bytes, int hkv, int b) {
+static bool mma_side_ok(const KvqCacheSide& s, int row_bytes, int hkv, int b, int n_out) {
     if (s.pay_stride_s < row_bytes || (s.pay_stride_s & 15) || (s.pay_stride_h & 15) || (s.pay_stride_b & 15)) return false;
     if (hkv > 1 && s.pay_stride_h <= 0) return false;
     if (b > 1 && s.pay_stride_b <= 0) return false;
     // scales [.., S, 4] with tokens contiguous and 16-byte aligned (b, h) rows
     if (s.sc_stride_s != 4 || (s.sc_stride_h & 7) || (s.sc_stride_b & 7)) return false;
     if (((uintptr_t)s.scale & 15) || (s.zp && ((uintptr_t)s.zp & 15))) return false;
+    if (n_out > 0) {
+        if (!s.side || ((uintptr_t)s.side & 15) || s.side_stride_s != n_out || (s.side_stride_h & 7) ||
+            (s.side_stride_b & 7))
+            return false;
+    }
     return true;
 }
 
@@ -169,44 +169,146 @@ static bool mma_eligible(const AttnParams& p, bool asym) {
     if (a.D != 128 || a.group_size != 32) return false;
     if (a.format != KVQ_FMT_INT8 && a.format != KVQ_FMT_INT4) return false;
     if (a.format == KVQ_FMT_INT8 && asym) return false;
-    if (a.n_out != 0) return false;
+    if (a.n_out < 0 || a.n_out > kMaxOut || (a.n_out > 0 && asym)) return false;
     if (a.max_ctx < 1) return false;
+    if (!a.k.payload || !a.v.payload || !a.k.scale || !a.v.scale) return false;
     const int rb = a.format == KVQ_FMT_INT8 ? 128 : 64;
-    if (!mma_side_ok(a.k, rb, a.Hkv, a.B) || !mma_side_ok(a.v, rb, a.Hkv, a.B)) return false;
+    if (!mma_side_ok(a.k, rb, a.Hkv, a.B, a.n_out) || !mma_side_ok(a.v, rb, a.Hkv, a.B, a.n_out)) return false;
     if (((uintptr_t)a.q & 15) || (a.q_stride_b & 7) || (a.q_stride_h & 7)) return false;
     return true;
 }
 
-template <int FMT, bool ASYM>
+// Launch configuration of one instantiation: stages, shared memory, resident CTAs per SM.
+struct MmaConfig {
+    int nstage;
+    int stage_bytes;
+    size_t dyn_smem;
+    int ctas_per_sm;
+    int rc;
+};
+
+static int stages_from_env(int dflt) {
+    const char* e = getenv("KVQ_MMA_STAGES");
+    if (!e) return dflt;
+    int v = atoi(e);
+    return (v >= 2 && v <= 8) ? v : dflt;
+}
+
+template <int FMT, bool ASYM, bool OUTL>
+static const MmaConfig& mma_config() {
+    static MmaConfig cfg = [] {
+        MmaConfig c;
+        c.nstage = stages_from_env(3);
+        c.stage_bytes = mma_stage_bytes(FMT, ASYM, OUTL);
+        c.dyn_smem = (size_t)kMmaWarps * c.nstage * c.stage_bytes + 1024;
+        c.ctas_per_sm = 1;
+        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM, OUTL>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.dyn_smem));
+        if (c.rc == KVQ_OK) {
+            int n = 0;
+            c.rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &n, decode_split_mma_kernel<FMT, ASYM, OUTL>, kMmaWarps * 32, c.dyn_smem));
+            if (n > 0) c.ctas_per_sm = n;
+        }
+        return c;
+    }();
+    return cfg;
+}
+
+static const MmaConfig* mma_config_for(const AttnParams& p, bool asym) {
+    const bool outl = p.a.n_out > 0;
+    if (p.a.format == KVQ_FMT_INT8)
+        return outl ? &mma_config<KVQ_FMT_INT8, false, true>() : &mma_config<KVQ_FMT_INT8, false, false>();
+    if (asym) return &mma_config<KVQ_FMT_INT4, true, false>();
+    return outl ? &mma_config<KVQ_FMT_INT4, false, true>() : &mma_config<KVQ_FMT_INT4, false, false>();
+}
+
+template <int FMT, bool ASYM, bool OUTL>
 static int launch_mma(const AttnParams& p, cudaStream_t st) {
     constexpr int RB = FMT == KVQ_FMT_INT8 ? 128 : 64;
+    const MmaConfig& cfg = mma_config<FMT, ASYM, OUTL>();
+    if (cfg.rc) return cfg.rc;
     MmaParams mp;
     mp.p = p;
-    mp.nstage = FMT == KVQ_FMT_INT8 ? 3 : 4;
-    mp.stage_bytes = mma_stage_bytes(FMT, ASYM);
-    mp.warp_smem_bytes = mp.nstage * mp.stage_bytes;
+    mp.nstage = cfg.nstage;
+    mp.stage_bytes = cfg.stage_bytes;
+    mp.warp_smem_bytes = cfg.nstage * cfg.stage_bytes;
     mp.row_bytes = RB;
-    const size_t dyn = (size_t)kMmaWarps * mp.warp_smem_bytes + 1024;
-    static bool attr_done = false;          // one flag per template instantiation
-    if (!attr_done) {
-        int rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        if (rc) return rc;
-        attr_done = true;
-    }
     CUtensorMap kmap, vmap;
     int rc = make_payload_map(&kmap, p.a.k, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;
     rc = make_payload_map(&vmap, p.a.v, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;
     dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
-    decode_split_mma_kernel<FMT, ASYM><<<grid, kMmaWarps * 32, dyn, st>>>(mp, kmap, vmap);
+    decode_split_mma_kernel<FMT, ASYM, OUTL><<<grid, kMmaWarps * 32, cfg.dyn_smem, st>>>(mp, kmap, vmap);
     return check_launch();
 }
 
 static int dispatch_mma(const AttnParams& p, bool asym, cudaStream_t st) {
-    if (p.a.format == KVQ_FMT_INT8) return launch_mma<KVQ_FMT_INT8, false>(p, st);
-    return asym ? launch_mma<KVQ_FMT_INT4, true>(p, st) : launch_mma<KVQ_FMT_INT4, false>(p, st);
+    const bool outl = p.a.n_out > 0;
+    if (p.a.format == KVQ_FMT_INT8)
+        return outl ? launch_mma<KVQ_FMT_INT8, false, true>(p, st) : launch_mma<KVQ_FMT_INT8, false, false>(p, st);
+    if (asym) return launch_mma<KVQ_FMT_INT4, true, false>(p, st);
+    return outl ? launch_mma<KVQ_FMT_INT4, false, true>(p, st) : launch_mma<KVQ_FMT_INT4, false, false>(p, st);
+}
+
+// ---------------------------------------------------------------------------
+// Split heuristic.  All CTAs of a launch do the same amount of work when the
+// batch rows have equal context, so the launch takes ceil(ctas / slots) "waves"
+// (slots = SMs x resident CTAs per SM).  Pick the split count whose last wave
+// is fullest, among those that leave at least `min_tokens` per split; prefer
+// fewer splits on ties (less workspace traffic, cheaper combine).
+// ---------------------------------------------------------------------------
+static int pick_splits_waves(long long rows, int max_ctx, int slots, int min_tokens) {
+    long long by_len = max_ctx / min_tokens;
+    if (by_len < 1) by_len = 1;
+    if (by_len > 256) by_len = 256;
+    if (rows >= 4LL * slots) return 1;            // many waves already: the tail is a small fraction
+    int best = 1;
+    double best_score = -1.0;
+    for (int s = 1; s <= by_len; ++s) {
+        const long long ctas = rows * s;
+        const long long waves = (ctas + slots - 1) / slots;
+        if (waves > 4 && s > 1) break;
+        // tokens are scanned in units of 32 per warp-stage: quantisation of the per-split length
+        const int per = ((max_ctx + s - 1) / s + kTS - 1) / kTS * kTS;
+        const double useful = (double)max_ctx / ((double)per * s);
+        const double score = (double)ctas / (double)(waves * slots) * useful;
+        if (score > best_score + 0.02) {
+            best_score = score;
+            best = s;
+        }
+    }
+    return best;
+}
+
+static int pick_splits_internal(const AttnParams& p, bool asym, bool mma) {
+    const long long rows = (long long)p.a.B * p.a.Hkv * p.rep_chunks;
+    const int sms = device_sm_count();
+    if (mma) {
+        const MmaConfig* cfg = mma_config_for(p, asym);
+        return pick_splits_waves(rows, p.a.max_ctx, sms * cfg->ctas_per_sm, kMmaWarps * kTS);
+    }
+    return pick_splits_waves(rows, p.a.max_ctx, sms * 8, 256);
+}
+
+static int fill_params(const KvqAttnArgs& a, AttnParams& p, bool& asym) {
+    if (a.B < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.D <= 0 || a.max_ctx < 0) return KVQ_EINVAL;
+    if (a.Hq % a.Hkv != 0) return KVQ_EINVAL;
+    if (a.D != 64 && a.D != 128 && a.D != 256) return KVQ_EUNSUPPORTED;
+    int gs = a.group_size == -1 ? a.D : a.group_size;
+    if (a.format == KVQ_FMT_FP16) gs = a.D;
+    if (gs <= 0 || a.D % gs != 0 || gs % 8 != 0) return KVQ_EINVAL;
+    asym = a.k.zp != nullptr || a.v.zp != nullptr;
+    p.a = a;
+    p.a.group_size = gs;
+    p.G = a.D / gs;
+    p.n_rep = a.Hq / a.Hkv;
+    p.rep_chunks = (p.n_rep + kHeadsPerCta - 1) / kHeadsPerCta;
+    p.splits = 1;
+    p.ws_o = nullptr;
+    p.ws_ml = nullptr;
+    return KVQ_OK;
 }
 
 }  // namespace kvq
@@ -219,50 +321,48 @@ extern "C" size_t kvq_decode_workspace_bytes(int32_t B, int32_t Hq, int32_t D, i
     return ((o + 255) & ~(size_t)255) + ((ml + 255) & ~(size_t)255);
 }
 
-extern "C" int32_t kvq_decode_pick_splits(int32_t B, int32_t Hkv, int32_t max_ctx) {
-    if (B <= 0 || Hkv <= 0 || max_ctx <= 0) return 1;
-    const int sms = kvq::device_sm_count();
-    long long base = (long long)B * Hkv;
-    long long want = 4LL * sms;                         // ~4 CTAs per SM in flight
-    long long splits = (want + base - 1) / base;
-    long long by_len = max_ctx / 256;                   // keep >= 256 tokens per split
-    if (by_len < 1) by_len = 1;
-    if (splits > by_len) splits = by_len;
-    if (splits > 256) splits = 256;
-    if (splits < 1) splits = 1;
-    return (int32_t)splits;
+extern "C" int32_t kvq_decode_pick_splits(const KvqAttnArgs* args) {
+    using namespace kvq;
+    if (!args) return 1;
+    AttnParams p;
+    bool asym = false;
+    if (fill_params(*args, p, asym) != KVQ_OK || args->B == 0 || args->max_ctx == 0) return 1;
+    return pick_splits_internal(p, asym, mma_eligible(p, asym));
+}
+
+extern "C" int kvq_decode_kernel_kind(const KvqAttnArgs* args) {
+    using namespace kvq;
+    if (!args) return KVQ_EINVAL;
+    AttnParams p;
+    bool asym = false;
+    int rc = fill_params(*args, p, asym);
+    if (rc) return rc;
+    return mma_eligible(p, asym) ? 1 : 0;
 }
 
 extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     using namespace kvq;
     if (!args) return KVQ_EINVAL;
     const KvqAttnArgs& a = *args;
-    if (a.B < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.D <= 0 || a.max_ctx < 0) return KVQ_EINVAL;
-    if (a.Hq % a.Hkv != 0) return KVQ_EINVAL;
+    AttnParams p;
+    bool asym = false;
+    int rc = fill_params(a, p, asym);
+    if (rc) return rc;
     if (a.B == 0) return KVQ_OK;
     if (!a.q || !a.context_lens) return KVQ_EINVAL;
     if (!a.out && !a.part_o) return KVQ_EINVAL;
     if ((a.part_o != nullptr) != (a.part_m != nullptr) || (a.part_o != nullptr) != (a.part_l != nullptr))
         return KVQ_EINVAL;
-    if (a.D != 64 && a.D != 128 && a.D != 256) return KVQ_EUNSUPPORTED;
-    int gs = a.group_size == -1 ? a.D : a.group_size;
-    if (a.format == KVQ_FMT_FP16) gs = a.D;
-    if (gs <= 0 || a.D % gs != 0 || gs % 8 != 0) return KVQ_EINVAL;
-    const bool asym = a.k.zp != nullptr || a.v.zp != nullptr;
     if (a.n_out < 0 || (a.n_out > 0 && (!a.outlier_idx || asym))) return KVQ_EINVAL;
-    int rc = validate_side(a.k, a, asym);
+    rc = validate_side(a.k, a, asym);
     if (rc) return rc;
     rc = validate_side(a.v, a, asym);
     if (rc) return rc;
     if ((a.q_stride_b & 1) || (a.q_stride_h & 1) || (((uintptr_t)a.q) & 3)) return KVQ_EINVAL;
+    if (a.stages < 0 || a.stages > 2) return KVQ_EINVAL;
 
-    AttnParams p;
-    p.a = a;
-    p.a.group_size = gs;
-    p.G = a.D / gs;
-    p.n_rep = a.Hq / a.Hkv;
-    p.rep_chunks = (p.n_rep + kHeadsPerCta - 1) / kHeadsPerCta;
-    p.splits = a.splits > 0 ? a.splits : kvq_decode_pick_splits(a.B, a.Hkv, a.max_ctx);
+    const bool mma = mma_eligible(p, asym);
+    p.splits = a.splits > 0 ? a.splits : pick_splits_internal(p, asym, mma);
     size_t need = kvq_decode_workspace_bytes(a.B, a.Hq, a.D, p.splits);
     if (!a.workspace || a.workspace_bytes < need || (((uintptr_t)a.workspace) & 15)) return KVQ_EWORKSPACE;
     size_t o_bytes = ((size_t)a.B * a.Hq * p.splits * a.D * sizeof(float) + 255) & ~(size_t)255;
@@ -270,10 +370,9 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     p.ws_ml = (float*)((char*)a.workspace + o_bytes);
 
     cudaStream_t st = (cudaStream_t)stream;
-    if (a.stages < 0 || a.stages > 2) return KVQ_EINVAL;
     if (a.stages != 2) {
         rc = KVQ_EUNSUPPORTED;
-        if (mma_eligible(p, asym)) rc = dispatch_mma(p, asym, st);
+        if (mma) rc = dispatch_mma(p, asym, st);
         if (rc == KVQ_EUNSUPPORTED) rc = dispatch_generic(p, asym, st);
         if (rc) return rc;
     }
@@ -282,16 +381,6 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
         rc = check_launch();
     }
     return rc;
-}
-
-extern "C" int kvq_decode_kernel_kind(const KvqAttnArgs* args) {
-    using namespace kvq;
-    if (!args) return KVQ_EINVAL;
-    AttnParams p;
-    p.a = *args;
-    if (p.a.group_size == -1) p.a.group_size = p.a.D;
-    const bool asym = p.a.k.zp != nullptr || p.a.v.zp != nullptr;
-    return mma_eligible(p, asym) ? 1 : 0;
 }
 
 extern "C" int kvq_debug_error_flag(int reset) {

@@ -59,8 +59,10 @@ struct MmaParams {
 // Bytes of one pipeline stage: K tile, V tile (each TS rows), then 2 (4 with zero-points)
 // scale tiles of TS x 8 B.  Rounded so that every payload tile stays aligned to the swizzle
 // period (1024 B for 128-byte rows, 512 B for 64-byte rows).
-__host__ __device__ constexpr int mma_stage_bytes(int fmt, bool asym) {
-    return fmt == KVQ_FMT_INT8 ? 2 * kTS * 128 + 1024 : 2 * kTS * 64 + (asym ? 1024 : 512);
+constexpr int kMaxOut = 4;           // fp16 outlier channels per kv head the tensor-core kernel handles
+__host__ __device__ constexpr int mma_stage_bytes(int fmt, bool asym, bool outl) {
+    // with outliers: + K and V side tiles of TS x kMaxOut fp16 (256 B each)
+    return fmt == KVQ_FMT_INT8 ? 2 * kTS * 128 + 1024 : 2 * kTS * 64 + ((asym || outl) ? 1024 : 512);
 }
 
 // ---------------------------------------------------------------- PTX helpers
@@ -134,6 +136,12 @@ __device__ __forceinline__ uint32_t hsub2_u(uint32_t a, uint32_t b) { return h2_
 __device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
     return h2_as_u32(__hfma2(u32_as_h2(a), u32_as_h2(b), u32_as_h2(c)));
 }
+// exp2 on the special-function unit; ex2.approx(-inf) = +0
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     return h2_as_u32(__floats2half2_rn(lo, hi));
 }
@@ -169,13 +177,14 @@ __device__ __forceinline__ uint32_t apply_scale(uint32_t c, uint32_t s2, uint32_
 //   [0, TS*RB)            K payload tile   (TMA, swizzled)
 //   [TS*RB, 2*TS*RB)      V payload tile   (TMA, swizzled)
 //   then K scales [TS][4] fp16, V scales, (K zero-points, V zero-points)   256 B each
-template <int FMT, bool ASYM>
+template <int FMT, bool ASYM, bool OUTL>
 __global__ void __launch_bounds__(kMmaWarps * 32)
 decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
     constexpr int RB = (FMT == KVQ_FMT_INT8) ? 128 : 64;      // payload bytes per token row
     constexpr int D = 128;
-    constexpr int STAGE_BYTES = mma_stage_bytes(FMT, ASYM);
+    constexpr int STAGE_BYTES = mma_stage_bytes(FMT, ASYM, OUTL);
+    static_assert(!(ASYM && OUTL), "outlier side buffer is defined for symmetric formats");
     const AttnParams& p = mp.p;
     const KvqAttnArgs& a = p.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -242,6 +251,29 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         }
     }
 
+    // outlier channels: q values of heads 2t, 2t+1 at the listed channels, and fp32 side accumulators
+    const int n_out = OUTL ? a.n_out : 0;
+    float qo[2][kMaxOut], oo[2][kMaxOut];
+    int och[kMaxOut];
+    if (OUTL) {
+#pragma unroll
+        for (int j = 0; j < kMaxOut; ++j) {
+            och[j] = (j < n_out) ? (int)a.outlier_idx[kvh * n_out + j] : 0;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int hd = 2 * t + e;
+                float v = 0.f;
+                if (j < n_out && hd < nh) {
+                    __half qv = ((const __half*)a.q)[(long long)b * a.q_stride_b + (long long)(h0 + hd) * a.q_stride_h + och[j]];
+                    if (a.inv_tau) qv = __hmul(qv, __float2half_rn(a.inv_tau[h0 + hd]));
+                    v = __half2float(qv);
+                }
+                qo[e][j] = v;
+                oo[e][j] = 0.f;
+            }
+        }
+    }
+
     const float qk_scale = a.sm_scale * kLog2e;
     float m_run[2] = {-INFINITY, -INFINITY};   // running max (log2 domain) of heads 2t, 2t+1
     float l_run[2] = {0.f, 0.f};               // this thread's share of the softmax denominator
@@ -258,6 +290,9 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     const __half* vs_row = (const __half*)a.v.scale + (long long)b * a.v.sc_stride_b + (long long)kvh * a.v.sc_stride_h;
     const __half* kz_row = ASYM ? (const __half*)a.k.zp + (long long)b * a.k.sc_stride_b + (long long)kvh * a.k.sc_stride_h : nullptr;
     const __half* vz_row = ASYM ? (const __half*)a.v.zp + (long long)b * a.v.sc_stride_b + (long long)kvh * a.v.sc_stride_h : nullptr;
+
+    const __half* kside_row = OUTL ? (const __half*)a.k.side + (long long)b * a.k.side_stride_b + (long long)kvh * a.k.side_stride_h : nullptr;
+    const __half* vside_row = OUTL ? (const __half*)a.v.side + (long long)b * a.v.side_stride_b + (long long)kvh * a.v.side_stride_h : nullptr;
 
     auto issue = [&](int k) {
         const int st = k % nstage;
@@ -279,6 +314,18 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             const uint32_t dst = sb + 2 * kTS * RB + (lane & 15) * 16;
             cp_async16(dst + which * (kTS * 8), (which ? vs_row : ks_row) + off, nbytes);
             if (ASYM) cp_async16(dst + (2 + which) * (kTS * 8), (which ? vz_row : kz_row) + off, nbytes);
+        }
+        if (OUTL) {
+            // side tiles: TS tokens x n_out fp16, contiguous; 4*n_out 16-byte chunks per side
+            const int nchunk = 4 * n_out;
+            const int which = lane >= nchunk;
+            const int c = lane - (which ? nchunk : 0);
+            if (c < nchunk) {
+                const int valid = max(0, min(kTS, a.max_ctx - tok0)) * n_out * 2;   // bytes inside the view
+                const int nbytes = max(0, min(16, valid - 16 * c));
+                const __half* src = (which ? vside_row : kside_row) + (nbytes ? (long long)tok0 * n_out + 8 * c : 0);
+                cp_async16(sb + 2 * kTS * RB + 2 * (kTS * 8) + which * 256 + 16 * c, src, nbytes);
+            }
         }
         cp_async_mbar_arrive(bar);
     };
@@ -305,6 +352,8 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         const uint32_t vsb = ksb + kTS * 8;
         const uint32_t kzb = ksb + 2 * kTS * 8;
         const uint32_t vzb = ksb + 3 * kTS * 8;
+        const uint32_t kob = ksb + 2 * kTS * 8;            // outlier side tiles share the zero-point slots
+        const uint32_t vob = kob + 256;
 
         // ================= q.K : logits for 2 sub-tiles of 16 tokens =================
         float sacc[2][4];
@@ -319,13 +368,13 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 unsigned short u0, u1;
                 asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u0) : "r"(ksb + r0 * 8 + 2 * t));
                 asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u1) : "r"(ksb + r1 * 8 + 2 * t));
-                s2[0] = (uint32_t)u0 * 0x00010001u;
-                s2[1] = (uint32_t)u1 * 0x00010001u;
+                s2[0] = prmt((uint32_t)u0, 0u, 0x1010u);
+                s2[1] = prmt((uint32_t)u1, 0u, 0x1010u);
                 if (ASYM) {
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u0) : "r"(kzb + r0 * 8 + 2 * t));
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u1) : "r"(kzb + r1 * 8 + 2 * t));
-                    z2[0] = (uint32_t)u0 * 0x00010001u;
-                    z2[1] = (uint32_t)u1 * 0x00010001u;
+                    z2[0] = prmt((uint32_t)u0, 0u, 0x1010u);
+                    z2[1] = prmt((uint32_t)u1, 0u, 0x1010u);
                 }
             }
             if (FMT == KVQ_FMT_INT8) {
@@ -371,6 +420,26 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             }
         }
 
+        if (OUTL) {
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+                const int r0 = 16 * sub + g, r1 = r0 + 8;
+#pragma unroll
+                for (int j = 0; j < kMaxOut; ++j) {
+                    if (j < n_out) {
+                        unsigned short u0, u1;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u0) : "r"(kob + (r0 * n_out + j) * 2));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u1) : "r"(kob + (r1 * n_out + j) * 2));
+                        const float k0 = __half2float(__ushort_as_half(u0)), k1 = __half2float(__ushort_as_half(u1));
+                        sacc[sub][0] = fmaf(qo[0][j], k0, sacc[sub][0]);
+                        sacc[sub][1] = fmaf(qo[1][j], k0, sacc[sub][1]);
+                        sacc[sub][2] = fmaf(qo[0][j], k1, sacc[sub][2]);
+                        sacc[sub][3] = fmaf(qo[1][j], k1, sacc[sub][3]);
+                    }
+                }
+            }
+        }
+
         // ================= online softmax over the 32 tokens of the stage =================
         if (partial) {
 #pragma unroll
@@ -394,7 +463,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         for (int e = 0; e < 2; ++e) {
             const float m_new = fmaxf(m_run[e], mx[e] * qk_scale);   // finite: the stage has a valid token
             changed |= (m_new != m_run[e]);
-            corr[e] = exp2f(m_run[e] - m_new);                       // exp2(-inf) = 0 on the first stage
+            corr[e] = fast_exp2(m_run[e] - m_new);                       // exp2(-inf) = 0 on the first stage
             m_run[e] = m_new;
             mneg[e] = -m_new;
         }
@@ -402,12 +471,29 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         uint32_t pb[2][2];                                           // P^T B fragments per sub-tile
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
-            float p0 = exp2f(fmaf(sacc[sub][0], qk_scale, mneg[0]));
-            float p1 = exp2f(fmaf(sacc[sub][1], qk_scale, mneg[1]));
-            float p2 = exp2f(fmaf(sacc[sub][2], qk_scale, mneg[0]));
-            float p3 = exp2f(fmaf(sacc[sub][3], qk_scale, mneg[1]));
+            float p0 = fast_exp2(fmaf(sacc[sub][0], qk_scale, mneg[0]));
+            float p1 = fast_exp2(fmaf(sacc[sub][1], qk_scale, mneg[1]));
+            float p2 = fast_exp2(fmaf(sacc[sub][2], qk_scale, mneg[0]));
+            float p3 = fast_exp2(fmaf(sacc[sub][3], qk_scale, mneg[1]));
             psum[0] += p0 + p2;
             psum[1] += p1 + p3;
+            if (OUTL) {
+                const int r0 = 16 * sub + g, r1 = r0 + 8;
+                const bool ok0 = !partial || tok0 + r0 < s1, ok1 = !partial || tok0 + r1 < s1;
+#pragma unroll
+                for (int j = 0; j < kMaxOut; ++j) {
+                    if (j < n_out) {
+                        unsigned short u0, u1;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u0) : "r"(vob + (r0 * n_out + j) * 2));
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u1) : "r"(vob + (r1 * n_out + j) * 2));
+                        const float v0 = ok0 ? __half2float(__ushort_as_half(u0)) : 0.f;
+                        const float v1 = ok1 ? __half2float(__ushort_as_half(u1)) : 0.f;
+                        if (sub == 0) { oo[0][j] *= corr[0]; oo[1][j] *= corr[1]; }
+                        oo[0][j] = fmaf(p0, v0, fmaf(p2, v1, oo[0][j]));
+                        oo[1][j] = fmaf(p1, v0, fmaf(p3, v1, oo[1][j]));
+                    }
+                }
+            }
             pb[sub][0] = movmatrix_trans(pack_h2(p0, p1));           // tokens 2t,2t+1   of head g
             pb[sub][1] = movmatrix_trans(pack_h2(p2, p3));           // tokens 2t+8,2t+9 of head g
         }
@@ -521,6 +607,25 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         ra[(2 * t + 1) * D + d0] = o[i][1];
         ra[(2 * t) * D + d1] = o[i][2];
         ra[(2 * t + 1) * D + d1] = o[i][3];
+    }
+    if (OUTL) {
+#pragma unroll
+        for (int j = 0; j < kMaxOut; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+#pragma unroll
+                for (int off = 4; off <= 16; off <<= 1) oo[e][j] += __shfl_xor_sync(0xffffffffu, oo[e][j], off);
+        __syncwarp();
+        if (g == 0) {
+            float* ra = red_acc + (size_t)warp * kHeadsPerCta * D;
+#pragma unroll
+            for (int j = 0; j < kMaxOut; ++j) {      // the payload holds code 0 there, so this is the whole value
+                if (j < n_out) {
+                    ra[(2 * t) * D + och[j]] += oo[0][j];
+                    ra[(2 * t + 1) * D + och[j]] += oo[1][j];
+                }
+            }
+        }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nh * D; i += kMmaWarps * 32) {

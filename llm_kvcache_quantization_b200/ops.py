@@ -53,8 +53,12 @@ def release_workspaces() -> None:
     _WORKSPACES.clear()
 
 
-def pick_splits(batch: int, kv_heads: int, max_ctx: int) -> int:
-    return int(_lib.load().kvq_decode_pick_splits(batch, kv_heads, max_ctx))
+_LAST_SPLITS = 0
+
+
+def last_splits() -> int:
+    """KV split count used by the most recent decode_attn call (diagnostics)."""
+    return _LAST_SPLITS
 
 
 # --------------------------------------------------------------------------- append
@@ -210,7 +214,9 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     a.context_lens = context_lens.data_ptr()
     lib = _lib.load()
     with torch.cuda.device(dev):
-        a.splits = int(splits) if splits else int(lib.kvq_decode_pick_splits(B, Hkv, a.max_ctx))
+        a.splits = int(splits) if splits else int(lib.kvq_decode_pick_splits(C.byref(a)))
+        global _LAST_SPLITS
+        _LAST_SPLITS = a.splits
         need = int(lib.kvq_decode_workspace_bytes(B, Hq, D, a.splits))
         ws = get_workspace(dev, need)
         a.workspace = ws.data_ptr()
