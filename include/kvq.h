@@ -130,7 +130,7 @@ typedef struct KvqAttnArgs {
     KvqCacheSide k, v;
     int32_t n_out;
     const int16_t* outlier_idx;  /* [Hkv, n_out]                                          */
-    const int32_t* context_lens; /* int32 [B]; values are clamped to [0, max_ctx]         */
+    const int32_t* context_lens; /* int32 [B], clamped to [0, max_ctx]; NULL = every row has max_ctx tokens */
     int32_t splits;           /* KV splits per (batch, kv head); 0 = library heuristic    */
     int32_t stages;           /* 0 = split kernel + combine; 1 = split kernel only; 2 = combine only
                                  (for profiling one stage; the workspace carries the partials) */

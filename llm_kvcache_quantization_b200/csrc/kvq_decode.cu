@@ -349,7 +349,7 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     int rc = fill_params(a, p, asym);
     if (rc) return rc;
     if (a.B == 0) return KVQ_OK;
-    if (!a.q || !a.context_lens) return KVQ_EINVAL;
+    if (!a.q) return KVQ_EINVAL;
     if (!a.out && !a.part_o) return KVQ_EINVAL;
     if ((a.part_o != nullptr) != (a.part_m != nullptr) || (a.part_o != nullptr) != (a.part_l != nullptr))
         return KVQ_EINVAL;

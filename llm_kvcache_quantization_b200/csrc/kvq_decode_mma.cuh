@@ -195,7 +195,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     const int nh = min(kHeadsPerCta, p.n_rep - rc * kHeadsPerCta);
     const int nstage = mp.nstage;
 
-    int ctx = a.context_lens[b];
+    int ctx = a.context_lens ? a.context_lens[b] : a.max_ctx;
     ctx = max(0, min(ctx, a.max_ctx));
     int s0, s1;
     split_range(ctx, p.splits, split, kTS, s0, s1);

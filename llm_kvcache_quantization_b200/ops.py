@@ -169,7 +169,7 @@ def _cache_side(payload, scale, zp, side) -> _lib.KvqCacheSide:
 
 def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: torch.Tensor,
                 k_scale: Optional[torch.Tensor], v_scale: Optional[torch.Tensor],
-                context_lens: torch.Tensor, sm_scale: float, *, head_dim: int,
+                context_lens: Optional[torch.Tensor], sm_scale: float, *, head_dim: int,
                 k_zp=None, v_zp=None, inv_tau: Optional[torch.Tensor] = None,
                 outlier_idx=None, k_side=None, v_side=None,
                 splits: int = 0, out: Optional[torch.Tensor] = None,
@@ -209,9 +209,10 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     if outlier_idx is not None:
         a.n_out = outlier_idx.shape[1]
         a.outlier_idx = outlier_idx.data_ptr()
-    if context_lens.dtype != torch.int32 or not context_lens.is_contiguous():
-        context_lens = context_lens.to(torch.int32).contiguous()
-    a.context_lens = context_lens.data_ptr()
+    if context_lens is not None:        # None: every row attends over all max_ctx tokens of the view
+        if context_lens.dtype != torch.int32 or not context_lens.is_contiguous():
+            context_lens = context_lens.to(torch.int32).contiguous()
+        a.context_lens = context_lens.data_ptr()
     lib = _lib.load()
     with torch.cuda.device(dev):
         a.splits = int(splits) if splits else int(lib.kvq_decode_pick_splits(C.byref(a)))
