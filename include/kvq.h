@@ -142,6 +142,9 @@ typedef struct KvqAttnArgs {
     float*  part_o;           /* fp32 [B, Hq, D]  o = sum p v / l                         */
     float*  part_m;           /* fp32 [B, Hq]     running max of scaled logits (-inf if empty) */
     float*  part_l;           /* fp32 [B, Hq]     sum exp(logit - m)  (0 if empty)        */
+    int64_t part_o_stride;    /* elements between consecutive (b, h) rows of part_o; 0 = D        */
+    int64_t part_ml_stride;   /* elements between consecutive (b, h) entries of part_m / part_l; 0 = 1
+                                 (lets o, m, l share one packed [B, Hq, D+2] send buffer)          */
 } KvqAttnArgs;
 
 /*
@@ -174,6 +177,10 @@ typedef struct KvqCombineArgs {
     const float* part_l;      /* fp32 [P, B, Hq]                                          */
     void*   out;              /* fp16 [B, Hq, D]                                          */
     int64_t out_stride_b, out_stride_h;
+    int64_t part_o_stride;    /* elements between (b, h) rows of part_o; 0 = D                    */
+    int64_t part_ml_stride;   /* elements between (b, h) entries of part_m / part_l; 0 = 1        */
+    int64_t part_o_stride_p;  /* elements between partials p of part_o; 0 = B*Hq*part_o_stride    */
+    int64_t part_ml_stride_p; /* elements between partials p of part_m / part_l; 0 = B*Hq*part_ml_stride */
 } KvqCombineArgs;
 
 /*

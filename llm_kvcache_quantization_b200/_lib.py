@@ -68,6 +68,7 @@ class KvqAttnArgs(C.Structure):
         ("workspace", _vp), ("workspace_bytes", C.c_size_t),
         ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
         ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),
+        ("part_o_stride", _i64), ("part_ml_stride", _i64),
     ]
 
 
@@ -76,6 +77,7 @@ class KvqCombineArgs(C.Structure):
         ("P", _i32), ("B", _i32), ("Hq", _i32), ("D", _i32),
         ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),
         ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
+        ("part_o_stride", _i64), ("part_ml_stride", _i64), ("part_o_stride_p", _i64), ("part_ml_stride_p", _i64),
     ]
 
 

@@ -37,11 +37,13 @@ __global__ void combine_splits_kernel(const AttnParams p) {
     float r = (L > 0.f) ? o / L : 0.f;
     if (a.out) ((__half*)a.out)[b * a.out_stride_b + h * a.out_stride_h + d] = __float2half_rn(r);
     if (a.part_o) {
-        long long idx = (long long)b * a.Hq + h;
-        a.part_o[idx * D + d] = r;
+        const long long idx = (long long)b * a.Hq + h;
+        const long long so = a.part_o_stride ? a.part_o_stride : D;
+        const long long sm = a.part_ml_stride ? a.part_ml_stride : 1;
+        a.part_o[idx * so + d] = r;
         if (d == 0) {
-            a.part_m[idx] = (L > 0.f) ? M * 0.6931471805599453f : -INFINITY;
-            a.part_l[idx] = L;
+            a.part_m[idx * sm] = (L > 0.f) ? M * 0.6931471805599453f : -INFINITY;
+            a.part_l[idx * sm] = L;
         }
     }
 }
@@ -51,17 +53,21 @@ __global__ void lse_combine_kernel(const KvqCombineArgs c) {
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const long long BH = (long long)c.B * c.Hq;
     const long long idx = (long long)b * c.Hq + h;
+    const long long so = c.part_o_stride ? c.part_o_stride : c.D;
+    const long long sm = c.part_ml_stride ? c.part_ml_stride : 1;
+    const long long sop = c.part_o_stride_p ? c.part_o_stride_p : BH * so;
+    const long long smp = c.part_ml_stride_p ? c.part_ml_stride_p : BH * sm;
     float M = -INFINITY;
     for (int p = 0; p < c.P; ++p) {
-        float l = c.part_l[p * BH + idx];
-        if (l > 0.f) M = fmaxf(M, c.part_m[p * BH + idx]);
+        float l = c.part_l[p * smp + idx * sm];
+        if (l > 0.f) M = fmaxf(M, c.part_m[p * smp + idx * sm]);
     }
     float num = 0.f, den = 0.f;
     for (int p = 0; p < c.P; ++p) {
-        float l = c.part_l[p * BH + idx];
+        float l = c.part_l[p * smp + idx * sm];
         if (l > 0.f) {
-            float w = l * expf(c.part_m[p * BH + idx] - M);
-            num += c.part_o[(p * BH + idx) * c.D + d] * w;
+            float w = l * expf(c.part_m[p * smp + idx * sm] - M);
+            num += c.part_o[p * sop + idx * so + d] * w;
             den += w;
         }
     }
@@ -198,7 +204,9 @@ template <int FMT, bool ASYM, bool OUTL>
 static const MmaConfig& mma_config() {
     static MmaConfig cfg = [] {
         MmaConfig c;
-        c.nstage = stages_from_env(3);
+        // measured on B200: int8 and the 1 KB-stage int4 variants run best with 2 stages (one more
+        // resident CTA per SM), plain symmetric int4 with 3
+        c.nstage = stages_from_env((FMT == KVQ_FMT_INT4 && !ASYM && !OUTL) ? 3 : 2);
         c.stage_bytes = mma_stage_bytes(FMT, ASYM, OUTL);
         c.dyn_smem = (size_t)kMmaWarps * c.nstage * c.stage_bytes + 1024;
         c.ctas_per_sm = 1;

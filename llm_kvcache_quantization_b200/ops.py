@@ -173,12 +173,15 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
                 k_zp=None, v_zp=None, inv_tau: Optional[torch.Tensor] = None,
                 outlier_idx=None, k_side=None, v_side=None,
                 splits: int = 0, out: Optional[torch.Tensor] = None,
-                return_partial: bool = False, max_ctx: Optional[int] = None, stages: int = 0):
+                return_partial: bool = False, max_ctx: Optional[int] = None, stages: int = 0,
+                packed_partial: Optional[torch.Tensor] = None):
     """Fused q_len==1 attention over a (quantized) cache.  q fp16 [B,Hq,D].
 
     Returns `out` fp16 [B,Hq,D]; with `return_partial` also the normalised
     partial `(o fp32 [B,Hq,D], m fp32 [B,Hq], l fp32 [B,Hq])` used by the
-    sequence-sharded merge.  No host synchronisation happens here.
+    sequence-sharded merge.  `packed_partial` (fp32 [B,Hq,D+2], contiguous) receives the
+    same partial as one buffer `[o (D) | m | l]` per (b, h) - the send buffer of the
+    sequence-sharded all-gather.  No host synchronisation happens here.
     """
     dev = _require_cuda(q, k_payload, v_payload, k_scale, v_scale, context_lens)
     if q.dtype != torch.float16:
@@ -233,6 +236,13 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
             pl = torch.empty((B, Hq), dtype=torch.float32, device=dev)
             a.part_o, a.part_m, a.part_l = po.data_ptr(), pm.data_ptr(), pl.data_ptr()
             part = (po, pm, pl)
+        elif packed_partial is not None:
+            pp = packed_partial
+            if pp.dtype != torch.float32 or not pp.is_contiguous() or tuple(pp.shape) != (B, Hq, D + 2):
+                raise ValueError("packed_partial must be a contiguous fp32 [B, Hq, D+2] tensor")
+            a.part_o, a.part_m, a.part_l = pp.data_ptr(), pp.data_ptr() + 4 * D, pp.data_ptr() + 4 * (D + 1)
+            a.part_o_stride = a.part_ml_stride = D + 2
+            part = (pp[..., :D], pp[..., D], pp[..., D + 1])
         if B > 0 and a.max_ctx > 0:
             rc = lib.kvq_decode_attn(C.byref(a), _stream_ptr(dev))
         else:
@@ -276,6 +286,30 @@ def lse_combine(part_o: torch.Tensor, part_m: torch.Tensor, part_l: torch.Tensor
     c = _lib.KvqCombineArgs()
     c.P, c.B, c.Hq, c.D = P, B, Hq, D
     c.part_o, c.part_m, c.part_l = part_o.data_ptr(), part_m.data_ptr(), part_l.data_ptr()
+    c.out = out.data_ptr()
+    c.out_stride_b, c.out_stride_h = out.stride(0), out.stride(1)
+    with torch.cuda.device(dev):
+        rc = _lib.load().kvq_lse_combine(C.byref(c), _stream_ptr(dev))
+    _lib.check("kvq_lse_combine", rc)
+    return out
+
+
+def lse_combine_packed(packed: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Merge P packed partials (fp32 [P,B,Hq,D+2], rows `[o (D) | m | l]`, e.g. the receive buffer
+    of an all-gather) -> fp16 [B,Hq,D]."""
+    dev = _require_cuda(packed)
+    if packed.dtype != torch.float32 or not packed.is_contiguous() or packed.ndim != 4:
+        raise ValueError("packed partials must be a contiguous fp32 [P, B, Hq, D+2] tensor")
+    P, B, Hq, W = packed.shape
+    D = W - 2
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=torch.float16, device=dev)
+    c = _lib.KvqCombineArgs()
+    c.P, c.B, c.Hq, c.D = P, B, Hq, D
+    base = packed.data_ptr()
+    c.part_o, c.part_m, c.part_l = base, base + 4 * D, base + 4 * (D + 1)
+    c.part_o_stride = c.part_ml_stride = W
+    c.part_o_stride_p = c.part_ml_stride_p = B * Hq * W
     c.out = out.data_ptr()
     c.out_stride_b, c.out_stride_h = out.stride(0), out.stride(1)
     with torch.cuda.device(dev):

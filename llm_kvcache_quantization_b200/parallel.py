@@ -1,0 +1,113 @@
+"""Multi-GPU partitioning of the decode path: one process per GPU.
+
+Two ways the path shards (neither exists in the reference, which is single-GPU):
+
+* batch sharding   - sequences are independent; rank r owns batch rows `batch_shard(B, r, W)`,
+  its own cache and its own decode calls.  No collective on the data path.
+* sequence sharding - one long sequence; rank r owns the contiguous token range
+  `SequenceSharding.token_range(r)`, appends a new token only if it owns that position, runs the
+  fused decode over its chunk into a packed normalised partial `[o | m | l]`, and the partials are
+  merged after ONE all-gather per layer:
+      M = max_r m_r;  out = sum_r o_r l_r e^{m_r - M} / sum_r l_r e^{m_r - M}
+  Remote partials land in this GPU's own receive buffer before the merge kernel reads them.
+
+The collective goes through `torch.distributed` (NCCL on GPUs; gloo for the host-side tests).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+
+def batch_shard(batch: int, rank: int, world: int) -> Tuple[int, int]:
+    """Rows [lo, hi) of a batch owned by `rank`: contiguous, sizes differ by at most one."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world: {rank}/{world}")
+    base, rem = divmod(batch, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+@dataclass(frozen=True)
+class SequenceSharding:
+    """Contiguous token chunks of `chunk` tokens per rank (a multiple of 32 so that every shard
+    starts on a tile boundary of the decode kernel)."""
+    world: int
+    max_seq_len: int
+    align: int = 32
+
+    @property
+    def chunk(self) -> int:
+        per = -(-self.max_seq_len // self.world)
+        return -(-per // self.align) * self.align
+
+    def token_range(self, rank: int) -> Tuple[int, int]:
+        lo = min(self.max_seq_len, rank * self.chunk)
+        return lo, min(self.max_seq_len, lo + self.chunk)
+
+    def owner_of(self, position: int) -> int:
+        if position < 0 or position >= self.max_seq_len:
+            raise ValueError(f"position {position} outside [0, {self.max_seq_len})")
+        return position // self.chunk
+
+    def local_len(self, rank: int, total_len: int) -> int:
+        """How many of the first `total_len` tokens of the sequence live on `rank`."""
+        lo, hi = self.token_range(rank)
+        return max(0, min(total_len, hi) - lo)
+
+
+def gather_partials(packed: torch.Tensor, group=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather the packed partial `[B,Hq,D+2]` of every rank into `[W,B,Hq,D+2]` (one collective).
+    Ranks must agree on the shape; a mismatch is detected here, before the collective, through the
+    sizes exchanged at group set-up (`check_partial_shapes`)."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    if out is None:
+        out = torch.empty((world,) + tuple(packed.shape), dtype=packed.dtype, device=packed.device)
+    elif tuple(out.shape) != (world,) + tuple(packed.shape):
+        raise ValueError(f"receive buffer {tuple(out.shape)} does not match {world} x {tuple(packed.shape)}")
+    if packed.is_cuda:
+        dist.all_gather_into_tensor(out, packed.contiguous(), group=group)      # one NCCL all-gather
+    else:
+        dist.all_gather(list(out.unbind(0)), packed.contiguous(), group=group)  # gloo (host-side tests)
+    return out
+
+
+def check_partial_shapes(shape, group=None) -> None:
+    """Host-side agreement check (run once per configuration, not per step): every rank must use the
+    same [B, Hq, D+2]; raises on all ranks if any differs."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    mine = [int(x) for x in shape]
+    all_shapes = [None] * world
+    dist.all_gather_object(all_shapes, mine, group=group)
+    if any(s != mine for s in all_shapes):
+        raise RuntimeError(f"sequence-sharded ranks disagree on the partial shape: {all_shapes}")
+
+
+def sharded_decode(fmt: int, q: torch.Tensor, tensors: dict, local_len: int, sm_scale: float, *,
+                   send: torch.Tensor, recv: torch.Tensor, inv_tau=None, out=None, group=None) -> torch.Tensor:
+    """One layer of sequence-sharded decode attention on this rank.
+
+    `tensors` is `cache.get_decode_tensors(layer)` of the LOCAL chunk, `local_len` the number of
+    valid local tokens (0 is fine: the rank then contributes the neutral partial), `send` a
+    persistent fp32 `[B,Hq,D+2]` buffer and `recv` a persistent `[W,B,Hq,D+2]` buffer.
+    Returns the merged fp16 `[B,Hq,D]` output (identical on every rank)."""
+    from . import ops
+    k = tensors["k"][:, :, :local_len]
+    v = tensors["v"][:, :, :local_len]
+    ks = tensors["ks"][:, :, :local_len]
+    vs = tensors["vs"][:, :, :local_len]
+    extra = {}
+    if tensors.get("kz") is not None:
+        extra.update(k_zp=tensors["kz"][:, :, :local_len], v_zp=tensors["vz"][:, :, :local_len])
+    if tensors.get("outlier_idx") is not None:
+        extra.update(outlier_idx=tensors["outlier_idx"].contiguous(), k_side=tensors["kside"][:, :, :local_len],
+                     v_side=tensors["vside"][:, :, :local_len])
+    scratch = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=torch.float16, device=q.device) if out is None else out
+    ops.decode_attn(fmt, q, k, v, ks, vs, None, sm_scale, head_dim=q.shape[-1], inv_tau=inv_tau,
+                    out=scratch, packed_partial=send, **extra)
+    gather_partials(send, group=group, out=recv)
+    return ops.lse_combine_packed(recv, out=scratch)
