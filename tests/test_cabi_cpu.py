@@ -54,7 +54,7 @@ def test_null_args_are_rejected_without_launch(lib):
 def test_struct_sizes_match_header(lib):
     # all fields are 4- or 8-byte scalars/pointers: natural alignment, no packing pragma
     assert ctypes.sizeof(_lib.KvqCacheSide) == 13 * 8
-    assert ctypes.sizeof(_lib.KvqCombineArgs) == 4 * 4 + 6 * 8
+    assert ctypes.sizeof(_lib.KvqCombineArgs) == 4 * 4 + 10 * 8
 
 
 def test_cpu_tensors_raise_value_error():
