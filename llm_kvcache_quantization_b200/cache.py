@@ -236,6 +236,17 @@ class FP16KVCache(_CacheBase):
     def get_fp16_tensors(self, layer_id: int) -> Tuple[Tensor, Tensor]:
         return self._layer_view(layer_id, ("k", "v"))
 
+    def fused_decode(self, layer_id: int, q: Tensor, sm_scale: float, inv_tau: Optional[Tensor] = None,
+                     out: Optional[Tensor] = None) -> Tensor:
+        """q_len==1 attention over the cached fp16 K/V of this layer through the split-K kernel."""
+        k, v = self.get_fp16_tensors(layer_id)
+        original = q.dtype
+        if original != torch.float16:
+            q = q.to(torch.float16)
+        res = ops.decode_attn(FMT_FP16, q, k, v, None, None, None, float(sm_scale), head_dim=q.shape[-1],
+                              inv_tau=None if inv_tau is None else inv_tau.float(), out=out)
+        return res if original == torch.float16 else res.to(original)
+
     @classmethod
     def from_tuple(cls, past_key_values, device="cuda") -> "FP16KVCache":
         cache = cls(num_layers=len(past_key_values), device=device)
@@ -417,6 +428,26 @@ class _QuantCache(_CacheBase):
         vals = dict(zip(names, self._layer_view(layer_id, names)))
         vals["outlier_idx"] = None if self.outlier_idx is None else self.outlier_idx[layer_id]
         return vals
+
+    def fused_decode(self, layer_id: int, q: Tensor, sm_scale: float, inv_tau: Optional[Tensor] = None,
+                     out: Optional[Tensor] = None) -> Tensor:
+        """q_len==1 attention of `q` [B,Hq,D] over everything cached for this layer, in one fused
+        call (format, zero-points, outlier side buffer and per-head `inv_tau` handled by the
+        kernel).  All rows attend over the layer's full length (no host sync, no length tensor)."""
+        t = self.get_decode_tensors(layer_id)
+        original = q.dtype
+        if original != torch.float16:
+            q = q.to(torch.float16)
+        extra = {}
+        if self.asymmetric:
+            extra.update(k_zp=t["kz"], v_zp=t["vz"])
+        if self.outlier_idx is not None:
+            extra.update(outlier_idx=t["outlier_idx"].to(q.device).contiguous(), k_side=t["kside"], v_side=t["vside"])
+        if inv_tau is not None and inv_tau.dtype != torch.float32:
+            inv_tau = inv_tau.float()
+        res = ops.decode_attn(self._fmt, q, t["k"], t["v"], t["ks"], t["vs"], None, float(sm_scale),
+                              head_dim=q.shape[-1], inv_tau=inv_tau, out=out, **extra)
+        return res if original == torch.float16 else res.to(original)
 
     def release(self) -> None:
         super().release()
