@@ -160,6 +160,31 @@ typedef struct KvqAttnArgs {
  */
 KVQ_API int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream);
 
+/*
+ * kvq_decode_attn for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: its Triton wrapper allocates freely through torch.)
+ *
+ * Who needs it: a host that has handed all of HBM to its own pool and must not call cudaMalloc
+ * any more, or one that calls this library from a place where no allocator may run.  Such a
+ * caller has nowhere to get the split-K scratch buffer from, so this variant keeps the partials
+ * in a fixed KVQ_STATIC_WORKSPACE_BYTES array that is part of the library image (every GPU that
+ * loads the library holds that much until the process exits).
+ *
+ * Same arguments and result as kvq_decode_attn; `workspace` / `workspace_bytes` are ignored.
+ * It calls no cudaMalloc, cudaFree or other allocating routine.
+ *  - Limit: B * Hq * splits * (D + 2) * 4 bytes must fit the array.  With `splits == 0` the
+ *    library lowers its own split choice until it fits; if even one split does not fit, or an
+ *    explicit `splits` is too large, the call returns KVQ_ELIMIT and launches nothing.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current) and caches it; make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's partials.
+ *    Nothing in it has to start at zero (every slot a call reads it has written first), but two
+ *    calls that overlap on the GPU - different streams, or graphs replayed concurrently - race
+ *    on it.  Serialise them on one stream.
+ */
+#define KVQ_STATIC_WORKSPACE_BYTES (8u << 20)
+KVQ_API int kvq_decode_attn_static(const KvqAttnArgs* args, kvq_stream_t stream);
+
 /* Host-side query, no launch: 1 if kvq_decode_attn would take the tensor-core TMA kernel for these
  * arguments (head_dim 128, group 32, int8 / packed int4, 16-byte aligned rows), 0 for the generic kernel. */
 KVQ_API int kvq_decode_kernel_kind(const KvqAttnArgs* args);

@@ -85,6 +85,7 @@ class KvqCombineArgs(C.Structure):
 EXPORTS = (
     ("kvq_quantize_append", C.c_int, (C.POINTER(KvqAppendArgs), _vp)),
     ("kvq_decode_attn", C.c_int, (C.POINTER(KvqAttnArgs), _vp)),
+    ("kvq_decode_attn_static", C.c_int, (C.POINTER(KvqAttnArgs), _vp)),
     ("kvq_decode_workspace_bytes", C.c_size_t, (_i32, _i32, _i32, _i32)),
     ("kvq_decode_pick_splits", _i32, (C.POINTER(KvqAttnArgs),)),
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),

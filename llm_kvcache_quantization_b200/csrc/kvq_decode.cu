@@ -391,6 +391,63 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     return rc;
 }
 
+// ---------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to obtain scratch memory at call time: a
+// serving runtime that has already handed every byte of HBM to its own pool and
+// forbids cudaMalloc afterwards, or a plugin called from inside a region where the
+// allocator must not run.  For them the split-K partials live in a fixed array inside
+// the library image instead of a caller-provided workspace.
+//
+// The array is a file-scope __device__ object: every GPU that loads the library keeps
+// its own copy (KVQ_STATIC_WS_BYTES) until the process exits.  In host code the name
+// `g_static_workspace` is only a handle for the runtime, not a device address, so the
+// address is resolved with cudaGetSymbolAddress, once per device, with that device
+// current, and cached.
+// ---------------------------------------------------------------------------
+#define KVQ_STATIC_WS_BYTES KVQ_STATIC_WORKSPACE_BYTES
+static __device__ __align__(256) unsigned char g_static_workspace[KVQ_STATIC_WS_BYTES];
+
+static int static_workspace_ptr(void** out) {
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    int rc = kvq::check_cuda(cudaGetDevice(&dev));
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return KVQ_EUNSUPPORTED;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        rc = kvq::check_cuda(cudaGetSymbolAddress(&p, g_static_workspace));
+        if (rc) return rc;
+        if (!p) return KVQ_ECUDA;
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return KVQ_OK;
+}
+
+extern "C" int kvq_decode_attn_static(const KvqAttnArgs* args, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!args) return KVQ_EINVAL;
+    KvqAttnArgs a = *args;
+    if (a.B == 0) return KVQ_OK;
+    if (a.B < 0 || a.Hq <= 0 || a.D <= 0) return KVQ_EINVAL;
+    if (a.splits <= 0) {
+        a.splits = kvq_decode_pick_splits(&a);
+        // prefer fewer splits over refusing: shrink until the partials fit the fixed array
+        while (a.splits > 1 && kvq_decode_workspace_bytes(a.B, a.Hq, a.D, a.splits) > KVQ_STATIC_WS_BYTES) --a.splits;
+    }
+    const size_t need = kvq_decode_workspace_bytes(a.B, a.Hq, a.D, a.splits);
+    if (need == 0) return KVQ_EINVAL;
+    if (need > KVQ_STATIC_WS_BYTES) return KVQ_ELIMIT;       // B * Hq * splits * (D + 2) * 4 bytes > 8 MiB
+    void* ws = nullptr;
+    int rc = static_workspace_ptr(&ws);
+    if (rc) return rc;
+    a.workspace = ws;
+    a.workspace_bytes = KVQ_STATIC_WS_BYTES;
+    return kvq_decode_attn(&a, stream);
+}
+
 extern "C" int kvq_debug_error_flag(int reset) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, kvq::g_kvq_error_flag, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;

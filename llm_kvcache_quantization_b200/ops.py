@@ -316,3 +316,50 @@ def lse_combine_packed(packed: torch.Tensor, out: Optional[torch.Tensor] = None)
         rc = _lib.load().kvq_lse_combine(C.byref(c), _stream_ptr(dev))
     _lib.check("kvq_lse_combine", rc)
     return out
+
+
+def decode_attn_static(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: torch.Tensor,
+                       k_scale: Optional[torch.Tensor], v_scale: Optional[torch.Tensor],
+                       context_lens: Optional[torch.Tensor], sm_scale: float, out: torch.Tensor, *,
+                       k_zp=None, v_zp=None, inv_tau: Optional[torch.Tensor] = None,
+                       outlier_idx=None, k_side=None, v_side=None, splits: int = 0) -> torch.Tensor:
+    """Fused decode attention through `kvq_decode_attn_static`, the entry point for hosts that are
+    not allowed to allocate GPU memory at call time (for instance a serving process whose memory
+    pool already owns all of HBM).  The split-K partials go to an 8 MiB array inside the library
+    instead of a torch-allocated workspace, and this wrapper allocates nothing either: the caller
+    passes `out` (fp16 [B,Hq,D]).
+
+    Raises `KvqError` with code `KVQ_ELIMIT` when B*Hq*splits*(D+2)*4 bytes exceed the array.
+    Calls on one device share that array: keep them on one stream (overlapping calls race).
+    The first call per device resolves the array's address; do it before capturing a CUDA graph.
+    """
+    dev = _require_cuda(q, k_payload, v_payload, k_scale, v_scale, context_lens, out)
+    if q.dtype != torch.float16 or out.dtype != torch.float16:
+        raise ValueError("decode_attn_static expects fp16 q and out")
+    if q.stride(-1) != 1 or out.stride(-1) != 1:
+        raise ValueError("q and out must be contiguous in head_dim")
+    B, Hq, D = q.shape
+    a = _lib.KvqAttnArgs()
+    a.format = fmt
+    a.B, a.Hq, a.Hkv, a.D = B, Hq, k_payload.shape[1], D
+    a.group_size = D // (1 if k_scale is None else k_scale.shape[-1])
+    a.max_ctx = k_payload.shape[2]
+    a.q, a.q_stride_b, a.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    if inv_tau is not None:
+        a.inv_tau = inv_tau.data_ptr()
+    a.sm_scale = float(sm_scale)
+    a.k = _cache_side(k_payload, k_scale, k_zp, k_side)
+    a.v = _cache_side(v_payload, v_scale, v_zp, v_side)
+    if outlier_idx is not None:
+        a.n_out = outlier_idx.shape[1]
+        a.outlier_idx = outlier_idx.data_ptr()
+    if context_lens is not None:
+        if context_lens.dtype != torch.int32 or not context_lens.is_contiguous():
+            raise ValueError("context_lens must be a contiguous int32 tensor (no conversion is done here)")
+        a.context_lens = context_lens.data_ptr()
+    a.splits = int(splits)
+    a.out, a.out_stride_b, a.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    with torch.cuda.device(dev):
+        rc = _lib.load().kvq_decode_attn_static(C.byref(a), _stream_ptr(dev))
+    _lib.check("kvq_decode_attn_static", rc)
+    return out
