@@ -407,43 +407,24 @@ def main():
                 "us_per_launch": split_us, "algorithmic_bytes_per_launch": alg_bytes,
                 "frac_of_8TBps": achieved / 8000.0}
 
-    # end to end through the public API with host buffers
+    # end to end through the public API with HOST buffers: every step uploads this token's q / k / v
+    # for all layers from pinned memory, replays the captured whole-stack step (append + attention per
+    # layer, device-side position counter, the cache grows by one token) and downloads the outputs
     e2e = None
     if not args.no_e2e:
-        os.environ["KVQ_SKIP_CONTEXT_CHECK"] = "1"
-        hq = q.cpu().pin_memory(); hk = k_new.cpu().pin_memory(); hv = v_new.cpu().pin_memory()
-        hout = torch.empty(L, B, Hq, D, dtype=torch.float16).pin_memory()
-        kind = wl["kind"]
-
-        def e2e_step():
-            for l in range(L):
-                dq = hq[l].to(dev, non_blocking=True)
-                dk = hk[l].to(dev, non_blocking=True)
-                dv = hv[l].to(dev, non_blocking=True)
-                cache.append(l, dk, dv)
-                t = cache.get_decode_tensors(l)
-                n = t["k"].shape[2]
-                ctx = torch.full((B,), n, dtype=torch.int32, device=dev)
-                tau = inv_tau[l]
-                if kind == "int4_asym":
-                    o = kvq.decode_attn_int4_asym(dq, t["k"], t["v"], t["ks"], t["kz"], t["vs"], t["vz"], ctx, inv_tau=tau)
-                elif kind == "int4_outlier":
-                    o = kvq.decode_attn_int4_outlier(dq, t["k"], t["v"], t["ks"], t["vs"], t["kside"], t["vside"],
-                                                     t["outlier_idx"].contiguous(), ctx, inv_tau=tau)
-                else:
-                    o = kvq.decode_attn_int8(dq, t["k"], t["v"], t["ks"], t["vs"], ctx, inv_tau=tau)
-                hout[l].copy_(o, non_blocking=True)
-            torch.cuda.synchronize()
-
+        from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
+        stepper = GraphedKVStackStep(cache, Hq, 1.0 / D ** 0.5, inv_tau=inv_tau)
+        stepper.capture()
+        stepper.host_q.copy_(q.cpu()); stepper.host_k.copy_(k_new.cpu()); stepper.host_v.copy_(v_new.cpu())
         for _ in range(3):
-            e2e_step()
+            stepper.step(stepper.host_q, stepper.host_k, stepper.host_v)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
         e0.record()
         for _ in range(args.steps):
-            e2e_step()
+            res = stepper.step(stepper.host_q, stepper.host_k, stepper.host_v)
         e1.record()
         torch.cuda.synchronize()
         ems = e0.elapsed_time(e1)
@@ -451,11 +432,12 @@ def main():
             t = torch.tensor([ems], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ems = float(t[0])
-        h2d = L * (B * Hq * D + 2 * B * Hkv * D) * 2
-        d2h = L * B * Hq * D * 2
-        e2e = {"value": world * B / (ems / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": ems / args.steps,
-               "api": "cache.append + decode_attn_* per layer, eager (no CUDA graph), pinned host q/k/v in, out to host"}
+        assert bool(torch.isfinite(res.float()).all())
+        e2e = {"value": world * B / (ems / args.steps * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": stepper.h2d_bytes_per_step, "d2h_bytes_per_step": stepper.d2h_bytes_per_step,
+               "ms_per_step": ems / args.steps,
+               "api": "GraphedKVStackStep.step(host_q, host_k, host_v) -> host_out: pinned H2D of q/k/v, one CUDA "
+                      "graph (append + attention for every layer), pinned D2H of the outputs, stream sync"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -134,6 +134,10 @@ typedef struct KvqAttnArgs {
     int32_t splits;           /* KV splits per (batch, kv head); 0 = library heuristic    */
     int32_t stages;           /* 0 = split kernel + combine; 1 = split kernel only; 2 = combine only
                                  (for profiling one stage; the workspace carries the partials) */
+    int32_t exact_dequant;    /* packed INT4 on the tensor-core kernel: 0 = scales applied outside the integer
+                                 products (fast; differs from the reference's fp16-rounded code*scale by
+                                 <= 2^-11 relative per element), 1 = bit-faithful RN16(code*scale) per element.
+                                 INT8 and the generic kernel are always bit-faithful.                   */
     void*   workspace;        /* >= kvq_decode_workspace_bytes(...)                       */
     size_t  workspace_bytes;
     void*   out;              /* fp16 [B, Hq, D] or NULL                                  */

@@ -15,37 +15,88 @@ namespace kvq {
 // ---------------------------------------------------------------------------
 // In-GPU combine over KV splits: unnormalised partials (o, m, l) -> fp16 output
 // and, optionally, a normalised partial (o/l, m in natural-log units, l) for a
-// cross-GPU merge.  grid = (Hq, B), block = D threads.
+// cross-GPU merge.  grid = (Hq, B), block = 4 warps.  Every warp first finds the
+// global max over all splits (lane s reads split s), then warp w sums the splits
+// w, w+4, ... with four independent loads in flight per lane (a lane owns D/32
+// channels), and the four warps are added through shared memory.  The loop over
+// splits is latency-bound when run serially; this form keeps it near one round trip.
 // ---------------------------------------------------------------------------
-__global__ void combine_splits_kernel(const AttnParams p) {
+template <int EPL>   // channels per lane = D / 32
+__global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p) {
     const KvqAttnArgs& a = p.a;
-    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-    const int D = a.D;
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int D = EPL * 32;
     const long long row0 = ((long long)b * a.Hq + h) * p.splits;
+    const float2* ml = reinterpret_cast<const float2*>(p.ws_ml) + row0;
     float M = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.ws_ml[(row0 + s) * 2]);
-    float o = 0.f, L = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-        float ms = p.ws_ml[(row0 + s) * 2];
-        float ls = p.ws_ml[(row0 + s) * 2 + 1];
-        if (ls > 0.f) {
-            float w = exp2f(ms - M);
-            o += p.ws_o[(row0 + s) * D + d] * w;
-            L += ls * w;
+    for (int s = lane; s < p.splits; s += 32) {
+        const float2 v = ml[s];
+        if (v.y > 0.f) M = fmaxf(M, v.x);
+    }
+    M = warp_max(M);
+    float acc[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
+    float L = 0.f;
+    const float* o_base = p.ws_o + row0 * D + lane * EPL;
+    for (int s0 = warp; s0 < p.splits; s0 += 16) {
+        float2 mv[4];
+        float ov[4][EPL];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int s = s0 + 4 * u;
+            mv[u] = s < p.splits ? ml[s] : make_float2(-INFINITY, 0.f);
+            if (s < p.splits) {
+                if (EPL == 4) *reinterpret_cast<float4*>(ov[u]) = *reinterpret_cast<const float4*>(o_base + (long long)s * D);
+                else {
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) ov[u][e] = o_base[(long long)s * D + e];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (mv[u].y > 0.f) {
+                const float w = exp2f(mv[u].x - M);
+                L += mv[u].y * w;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[e] += ov[u][e] * w;
+            }
         }
     }
-    float r = (L > 0.f) ? o / L : 0.f;
-    if (a.out) ((__half*)a.out)[b * a.out_stride_b + h * a.out_stride_h + d] = __float2half_rn(r);
-    if (a.part_o) {
-        const long long idx = (long long)b * a.Hq + h;
-        const long long so = a.part_o_stride ? a.part_o_stride : D;
-        const long long sm = a.part_ml_stride ? a.part_ml_stride : 1;
-        a.part_o[idx * so + d] = r;
-        if (d == 0) {
-            a.part_m[idx * sm] = (L > 0.f) ? M * 0.6931471805599453f : -INFINITY;
-            a.part_l[idx * sm] = L;
+    __shared__ float red[4][D + 1];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) red[warp][lane * EPL + e] = acc[e];
+    if (lane == 0) red[warp][D] = L;
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += 128) {
+        const float o = red[0][d] + red[1][d] + red[2][d] + red[3][d];
+        const float Lt = red[0][D] + red[1][D] + red[2][D] + red[3][D];
+        const float r = (Lt > 0.f) ? o / Lt : 0.f;
+        if (a.out) ((__half*)a.out)[b * a.out_stride_b + h * a.out_stride_h + d] = __float2half_rn(r);
+        if (a.part_o) {
+            const long long idx = (long long)b * a.Hq + h;
+            const long long so = a.part_o_stride ? a.part_o_stride : D;
+            const long long sm = a.part_ml_stride ? a.part_ml_stride : 1;
+            a.part_o[idx * so + d] = r;
+            if (d == 0) {
+                a.part_m[idx * sm] = (Lt > 0.f) ? M * 0.6931471805599453f : -INFINITY;
+                a.part_l[idx * sm] = Lt;
+            }
         }
     }
+}
+
+static int launch_combine(const AttnParams& p, cudaStream_t st) {
+    dim3 grid(p.a.Hq, p.a.B);
+    switch (p.a.D) {
+        case 64: combine_splits_kernel<2><<<grid, 128, 0, st>>>(p); break;
+        case 128: combine_splits_kernel<4><<<grid, 128, 0, st>>>(p); break;
+        case 256: combine_splits_kernel<8><<<grid, 128, 0, st>>>(p); break;
+        default: return KVQ_EUNSUPPORTED;
+    }
+    return check_launch();
 }
 
 // Merge of P normalised partials (one per sequence shard).  grid = (Hq, B).
@@ -200,22 +251,23 @@ static int stages_from_env(int dflt) {
     return (v >= 2 && v <= 8) ? v : dflt;
 }
 
-template <int FMT, bool ASYM, bool OUTL>
+template <int FMT, bool ASYM, bool OUTL, bool FAST>
 static const MmaConfig& mma_config() {
     static MmaConfig cfg = [] {
         MmaConfig c;
         // measured on B200: int8 and the 1 KB-stage int4 variants run best with 2 stages (one more
         // resident CTA per SM), plain symmetric int4 with 3
         c.nstage = stages_from_env((FMT == KVQ_FMT_INT4 && !ASYM && !OUTL) ? 3 : 2);
+        (void)FAST;
         c.stage_bytes = mma_stage_bytes(FMT, ASYM, OUTL);
         c.dyn_smem = (size_t)kMmaWarps * c.nstage * c.stage_bytes + 1024;
         c.ctas_per_sm = 1;
-        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM, OUTL>,
+        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.dyn_smem));
         if (c.rc == KVQ_OK) {
             int n = 0;
             c.rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-                &n, decode_split_mma_kernel<FMT, ASYM, OUTL>, kMmaWarps * 32, c.dyn_smem));
+                &n, decode_split_mma_kernel<FMT, ASYM, OUTL, FAST>, kMmaWarps * 32, c.dyn_smem));
             if (n > 0) c.ctas_per_sm = n;
         }
         return c;
@@ -223,18 +275,25 @@ static const MmaConfig& mma_config() {
     return cfg;
 }
 
+// INT4 takes the factored-scale kernel unless the caller asks for bit-faithful dequantisation
+static bool use_fast(const AttnParams& p) { return p.a.format == KVQ_FMT_INT4 && !p.a.exact_dequant; }
+
 static const MmaConfig* mma_config_for(const AttnParams& p, bool asym) {
     const bool outl = p.a.n_out > 0;
     if (p.a.format == KVQ_FMT_INT8)
-        return outl ? &mma_config<KVQ_FMT_INT8, false, true>() : &mma_config<KVQ_FMT_INT8, false, false>();
-    if (asym) return &mma_config<KVQ_FMT_INT4, true, false>();
-    return outl ? &mma_config<KVQ_FMT_INT4, false, true>() : &mma_config<KVQ_FMT_INT4, false, false>();
+        return outl ? &mma_config<KVQ_FMT_INT8, false, true, false>() : &mma_config<KVQ_FMT_INT8, false, false, false>();
+    if (use_fast(p)) {
+        if (asym) return &mma_config<KVQ_FMT_INT4, true, false, true>();
+        return outl ? &mma_config<KVQ_FMT_INT4, false, true, true>() : &mma_config<KVQ_FMT_INT4, false, false, true>();
+    }
+    if (asym) return &mma_config<KVQ_FMT_INT4, true, false, false>();
+    return outl ? &mma_config<KVQ_FMT_INT4, false, true, false>() : &mma_config<KVQ_FMT_INT4, false, false, false>();
 }
 
-template <int FMT, bool ASYM, bool OUTL>
+template <int FMT, bool ASYM, bool OUTL, bool FAST>
 static int launch_mma(const AttnParams& p, cudaStream_t st) {
     constexpr int RB = FMT == KVQ_FMT_INT8 ? 128 : 64;
-    const MmaConfig& cfg = mma_config<FMT, ASYM, OUTL>();
+    const MmaConfig& cfg = mma_config<FMT, ASYM, OUTL, FAST>();
     if (cfg.rc) return cfg.rc;
     MmaParams mp;
     mp.p = p;
@@ -248,16 +307,20 @@ static int launch_mma(const AttnParams& p, cudaStream_t st) {
     rc = make_payload_map(&vmap, p.a.v, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;
     dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
-    decode_split_mma_kernel<FMT, ASYM, OUTL><<<grid, kMmaWarps * 32, cfg.dyn_smem, st>>>(mp, kmap, vmap);
+    decode_split_mma_kernel<FMT, ASYM, OUTL, FAST><<<grid, kMmaWarps * 32, cfg.dyn_smem, st>>>(mp, kmap, vmap);
     return check_launch();
 }
 
 static int dispatch_mma(const AttnParams& p, bool asym, cudaStream_t st) {
     const bool outl = p.a.n_out > 0;
     if (p.a.format == KVQ_FMT_INT8)
-        return outl ? launch_mma<KVQ_FMT_INT8, false, true>(p, st) : launch_mma<KVQ_FMT_INT8, false, false>(p, st);
-    if (asym) return launch_mma<KVQ_FMT_INT4, true, false>(p, st);
-    return outl ? launch_mma<KVQ_FMT_INT4, false, true>(p, st) : launch_mma<KVQ_FMT_INT4, false, false>(p, st);
+        return outl ? launch_mma<KVQ_FMT_INT8, false, true, false>(p, st) : launch_mma<KVQ_FMT_INT8, false, false, false>(p, st);
+    if (use_fast(p)) {
+        if (asym) return launch_mma<KVQ_FMT_INT4, true, false, true>(p, st);
+        return outl ? launch_mma<KVQ_FMT_INT4, false, true, true>(p, st) : launch_mma<KVQ_FMT_INT4, false, false, true>(p, st);
+    }
+    if (asym) return launch_mma<KVQ_FMT_INT4, true, false, false>(p, st);
+    return outl ? launch_mma<KVQ_FMT_INT4, false, true, false>(p, st) : launch_mma<KVQ_FMT_INT4, false, false, false>(p, st);
 }
 
 // ---------------------------------------------------------------------------
@@ -271,19 +334,20 @@ static int pick_splits_waves(long long rows, int max_ctx, int slots, int min_tok
     long long by_len = max_ctx / min_tokens;
     if (by_len < 1) by_len = 1;
     if (by_len > 256) by_len = 256;
-    if (rows >= 4LL * slots) return 1;            // many waves already: the tail is a small fraction
+    if (rows >= 8LL * slots) return 1;            // many waves already: the tail is a small fraction
+    // Cost of a launch in "token times": waves x (tokens of the busiest warp's share + a fixed
+    // per-CTA cost for prologue, first-copy latency and the 4-warp merge, about one 128-token slice).
+    const int quantum = kMmaWarps * kTS, fixed = quantum;
     int best = 1;
-    double best_score = -1.0;
+    double best_cost = 1e30;
     for (int s = 1; s <= by_len; ++s) {
         const long long ctas = rows * s;
         const long long waves = (ctas + slots - 1) / slots;
-        if (waves > 4 && s > 1) break;
-        // tokens are scanned in units of 32 per warp-stage: quantisation of the per-split length
-        const int per = ((max_ctx + s - 1) / s + kTS - 1) / kTS * kTS;
-        const double useful = (double)max_ctx / ((double)per * s);
-        const double score = (double)ctas / (double)(waves * slots) * useful;
-        if (score > best_score + 0.02) {
-            best_score = score;
+        if (waves > 8 && s > 1) break;
+        const int per = ((max_ctx + s - 1) / s + quantum - 1) / quantum * quantum;
+        const double cost = (double)waves * (per + fixed);
+        if (cost < best_cost * 0.98) {
+            best_cost = cost;
             best = s;
         }
     }
@@ -385,8 +449,7 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
         if (rc) return rc;
     }
     if (a.stages != 1) {
-        combine_splits_kernel<<<dim3(a.Hq, a.B), a.D, 0, st>>>(p);
-        rc = check_launch();
+        rc = launch_combine(p, st);
     }
     return rc;
 }

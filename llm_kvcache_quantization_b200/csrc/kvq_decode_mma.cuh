@@ -101,6 +101,13 @@ __device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void lds128(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+__device__ __forceinline__ void lds64(uint32_t addr, uint32_t (&r)[2]) {
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -177,14 +184,24 @@ __device__ __forceinline__ uint32_t apply_scale(uint32_t c, uint32_t s2, uint32_
 //   [0, TS*RB)            K payload tile   (TMA, swizzled)
 //   [TS*RB, 2*TS*RB)      V payload tile   (TMA, swizzled)
 //   then K scales [TS][4] fp16, V scales, (K zero-points, V zero-points)   256 B each
-template <int FMT, bool ASYM, bool OUTL>
-__global__ void __launch_bounds__(kMmaWarps * 32)
+//
+// FAST (packed INT4 only) applies the scales OUTSIDE the integer products instead of per element:
+//   q.K   one fp32 accumulator per quantisation group (2 mma each over exact integer codes), then
+//         logit = sum_g s[token][g] * S_g  (+ z[token][g] * sum_{d in g} q_d with zero-points);
+//   P.V   the scale of (token, group) is folded into P before the product, P'_g = RN16(P * s_g)
+//         (+ sum_token z[token][g] * p with zero-points, added to every channel of the group).
+// This removes 3 of every 4 fp16 instructions of the dequantisation; products of integer codes are
+// exact, so the result differs from the bit-faithful path only by the reference's own fp16 rounding
+// of code * scale (<= 2^-11 relative per element).  FAST = false keeps the bit-faithful path.
+template <int FMT, bool ASYM, bool OUTL, bool FAST>
+__global__ void __launch_bounds__(kMmaWarps * 32, (FAST && !OUTL) ? 4 : 1)
 decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
     constexpr int RB = (FMT == KVQ_FMT_INT8) ? 128 : 64;      // payload bytes per token row
     constexpr int D = 128;
     constexpr int STAGE_BYTES = mma_stage_bytes(FMT, ASYM, OUTL);
     static_assert(!(ASYM && OUTL), "outlier side buffer is defined for symmetric formats");
+    static_assert(!FAST || FMT == KVQ_FMT_INT4, "the factored-scale path exists for packed INT4");
     const AttnParams& p = mp.p;
     const KvqAttnArgs& a = p.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -219,20 +236,39 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     // ---- Q fragments: thread (g = head, t) holds q[head g][32t .. 32t+32) in the channel
     // order of the K fragments (INT8: natural; INT4: nibble order d1,d5 | d0,d4 | d3,d7 | d2,d6).
     uint32_t qf[16];
+    // FAST with zero-points: qs[e][G] = sum over the channels of group G of q[head 2t+e] (fp32);
+    // oz[G][e] = zero-point part of the output of that head, shared by every channel of the group
+    float qs[2][4], oz[4][2];
+#pragma unroll
+    for (int G = 0; G < 4; ++G) { qs[0][G] = qs[1][G] = 0.f; oz[G][0] = oz[G][1] = 0.f; }
     {
         const bool hv = g < nh;
-        const __half* qp = (const __half*)a.q + (long long)b * a.q_stride_b + (long long)(h0 + (hv ? g : 0)) * a.q_stride_h + 32 * t;
+        const __half* qp = (const __half*)a.q + (long long)b * a.q_stride_b + (long long)(h0 + (hv ? g : 0)) * a.q_stride_h +
+                           (FAST ? 8 * t : 32 * t);
         __half qv[32];
         const __half tau = (a.inv_tau && hv) ? __float2half_rn(a.inv_tau[h0 + g]) : __float2half(1.0f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            uint4 v = *(const uint4*)(qp + 8 * i);
+            // FAST: channels 32 i + 8 t .. + 7 (8 channels of every group); else 32 t + 8 i .. + 7
+            uint4 v = *(const uint4*)(qp + (FAST ? 32 : 8) * i);
             *(uint4*)(qv + 8 * i) = v;
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             qv[i] = hv ? qv[i] : __float2half(0.f);
             if (a.inv_tau) qv[i] = __hmul(qv[i], tau);
+        }
+        if (FAST && ASYM) {
+#pragma unroll
+            for (int G = 0; G < 4; ++G) {
+                float acc = 0.f;                                // this thread: 8 channels of group G of head g
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc += __half2float(qv[8 * G + i]);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);    // every lane of the quad: whole group of head g
+                qs[0][G] = __shfl_sync(0xffffffffu, acc, 4 * (2 * t));
+                qs[1][G] = __shfl_sync(0xffffffffu, acc, 4 * (2 * t + 1));
+            }
         }
         if (FMT == KVQ_FMT_INT8) {
 #pragma unroll
@@ -330,6 +366,17 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         cp_async_mbar_arrive(bar);
     };
 
+    // byte offsets (inside a 64-byte-row tile) of this lane's ldmatrix row for sub-tile `sub`, group pair `gp`:
+    // matrix (lane>>3): bit 0 = token half, bit 1 = second 16-byte chunk (= group) of the pair
+    uint32_t ldsm_off[2][2];
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub)
+#pragma unroll
+        for (int gp = 0; gp < 2; ++gp) {
+            const int lrow = 16 * sub + ((lane >> 3) & 1) * 8 + (lane & 7);
+            ldsm_off[sub][gp] = lrow * 64 + (((2 * gp + (lane >> 4)) ^ ((lrow >> 1) & 3)) << 4);
+        }
+
     bool failed = false;
     const int prolog = min(nstage - 1, n_my);
     for (int k = 0; k < prolog; ++k) issue(k);
@@ -357,8 +404,54 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 
         // ================= q.K : logits for 2 sub-tiles of 16 tokens =================
         float sacc[2][4];
+        if (FAST) {
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
+            for (int sub = 0; sub < 2; ++sub) {
+                float sg[4][4];                                  // per-group integer dot products
+#pragma unroll
+                for (int G = 0; G < 4; ++G)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sg[G][j] = 0.f;
+#pragma unroll
+                for (int gp = 0; gp < 2; ++gp) {
+                    uint32_t r[4];                               // rows g | g+8 of group 2gp, then of group 2gp+1
+                    ldmatrix_x4(kb + ldsm_off[sub][gp], r);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int G = 2 * gp + e;
+                        const uint32_t w0 = r[2 * e], w1 = r[2 * e + 1];
+                        mma16816(sg[G], nib_lo_to_h2(w0), nib_lo_to_h2(w1), nib_hi_to_h2(w0), nib_hi_to_h2(w1),
+                                 qf[4 * G], qf[4 * G + 1]);
+                        const uint32_t x0 = w0 >> 8, x1 = w1 >> 8;
+                        mma16816(sg[G], nib_lo_to_h2(x0), nib_lo_to_h2(x1), nib_hi_to_h2(x0), nib_hi_to_h2(x1),
+                                 qf[4 * G + 2], qf[4 * G + 3]);
+                    }
+                }
+                const int r0 = 16 * sub + g, r1 = r0 + 8;
+                uint32_t sa[2], sb2[2];
+                lds64(ksb + r0 * 8, sa);
+                lds64(ksb + r1 * 8, sb2);
+                const float2 a01 = __half22float2(u32_as_h2(sa[0])), a23 = __half22float2(u32_as_h2(sa[1]));
+                const float2 b01 = __half22float2(u32_as_h2(sb2[0])), b23 = __half22float2(u32_as_h2(sb2[1]));
+                sacc[sub][0] = fmaf(a01.x, sg[0][0], fmaf(a01.y, sg[1][0], fmaf(a23.x, sg[2][0], a23.y * sg[3][0])));
+                sacc[sub][1] = fmaf(a01.x, sg[0][1], fmaf(a01.y, sg[1][1], fmaf(a23.x, sg[2][1], a23.y * sg[3][1])));
+                sacc[sub][2] = fmaf(b01.x, sg[0][2], fmaf(b01.y, sg[1][2], fmaf(b23.x, sg[2][2], b23.y * sg[3][2])));
+                sacc[sub][3] = fmaf(b01.x, sg[0][3], fmaf(b01.y, sg[1][3], fmaf(b23.x, sg[2][3], b23.y * sg[3][3])));
+                if (ASYM) {
+                    lds64(kzb + r0 * 8, sa);
+                    lds64(kzb + r1 * 8, sb2);
+                    const float2 y01 = __half22float2(u32_as_h2(sa[0])), y23 = __half22float2(u32_as_h2(sa[1]));
+                    const float2 z01 = __half22float2(u32_as_h2(sb2[0])), z23 = __half22float2(u32_as_h2(sb2[1]));
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        sacc[sub][e] += fmaf(y01.x, qs[e][0], fmaf(y01.y, qs[e][1], fmaf(y23.x, qs[e][2], y23.y * qs[e][3])));
+                        sacc[sub][2 + e] += fmaf(z01.x, qs[e][0], fmaf(z01.y, qs[e][1], fmaf(z23.x, qs[e][2], z23.y * qs[e][3])));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int sub = 0; sub < (FAST ? 0 : 2); ++sub) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
             const int r0 = 16 * sub + g, r1 = r0 + 8;
@@ -468,6 +561,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             mneg[e] = -m_new;
         }
         float psum[2] = {0.f, 0.f};
+        float pf[2][4];                                              // fp32 probabilities (FAST + zero-points)
         uint32_t pb[2][2];                                           // P^T B fragments per sub-tile
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
@@ -477,6 +571,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             float p3 = fast_exp2(fmaf(sacc[sub][3], qk_scale, mneg[1]));
             psum[0] += p0 + p2;
             psum[1] += p1 + p3;
+            pf[sub][0] = p0; pf[sub][1] = p1; pf[sub][2] = p2; pf[sub][3] = p3;
             if (OUTL) {
                 const int r0 = 16 * sub + g, r1 = r0 + 8;
                 const bool ok0 = !partial || tok0 + r0 < s1, ok1 = !partial || tok0 + r1 < s1;
@@ -504,11 +599,73 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             for (int i = 0; i < 8; ++i) {
                 o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1];
             }
+            if (FAST && ASYM) {
+#pragma unroll
+                for (int G = 0; G < 4; ++G) { oz[G][0] *= corr[0]; oz[G][1] *= corr[1]; }
+            }
         }
 
         // ================= P.V =================
+        if (FAST) {
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
+            for (int sub = 0; sub < 2; ++sub) {
+                // fold the V scale of (token, group) into P: B fragments per group
+                uint32_t px[4], py[4];
+                {
+                    uint32_t r[4];
+                    const int ta = 16 * sub + 2 * t;
+                    uint32_t mxm = 0xffffffffu, mym = 0xffffffffu;
+                    if (partial) {   // scales past the range may be anything (even NaN): force P' to 0 there
+                        const int tg = tok0 + ta;
+                        mxm = (tg < s1 ? 0x0000ffffu : 0u) | (tg + 1 < s1 ? 0xffff0000u : 0u);
+                        mym = (tg + 8 < s1 ? 0x0000ffffu : 0u) | (tg + 9 < s1 ? 0xffff0000u : 0u);
+                    }
+                    lds128(vsb + ta * 8, r);
+                    px[0] = hmul2_u(pb[sub][0], prmt(r[0], r[2], 0x5410u) & mxm);
+                    px[1] = hmul2_u(pb[sub][0], prmt(r[0], r[2], 0x7632u) & mxm);
+                    px[2] = hmul2_u(pb[sub][0], prmt(r[1], r[3], 0x5410u) & mxm);
+                    px[3] = hmul2_u(pb[sub][0], prmt(r[1], r[3], 0x7632u) & mxm);
+                    lds128(vsb + (ta + 8) * 8, r);
+                    py[0] = hmul2_u(pb[sub][1], prmt(r[0], r[2], 0x5410u) & mym);
+                    py[1] = hmul2_u(pb[sub][1], prmt(r[0], r[2], 0x7632u) & mym);
+                    py[2] = hmul2_u(pb[sub][1], prmt(r[1], r[3], 0x5410u) & mym);
+                    py[3] = hmul2_u(pb[sub][1], prmt(r[1], r[3], 0x7632u) & mym);
+                }
+#pragma unroll
+                for (int gp = 0; gp < 2; ++gp) {
+                    uint32_t r[4];
+                    ldmatrix_x4_trans(vb + ldsm_off[sub][gp], r);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int G = 2 * gp + e;
+                        const uint32_t X = r[2 * e], Y = r[2 * e + 1];
+                        mma16816(o[2 * G], nib_lo_to_h2(X), nib_hi_to_h2(X), nib_lo_to_h2(Y), nib_hi_to_h2(Y), px[G], py[G]);
+                        const uint32_t X8 = X >> 8, Y8 = Y >> 8;
+                        mma16816(o[2 * G + 1], nib_lo_to_h2(X8), nib_hi_to_h2(X8), nib_lo_to_h2(Y8), nib_hi_to_h2(Y8),
+                                 px[G], py[G]);
+                    }
+                }
+                if (ASYM) {
+                    const int r0 = 16 * sub + g, r1 = r0 + 8;
+                    uint32_t za[2], zb[2];
+                    lds64(vzb + r0 * 8, za);
+                    lds64(vzb + r1 * 8, zb);
+                    const bool ok0 = !partial || tok0 + r0 < s1, ok1 = !partial || tok0 + r1 < s1;
+                    float y[4], z[4];
+                    const float2 y01 = __half22float2(u32_as_h2(za[0])), y23 = __half22float2(u32_as_h2(za[1]));
+                    const float2 z01 = __half22float2(u32_as_h2(zb[0])), z23 = __half22float2(u32_as_h2(zb[1]));
+                    y[0] = ok0 ? y01.x : 0.f; y[1] = ok0 ? y01.y : 0.f; y[2] = ok0 ? y23.x : 0.f; y[3] = ok0 ? y23.y : 0.f;
+                    z[0] = ok1 ? z01.x : 0.f; z[1] = ok1 ? z01.y : 0.f; z[2] = ok1 ? z23.x : 0.f; z[3] = ok1 ? z23.y : 0.f;
+#pragma unroll
+                    for (int G = 0; G < 4; ++G) {
+                        oz[G][0] = fmaf(pf[sub][0], y[G], fmaf(pf[sub][2], z[G], oz[G][0]));
+                        oz[G][1] = fmaf(pf[sub][1], y[G], fmaf(pf[sub][3], z[G], oz[G][1]));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int sub = 0; sub < (FAST ? 0 : 2); ++sub) {
             // scales of tokens (2t, 2t+1) and (2t+8, 2t+9), paired per group
             uint32_t sx[4], sy[4], zx[4] = {0, 0, 0, 0}, zy[4] = {0, 0, 0, 0};
             {
@@ -607,6 +764,28 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         ra[(2 * t + 1) * D + d0] = o[i][1];
         ra[(2 * t) * D + d1] = o[i][2];
         ra[(2 * t + 1) * D + d1] = o[i][3];
+    }
+    if (FAST && ASYM) {
+        // oz[G][e]: sum over this warp's tokens of p * zero-point for group G, head 2t+e; add it to the
+        // 16 channels [16g, 16g+16) (all in group g/2) of both heads
+#pragma unroll
+        for (int G = 0; G < 4; ++G)
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+#pragma unroll
+                for (int off = 4; off <= 16; off <<= 1) oz[G][e] += __shfl_xor_sync(0xffffffffu, oz[G][e], off);
+        __syncwarp();
+        const int G = g >> 1;
+        const float add0 = G == 0 ? oz[0][0] : G == 1 ? oz[1][0] : G == 2 ? oz[2][0] : oz[3][0];
+        const float add1 = G == 0 ? oz[0][1] : G == 1 ? oz[1][1] : G == 2 ? oz[2][1] : oz[3][1];
+        float* ra = red_acc + (size_t)warp * kHeadsPerCta * D;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int c = 16 * g + ((i + 4 * (g >> 1) + t) & 15);   // rotated: the 32 lanes hit 32 distinct banks
+            ra[(2 * t) * D + c] += add0;
+            ra[(2 * t + 1) * D + c] += add1;
+        }
+        __syncwarp();
     }
     if (OUTL) {
 #pragma unroll

@@ -1,0 +1,167 @@
+"""Whole-stack decode step as ONE CUDA graph.
+
+`GraphedKVStackStep` runs, for every layer of a KV cache, the fused quantize-append of the new
+token followed by the fused decode attention - the two library calls the patched attention
+forward makes per layer - as a single captured graph with a device-resident position counter,
+so that one host call (three pinned-memory uploads, one graph launch, one download) advances the
+whole stack by one token.  It replaces ~25 eager launches and several host syncs per layer in
+the reference's decode loop (src/engine/generate_loop.py:1320-1498, src/cache/int8_cache.py:350-488).
+
+The cache must be preallocated (`cache.reserve`) because graph replay needs stable addresses;
+lengths live on the device (`write_pos_dev`, `context_lens`) and are advanced inside the graph.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib, ops
+from .cache import FP16KVCache, INT4KVCache, INT8KVCache
+
+
+class GraphedKVStackStep:
+    def __init__(self, cache, num_q_heads: int, sm_scale: float, inv_tau: Optional[torch.Tensor] = None,
+                 capacity: Optional[int] = None):
+        if not isinstance(cache, (INT8KVCache, INT4KVCache, FP16KVCache)):
+            raise TypeError("GraphedKVStackStep needs one of this package's caches")
+        self.cache = cache
+        L = cache.num_layers
+        b0 = cache._bufs[0]
+        if b0 is None:
+            raise ValueError("preallocate the cache (append a prompt or call reserve) before building the step")
+        B, Hkv, cap_phys = b0["k"].shape[0], b0["k"].shape[1], b0["k"].shape[2]
+        D = b0["k"].shape[3] * (2 if cache._fmt == _lib.FMT_INT4 else 1)
+        self.L, self.B, self.Hq, self.Hkv, self.D = L, B, num_q_heads, Hkv, D
+        self.capacity = min(cap_phys, capacity or cache._layer_capacity[0])
+        dev = b0["k"].device
+        self.device = dev
+        self.sm_scale = float(sm_scale)
+        self.inv_tau = None if inv_tau is None else inv_tau.to(device=dev, dtype=torch.float32).contiguous()
+        lens = set(cache._layer_seq_lens)
+        if len(lens) != 1:
+            raise ValueError("all layers must hold the same number of tokens")
+        self._len = lens.pop()
+        # device state advanced inside the graph
+        self.pos = torch.full((1,), self._len, dtype=torch.int32, device=dev)
+        self.ctx = torch.full((B,), self._len + 1, dtype=torch.int32, device=dev)
+        # device staging + pinned host mirrors
+        self.q = torch.empty(L, B, num_q_heads, D, dtype=torch.float16, device=dev)
+        self.k_new = torch.empty(L, B, Hkv, 1, D, dtype=torch.float16, device=dev)
+        self.v_new = torch.empty_like(self.k_new)
+        self.out = torch.empty(L, B, num_q_heads, D, dtype=torch.float16, device=dev)
+        self.host_q = torch.empty(self.q.shape, dtype=torch.float16).pin_memory()
+        self.host_k = torch.empty(self.k_new.shape, dtype=torch.float16).pin_memory()
+        self.host_v = torch.empty(self.v_new.shape, dtype=torch.float16).pin_memory()
+        self.host_out = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
+        self.graph = None
+        self.launches_per_step = 0
+
+    # one layer: append at the device-side position, then attend over pos+1 tokens
+    def _layer(self, l: int) -> None:
+        c = self.cache
+        b = c._bufs[l]
+        cap = self.capacity
+        view = {n: t[:, :, :cap] for n, t in b.items()}
+        fmt = c._fmt
+        if fmt == _lib.FMT_FP16:
+            ops.quantize_append(fmt, _lib.SCALE_STATIC, self.k_new[l], self.v_new[l], b["k"], b["v"], None, None,
+                                self.pos, self.D)
+            ops.decode_attn(fmt, self.q[l], view["k"], view["v"], None, None, self.ctx, self.sm_scale,
+                            head_dim=self.D, inv_tau=None if self.inv_tau is None else self.inv_tau[l], out=self.out[l],
+                            max_ctx=cap)
+            return
+        G = b["ks"].shape[-1]
+        gs = self.D // G
+        app, att = {}, {}
+        flags = 0
+        if getattr(c, "asymmetric", False):
+            policy = _lib.SCALE_ASYM_MINMAX
+            app.update(k_zp=b["kz"], v_zp=b["vz"])
+            att.update(k_zp=view["kz"], v_zp=view["vz"])
+        elif c.static_k_scale is not None:
+            policy = _lib.SCALE_STATIC
+            app.update(k_static=c._static_table("k", l, self.Hkv, G, self.device),
+                       v_static=c._static_table("v", l, self.Hkv, G, self.device))
+            if c.adaptive_static_scales and c.adaptive_static_k:
+                flags |= _lib.F_ADAPTIVE
+            if getattr(c, "mixed_rescue", False) or getattr(c, "outlier_rescue_ratio", 0.0) >= 1.0:
+                flags |= _lib.F_MIXED_RESCUE
+            elif getattr(c, "outlier_rescue_ratio", 0.0) > 0.0:
+                raise ValueError("outlier_rescue_ratio in (0,1) needs a per-append quantile and is not graph-capturable")
+        else:
+            policy = _lib.SCALE_DYNAMIC_PCT
+            p = float(c.clip_percentile)
+            app.update(quantile=(max(min(p / 100.0, 1.0), 0.0) if p < 100.0 else 1.0))
+        if c.outlier_idx is not None:
+            oidx = c.outlier_idx[l].to(self.device).contiguous()
+            app.update(outlier_idx=oidx, k_side=b["kside"], v_side=b["vside"])
+            att.update(outlier_idx=oidx, k_side=view["kside"], v_side=view["vside"])
+        ops.quantize_append(fmt, policy, self.k_new[l], self.v_new[l], b["k"], b["v"], b["ks"], b["vs"], self.pos, gs,
+                            flags=flags, adaptive_margin=float(c.adaptive_static_margin),
+                            k_scale_f32=b.get("ks32"), v_scale_f32=b.get("vs32"), **app)
+        ops.decode_attn(fmt, self.q[l], view["k"], view["v"], view["ks"], view["vs"], self.ctx, self.sm_scale,
+                        head_dim=self.D, inv_tau=None if self.inv_tau is None else self.inv_tau[l], out=self.out[l],
+                        max_ctx=cap, **att)
+
+    def _body(self) -> None:
+        for l in range(self.L):
+            self._layer(l)
+        self.pos.add_(1)
+        self.ctx.add_(1)
+
+    def capture(self) -> None:
+        """Warm up once eagerly on a side stream (first-use set-up, workspace growth), rewind the
+        device counters, then capture the step."""
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._body()
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        self.pos.fill_(self._len)
+        self.ctx.fill_(self._len + 1)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._body()
+        self.pos.fill_(self._len)
+        self.ctx.fill_(self._len + 1)
+        self.graph = g
+        self.launches_per_step = self.L * 3
+
+    def step_device(self) -> torch.Tensor:
+        """Advance by one token with inputs already in `self.q / self.k_new / self.v_new`."""
+        if self.graph is None:
+            self.capture()
+        if self._len + 1 > self.capacity:
+            raise ValueError(f"cache capacity {self.capacity} exhausted")
+        self.graph.replay()
+        self._len += 1
+        for i in range(self.L):
+            self.cache._layer_seq_lens[i] = self._len
+        self.cache._seq_len = self._len
+        return self.out
+
+    def step(self, host_q: torch.Tensor, host_k: torch.Tensor, host_v: torch.Tensor) -> torch.Tensor:
+        """Host-to-host step: upload this token's q / k / v for all layers (pinned memory, one copy
+        each), replay the graph, download the attention outputs.  Returns the pinned output buffer
+        (valid until the next call) after synchronising the stream."""
+        if host_q is not self.host_q:
+            self.host_q.copy_(host_q)
+            self.host_k.copy_(host_k)
+            self.host_v.copy_(host_v)
+        self.q.copy_(self.host_q, non_blocking=True)
+        self.k_new.copy_(self.host_k, non_blocking=True)
+        self.v_new.copy_(self.host_v, non_blocking=True)
+        self.step_device()
+        self.host_out.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.host_out
+
+    @property
+    def h2d_bytes_per_step(self) -> int:
+        return (self.q.numel() + self.k_new.numel() + self.v_new.numel()) * 2
+
+    @property
+    def d2h_bytes_per_step(self) -> int:
+        return self.out.numel() * 2

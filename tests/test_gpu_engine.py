@@ -93,3 +93,37 @@ def test_torch_ref_impl_agrees_with_fused(tiny_model):
             E.remove_int8_fused_patch(tiny_model)
         assert cache.get_decode_stats()["torch_ref_calls" if impl == "torch_ref" else "triton_decode_calls"] == 3
     assert torch.allclose(outs["triton_fused"], outs["torch_ref"], atol=2e-2, rtol=2e-2)
+
+
+def test_graphed_stack_step_equals_eager_layer_calls():
+    """The captured whole-stack step (device-side position, cache growing inside the graph) must give
+    bit-identical caches and outputs to eager per-layer append + fused decode, over several steps."""
+    import llm_kvcache_quantization_b200 as kvq
+    from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
+    g = torch.Generator().manual_seed(5)
+    L, B, Hq, Hkv, S, D, steps = 3, 2, 12, 2, 200, 128, 4
+    for make in (lambda: kvq.INT4KVCache(L, device=DEV, group_size=32, asymmetric=True, max_seq_len=S + 8),
+                 lambda: kvq.INT8KVCache(L, device=DEV, group_size=32, clip_percentile=100.0, max_seq_len=S + 8)):
+        ca, cb = make(), make()
+        for l in range(L):
+            k = torch.randn(B, Hkv, S, D, generator=g).half().to(DEV)
+            v = torch.randn(B, Hkv, S, D, generator=g).half().to(DEV)
+            for c in (ca, cb):
+                c.reserve(l, B, Hkv, D, S + 8)
+                c.append(l, k, v)
+        tau = torch.empty(L, Hq).uniform_(0.8, 1.2, generator=g).to(DEV)
+        st = GraphedKVStackStep(ca, Hq, 0.088, inv_tau=tau)
+        for _ in range(steps):
+            hq = torch.randn(L, B, Hq, D, generator=g).half()
+            hk = torch.randn(L, B, Hkv, 1, D, generator=g).half()
+            hv = torch.randn(L, B, Hkv, 1, D, generator=g).half()
+            got = st.step(hq, hk, hv).clone()
+            for l in range(L):
+                cb.append(l, hk[l].to(DEV), hv[l].to(DEV))
+                ref = cb.fused_decode(l, hq[l].to(DEV), 0.088, inv_tau=tau[l])
+                assert torch.equal(got[l].to(DEV), ref), (l, (got[l].to(DEV).float() - ref.float()).abs().max())
+        assert ca.get_seq_len() == cb.get_seq_len() == S + steps
+        for l in range(L):
+            ta, tb = ca.get_decode_tensors(l), cb.get_decode_tensors(l)
+            for n in ("k", "v", "ks", "vs"):
+                assert torch.equal(ta[n], tb[n])
