@@ -56,11 +56,14 @@ __device__ float group_quantile(const float* v, int n, float q) {
     return (w < 0.5f) ? __fmaf_rn(w, diff, x0) : __fmaf_rn(__fsub_rn(w, 1.0f), diff, x1);
 }
 
-template <int FMT, int POLICY>
+// GS > 0: compile-time group size; the group is fetched with 16-byte loads into registers and every
+// loop over it unrolls (the decode-time append is a chain of dependent loads otherwise).  GS == 0:
+// any group size, element-wise loads.
+template <int FMT, int POLICY, int GS>
 __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams p) {
     const KvqAppendArgs& a = p.a;
     const int G = p.G;
-    const int gs = a.group_size;
+    const int gs = GS ? GS : a.group_size;
     const long long per_side = (long long)a.B * a.Hkv * a.T * G;
     long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= p.nsides * per_side) return;
@@ -81,8 +84,27 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
 
     if (FMT == KVQ_FMT_FP16) {
         __half* dst = (__half*)pay + g * gs;
-        for (int i = 0; i < gs; ++i) dst[i] = src[i];
+        if (GS) {
+#pragma unroll
+            for (int i = 0; i < (GS ? GS : 8); i += 8) *(uint4*)(dst + i) = *(const uint4*)(src + i);
+        } else {
+            for (int i = 0; i < gs; ++i) dst[i] = src[i];
+        }
         return;
+    }
+
+    float xr[GS ? GS : 1];
+    if (GS) {
+#pragma unroll
+        for (int i = 0; i < (GS ? GS : 8); i += 8) {
+            const uint4 v = *(const uint4*)(src + i);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                xr[GS ? i + 2 * j : 0] = __low2float(h2[j]);
+                xr[GS ? i + 2 * j + 1 : 0] = __high2float(h2[j]);
+            }
+        }
     }
 
     // outlier channels of this head that fall in this group: copy raw, treat as 0
@@ -94,7 +116,16 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
             if (ch >= 0 && ch < gs) side[j] = src[ch];
         }
     }
+    if (GS && oidx) {
+        for (int j = 0; j < a.n_out; ++j) {
+            const int ch = oidx[j] - g * gs;
+#pragma unroll
+            for (int i = 0; i < (GS ? GS : 1); ++i)
+                if (i == ch) xr[GS ? i : 0] = 0.0f;
+        }
+    }
     auto load = [&](int i) -> float {
+        if (GS) return xr[GS ? i : 0];
         if (oidx) {
             for (int j = 0; j < a.n_out; ++j)
                 if (oidx[j] == g * gs + i) return 0.0f;
@@ -111,6 +142,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
         s32 = st;
         if (a.flags & (KVQ_F_ADAPTIVE | KVQ_F_MIXED_RESCUE | KVQ_F_RESCUE_THR)) {
             float amax = 0.f;   // |x| is exact in fp16, so the fp32 max equals the fp16 amax
+#pragma unroll
             for (int i = 0; i < gs; ++i) amax = fmaxf(amax, fabsf(load(i)));
             const float qmax = (FMT == KVQ_FMT_INT8) ? 127.0f : 7.0f;
             float dyn = __fdiv_rn(fmaxf(amax, 1e-5f), qmax);
@@ -132,6 +164,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
             if (FMT == KVQ_FMT_INT8) amax = h2f(__float2half_rn(amax));
         } else {
             amax = 0.f;
+#pragma unroll
             for (int i = 0; i < gs; ++i) amax = fmaxf(amax, fabsf(load(i)));
             // the reference clamps the fp16 amax in fp16
             amax = h2f(__float2half_rn(fmaxf(amax, 1e-5f)));
@@ -143,6 +176,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
         }
     } else {  // KVQ_SCALE_ASYM_MINMAX
         float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
         for (int i = 0; i < gs; ++i) {
             float x = load(i);
             mn = fminf(mn, x);
@@ -181,6 +215,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
 
     if (FMT == KVQ_FMT_INT8) {
         int8_t* dst = (int8_t*)pay + g * gs;
+#pragma unroll
         for (int i = 0; i < gs; i += 4) {
             int c0 = code_of(i), c1 = code_of(i + 1), c2 = code_of(i + 2), c3 = code_of(i + 3);
             uint32_t w = (uint32_t)(c0 & 0xff) | ((uint32_t)(c1 & 0xff) << 8) |
@@ -189,6 +224,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
         }
     } else {
         uint8_t* dst = (uint8_t*)pay + (g * gs) / 2;
+#pragma unroll
         for (int i = 0; i < gs; i += 8) {
             uint32_t w = 0;
 #pragma unroll
@@ -201,15 +237,28 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
     }
 }
 
-template <int FMT, int POLICY>
-static int launch(const QuantParams& p, cudaStream_t st) {
+static bool side_vec_ok(const KvqAppendSide& s) {
+    return !s.src || ((((uintptr_t)s.src) & 15) == 0 && (s.src_stride_b & 7) == 0 && (s.src_stride_h & 7) == 0 &&
+                      (s.src_stride_t & 7) == 0);
+}
+
+template <int FMT, int POLICY, int GS>
+static int launch_gs(const QuantParams& p, cudaStream_t st) {
     const long long threads = (long long)p.nsides * p.a.B * p.a.Hkv * p.a.T * p.G;
     if (threads == 0) return KVQ_OK;
     const int block = 128;
     const long long grid = (threads + block - 1) / block;
     if (grid > 0x7fffffffLL) return KVQ_EINVAL;
-    quantize_append_kernel<FMT, POLICY><<<(unsigned)grid, block, 0, st>>>(p);
+    quantize_append_kernel<FMT, POLICY, GS><<<(unsigned)grid, block, 0, st>>>(p);
     return check_launch();
+}
+
+template <int FMT, int POLICY>
+static int launch(const QuantParams& p, cudaStream_t st) {
+    const bool dyn_sort = POLICY == KVQ_SCALE_DYNAMIC_PCT && p.a.quantile < 1.0f;   // needs the sortable copy
+    if (p.a.group_size == 32 && !dyn_sort && side_vec_ok(p.a.k) && side_vec_ok(p.a.v))
+        return launch_gs<FMT, POLICY, 32>(p, st);
+    return launch_gs<FMT, POLICY, 0>(p, st);
 }
 
 static bool side_ok(const KvqAppendSide& s, const KvqAppendArgs& a) {
