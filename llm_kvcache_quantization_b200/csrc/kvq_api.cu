@@ -1,4 +1,6 @@
 // Error reporting and device queries of the C ABI.
+#include <stdlib.h>
+
 #include "kvq_internal.h"
 
 namespace kvq {
@@ -19,6 +21,15 @@ int device_sm_count() {
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("KVQ_NO_PDL");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
 }
 
 }  // namespace kvq

@@ -23,6 +23,7 @@ namespace kvq {
 // ---------------------------------------------------------------------------
 template <int EPL>   // channels per lane = D / 32
 __global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p) {
+    pdl_wait();                   // the split kernel's partials
     const KvqAttnArgs& a = p.a;
     const int h = blockIdx.x, b = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -91,12 +92,11 @@ __global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p)
 static int launch_combine(const AttnParams& p, cudaStream_t st) {
     dim3 grid(p.a.Hq, p.a.B);
     switch (p.a.D) {
-        case 64: combine_splits_kernel<2><<<grid, 128, 0, st>>>(p); break;
-        case 128: combine_splits_kernel<4><<<grid, 128, 0, st>>>(p); break;
-        case 256: combine_splits_kernel<8><<<grid, 128, 0, st>>>(p); break;
+        case 64: return launch_pdl(combine_splits_kernel<2>, grid, dim3(128), 0, st, p);
+        case 128: return launch_pdl(combine_splits_kernel<4>, grid, dim3(128), 0, st, p);
+        case 256: return launch_pdl(combine_splits_kernel<8>, grid, dim3(128), 0, st, p);
         default: return KVQ_EUNSUPPORTED;
     }
-    return check_launch();
 }
 
 // Merge of P normalised partials (one per sequence shard).  grid = (Hq, B).
@@ -307,8 +307,8 @@ static int launch_mma(const AttnParams& p, cudaStream_t st) {
     rc = make_payload_map(&vmap, p.a.v, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;
     dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
-    decode_split_mma_kernel<FMT, ASYM, OUTL, FAST><<<grid, kMmaWarps * 32, cfg.dyn_smem, st>>>(mp, kmap, vmap);
-    return check_launch();
+    return launch_pdl(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST>, grid, dim3(kMmaWarps * 32), cfg.dyn_smem, st, mp,
+                      kmap, vmap);
 }
 
 static int dispatch_mma(const AttnParams& p, bool asym, cudaStream_t st) {

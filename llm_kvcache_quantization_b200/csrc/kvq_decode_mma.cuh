@@ -39,6 +39,7 @@
 #include <stdint.h>
 
 #include "kvq_decode_generic.cuh"
+#include "kvq_internal.h"
 
 namespace kvq {
 
@@ -212,11 +213,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     const int nh = min(kHeadsPerCta, p.n_rep - rc * kHeadsPerCta);
     const int nstage = mp.nstage;
 
-    int ctx = a.context_lens ? a.context_lens[b] : a.max_ctx;
-    ctx = max(0, min(ctx, a.max_ctx));
-    int s0, s1;
-    split_range(ctx, p.splits, split, kTS, s0, s1);
-
     extern __shared__ unsigned char smem_dyn[];
     // stage buffers, 1024-byte aligned by hand: the TMA swizzle pattern is a function of the
     // shared-memory address bits, and the read side recomputes it from row indices
@@ -232,6 +228,15 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
+
+    // Nothing above touched global memory.  From here on the kernel reads q and the cache, which the
+    // previous kernel in the stream (the append of the new token) may still be writing.
+    pdl_wait();
+
+    int ctx = a.context_lens ? a.context_lens[b] : a.max_ctx;
+    ctx = max(0, min(ctx, a.max_ctx));
+    int s0, s1;
+    split_range(ctx, p.splits, split, kTS, s0, s1);
 
     // ---- Q fragments: thread (g = head, t) holds q[head g][32t .. 32t+32) in the channel
     // order of the K fragments (INT8: natural; INT4: nibble order d1,d5 | d0,d4 | d3,d7 | d2,d6).
@@ -739,6 +744,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         }
     }
     if (failed && lane == 0) atomicExch(&g_kvq_error_flag, 1);
+    pdl_launch_dependents();      // the combine kernel may be scheduled while this CTA merges its warps
 
     // ---- epilogue: warp totals, then merge the 4 warps through shared memory.
     // The stage buffers are reused as [warp][head][channel] fp32; all copies have landed

@@ -61,6 +61,7 @@ __device__ float group_quantile(const float* v, int n, float q) {
 // any group size, element-wise loads.
 template <int FMT, int POLICY, int GS>
 __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams p) {
+    pdl_launch_dependents();      // the decode kernel that follows may start its prologue now
     const KvqAppendArgs& a = p.a;
     const int G = p.G;
     const int gs = GS ? GS : a.group_size;
