@@ -134,10 +134,11 @@ typedef struct KvqAttnArgs {
     int32_t splits;           /* KV splits per (batch, kv head); 0 = library heuristic    */
     int32_t stages;           /* 0 = split kernel + combine; 1 = split kernel only; 2 = combine only
                                  (for profiling one stage; the workspace carries the partials) */
-    int32_t exact_dequant;    /* packed INT4 on the tensor-core kernel: 0 = scales applied outside the integer
-                                 products (fast; differs from the reference's fp16-rounded code*scale by
-                                 <= 2^-11 relative per element), 1 = bit-faithful RN16(code*scale) per element.
-                                 INT8 and the generic kernel are always bit-faithful.                   */
+    int32_t fast_dequant;     /* 0 (default): every kernel dequantises bit-faithfully, RN16(code*scale) per element.
+                                 1: packed INT4 with group size >= 32 on the tensor-core kernel applies the scales
+                                 outside the integer products (about 10 % faster; differs from the reference's
+                                 fp16-rounded code*scale by <= 2^-11 relative per element, which can exceed the
+                                 2e-3 / 1e-2 tolerance on data with unquantised x20 outlier channels).             */
     void*   workspace;        /* >= kvq_decode_workspace_bytes(...)                       */
     size_t  workspace_bytes;
     void*   out;              /* fp16 [B, Hq, D] or NULL                                  */

@@ -64,7 +64,7 @@ class KvqAttnArgs(C.Structure):
         ("k", KvqCacheSide), ("v", KvqCacheSide),
         ("n_out", _i32), ("outlier_idx", _vp),
         ("context_lens", _vp),
-        ("splits", _i32), ("stages", _i32), ("exact_dequant", _i32),
+        ("splits", _i32), ("stages", _i32), ("fast_dequant", _i32),
         ("workspace", _vp), ("workspace_bytes", C.c_size_t),
         ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
         ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),

@@ -205,12 +205,12 @@ static int make_payload_map(CUtensorMap* map, const KvqCacheSide& sd, int row_by
     return r == CUDA_SUCCESS ? KVQ_OK : KVQ_EUNSUPPORTED;
 }
 
-static bool mma_side_ok(const KvqCacheSide& s, int row_bytes, int hkv, int b, int n_out) {
+static bool mma_side_ok(const KvqCacheSide& s, int row_bytes, int hkv, int b, int n_out, int ng) {
     if (s.pay_stride_s < row_bytes || (s.pay_stride_s & 15) || (s.pay_stride_h & 15) || (s.pay_stride_b & 15)) return false;
     if (hkv > 1 && s.pay_stride_h <= 0) return false;
     if (b > 1 && s.pay_stride_b <= 0) return false;
-    // scales [.., S, 4] with tokens contiguous and 16-byte aligned (b, h) rows
-    if (s.sc_stride_s != 4 || (s.sc_stride_h & 7) || (s.sc_stride_b & 7)) return false;
+    // scales [.., S, NG] with tokens contiguous and 16-byte aligned (b, h) rows
+    if (s.sc_stride_s != ng || (s.sc_stride_h & 7) || (s.sc_stride_b & 7)) return false;
     if (((uintptr_t)s.scale & 15) || (s.zp && ((uintptr_t)s.zp & 15))) return false;
     if (n_out > 0) {
         if (!s.side || ((uintptr_t)s.side & 15) || s.side_stride_s != n_out || (s.side_stride_h & 7) ||
@@ -223,14 +223,17 @@ static bool mma_side_ok(const KvqCacheSide& s, int row_bytes, int hkv, int b, in
 static bool mma_eligible(const AttnParams& p, bool asym) {
     const KvqAttnArgs& a = p.a;
     if (getenv("KVQ_FORCE_GENERIC")) return false;
-    if (a.D != 128 || a.group_size != 32) return false;
+    const int gs = a.group_size;
+    if (a.D != 128 || (gs != 16 && gs != 32 && gs != 64 && gs != 128)) return false;
+    if (a.n_out > 0 && gs != 32) return false;
     if (a.format != KVQ_FMT_INT8 && a.format != KVQ_FMT_INT4) return false;
     if (a.format == KVQ_FMT_INT8 && asym) return false;
     if (a.n_out < 0 || a.n_out > kMaxOut || (a.n_out > 0 && asym)) return false;
     if (a.max_ctx < 1) return false;
     if (!a.k.payload || !a.v.payload || !a.k.scale || !a.v.scale) return false;
     const int rb = a.format == KVQ_FMT_INT8 ? 128 : 64;
-    if (!mma_side_ok(a.k, rb, a.Hkv, a.B, a.n_out) || !mma_side_ok(a.v, rb, a.Hkv, a.B, a.n_out)) return false;
+    if (!mma_side_ok(a.k, rb, a.Hkv, a.B, a.n_out, 128 / gs) || !mma_side_ok(a.v, rb, a.Hkv, a.B, a.n_out, 128 / gs))
+        return false;
     if (((uintptr_t)a.q & 15) || (a.q_stride_b & 7) || (a.q_stride_h & 7)) return false;
     return true;
 }
@@ -251,23 +254,25 @@ static int stages_from_env(int dflt) {
     return (v >= 2 && v <= 8) ? v : dflt;
 }
 
-template <int FMT, bool ASYM, bool OUTL, bool FAST>
-static const MmaConfig& mma_config() {
+template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
+struct MmaTag {};
+
+template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
+static const MmaConfig& mma_config(MmaTag<FMT, ASYM, OUTL, FAST, GS>) {
     static MmaConfig cfg = [] {
         MmaConfig c;
-        // measured on B200: int8 and the 1 KB-stage int4 variants run best with 2 stages (one more
-        // resident CTA per SM), plain symmetric int4 with 3
-        c.nstage = stages_from_env((FMT == KVQ_FMT_INT4 && !ASYM && !OUTL) ? 3 : 2);
-        (void)FAST;
-        c.stage_bytes = mma_stage_bytes(FMT, ASYM, OUTL);
+        // measured on B200: int8 and the outlier variants run best with 2 stages (one more resident
+        // CTA per SM), packed int4 without outliers with 3
+        c.nstage = stages_from_env((FMT == KVQ_FMT_INT4 && !OUTL) ? 3 : 2);
+        c.stage_bytes = mma_stage_bytes(FMT, ASYM, OUTL, GS);
         c.dyn_smem = (size_t)kMmaWarps * c.nstage * c.stage_bytes + 1024;
         c.ctas_per_sm = 1;
-        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST>,
+        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST, GS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.dyn_smem));
         if (c.rc == KVQ_OK) {
             int n = 0;
             c.rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-                &n, decode_split_mma_kernel<FMT, ASYM, OUTL, FAST>, kMmaWarps * 32, c.dyn_smem));
+                &n, decode_split_mma_kernel<FMT, ASYM, OUTL, FAST, GS>, kMmaWarps * 32, c.dyn_smem));
             if (n > 0) c.ctas_per_sm = n;
         }
         return c;
@@ -275,25 +280,50 @@ static const MmaConfig& mma_config() {
     return cfg;
 }
 
-// INT4 takes the factored-scale kernel unless the caller asks for bit-faithful dequantisation
-static bool use_fast(const AttnParams& p) { return p.a.format == KVQ_FMT_INT4 && !p.a.exact_dequant; }
-
-static const MmaConfig* mma_config_for(const AttnParams& p, bool asym) {
-    const bool outl = p.a.n_out > 0;
-    if (p.a.format == KVQ_FMT_INT8)
-        return outl ? &mma_config<KVQ_FMT_INT8, false, true, false>() : &mma_config<KVQ_FMT_INT8, false, false, false>();
-    if (use_fast(p)) {
-        if (asym) return &mma_config<KVQ_FMT_INT4, true, false, true>();
-        return outl ? &mma_config<KVQ_FMT_INT4, false, true, true>() : &mma_config<KVQ_FMT_INT4, false, false, true>();
-    }
-    if (asym) return &mma_config<KVQ_FMT_INT4, true, false, false>();
-    return outl ? &mma_config<KVQ_FMT_INT4, false, true, false>() : &mma_config<KVQ_FMT_INT4, false, false, false>();
+// Bit-faithful dequantisation is the default everywhere.  Packed INT4 with groups of >= 32 channels
+// takes the factored-scale kernel only when the caller opts in (`fast_dequant`).
+static bool use_fast(const AttnParams& p) {
+    return p.a.format == KVQ_FMT_INT4 && p.a.fast_dequant && p.a.group_size >= 32;
 }
 
-template <int FMT, bool ASYM, bool OUTL, bool FAST>
-static int launch_mma(const AttnParams& p, cudaStream_t st) {
+// Calls f(MmaTag<...>{}) for the instantiation that serves these arguments.
+template <class F>
+static int mma_dispatch(const AttnParams& p, bool asym, F&& f) {
+    const bool outl = p.a.n_out > 0, fast = use_fast(p);
+    const int fmt = p.a.format, gs = p.a.group_size;
+#define KVQ_MMA_CASE(FMT_, ASYM_, OUTL_, FAST_, GS_)                                              \
+    if (fmt == FMT_ && asym == ASYM_ && outl == OUTL_ && fast == FAST_ && gs == GS_)              \
+        return f(MmaTag<FMT_, ASYM_, OUTL_, FAST_, GS_>{});
+#define KVQ_MMA_GS(FMT_, ASYM_, FAST_)                                                            \
+    KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 32)                                                   \
+    KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 64)                                                   \
+    KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 128)
+    KVQ_MMA_GS(KVQ_FMT_INT8, false, false)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, false, 16)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, false, true, false, 32)
+    KVQ_MMA_GS(KVQ_FMT_INT4, false, true)
+    KVQ_MMA_GS(KVQ_FMT_INT4, true, true)
+    KVQ_MMA_CASE(KVQ_FMT_INT4, false, true, true, 32)
+    KVQ_MMA_GS(KVQ_FMT_INT4, false, false)
+    KVQ_MMA_GS(KVQ_FMT_INT4, true, false)
+    KVQ_MMA_CASE(KVQ_FMT_INT4, false, false, false, 16)
+    KVQ_MMA_CASE(KVQ_FMT_INT4, true, false, false, 16)
+    KVQ_MMA_CASE(KVQ_FMT_INT4, false, true, false, 32)
+#undef KVQ_MMA_GS
+#undef KVQ_MMA_CASE
+    return KVQ_EUNSUPPORTED;
+}
+
+static const MmaConfig* mma_config_for(const AttnParams& p, bool asym) {
+    const MmaConfig* out = nullptr;
+    mma_dispatch(p, asym, [&](auto tag) { out = &mma_config(tag); return KVQ_OK; });
+    return out;
+}
+
+template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
+static int launch_mma(MmaTag<FMT, ASYM, OUTL, FAST, GS> tag, const AttnParams& p, cudaStream_t st) {
     constexpr int RB = FMT == KVQ_FMT_INT8 ? 128 : 64;
-    const MmaConfig& cfg = mma_config<FMT, ASYM, OUTL, FAST>();
+    const MmaConfig& cfg = mma_config(tag);
     if (cfg.rc) return cfg.rc;
     MmaParams mp;
     mp.p = p;
@@ -307,20 +337,12 @@ static int launch_mma(const AttnParams& p, cudaStream_t st) {
     rc = make_payload_map(&vmap, p.a.v, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;
     dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
-    return launch_pdl(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST>, grid, dim3(kMmaWarps * 32), cfg.dyn_smem, st, mp,
+    return launch_pdl(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST, GS>, grid, dim3(kMmaWarps * 32), cfg.dyn_smem, st, mp,
                       kmap, vmap);
 }
 
 static int dispatch_mma(const AttnParams& p, bool asym, cudaStream_t st) {
-    const bool outl = p.a.n_out > 0;
-    if (p.a.format == KVQ_FMT_INT8)
-        return outl ? launch_mma<KVQ_FMT_INT8, false, true, false>(p, st) : launch_mma<KVQ_FMT_INT8, false, false, false>(p, st);
-    if (use_fast(p)) {
-        if (asym) return launch_mma<KVQ_FMT_INT4, true, false, true>(p, st);
-        return outl ? launch_mma<KVQ_FMT_INT4, false, true, true>(p, st) : launch_mma<KVQ_FMT_INT4, false, false, true>(p, st);
-    }
-    if (asym) return launch_mma<KVQ_FMT_INT4, true, false, false>(p, st);
-    return outl ? launch_mma<KVQ_FMT_INT4, false, true, false>(p, st) : launch_mma<KVQ_FMT_INT4, false, false, false>(p, st);
+    return mma_dispatch(p, asym, [&](auto tag) { return launch_mma(tag, p, st); });
 }
 
 // ---------------------------------------------------------------------------
@@ -359,6 +381,7 @@ static int pick_splits_internal(const AttnParams& p, bool asym, bool mma) {
     const int sms = device_sm_count();
     if (mma) {
         const MmaConfig* cfg = mma_config_for(p, asym);
+        if (!cfg) return 1;
         return pick_splits_waves(rows, p.a.max_ctx, sms * cfg->ctas_per_sm, kMmaWarps * kTS);
     }
     return pick_splits_waves(rows, p.a.max_ctx, sms * 8, 256);

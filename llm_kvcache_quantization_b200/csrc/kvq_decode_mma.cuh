@@ -61,9 +61,14 @@ struct MmaParams {
 // scale tiles of TS x 8 B.  Rounded so that every payload tile stays aligned to the swizzle
 // period (1024 B for 128-byte rows, 512 B for 64-byte rows).
 constexpr int kMaxOut = 4;           // fp16 outlier channels per kv head the tensor-core kernel handles
-__host__ __device__ constexpr int mma_stage_bytes(int fmt, bool asym, bool outl) {
-    // with outliers: + K and V side tiles of TS x kMaxOut fp16 (256 B each)
-    return fmt == KVQ_FMT_INT8 ? 2 * kTS * 128 + 1024 : 2 * kTS * 64 + ((asym || outl) ? 1024 : 512);
+__host__ __device__ constexpr int mma_stage_bytes(int fmt, bool asym, bool outl, int gs) {
+    // K tile, V tile, then 2 (4 with zero-points) scale tiles of TS x (128/gs) fp16, then, with outliers,
+    // K and V side tiles of TS x kMaxOut fp16 (256 B each); rounded up to the swizzle period
+    const int payload = 2 * kTS * (fmt == KVQ_FMT_INT8 ? 128 : 64);
+    const int scb = kTS * (128 / gs) * 2;
+    const int raw = payload + (asym ? 4 : 2) * scb + (outl ? 512 : 0);
+    const int al = fmt == KVQ_FMT_INT8 ? 1024 : 512;
+    return (raw + al - 1) / al * al;
 }
 
 // ---------------------------------------------------------------- PTX helpers
@@ -154,6 +159,55 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     return h2_as_u32(__floats2half2_rn(lo, hi));
 }
 
+// fp16 scales of the token pair (tok, tok+1), `NG` groups each, re-paired per group:
+// out[G] = half2(s[tok][G], s[tok+1][G]); `addr` = shared address of s[tok][0]
+template <int NG>
+__device__ __forceinline__ void load_scale_pairs(uint32_t addr, uint32_t (&out)[NG], uint32_t mask) {
+    if (NG == 1) {
+        uint32_t w;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(addr));
+        out[0] = w & mask;
+    } else if (NG == 2) {
+        uint32_t r[2];
+        lds64(addr, r);
+        out[0] = prmt(r[0], r[1], 0x5410u) & mask;
+        out[NG - 1] = prmt(r[0], r[1], 0x7632u) & mask;
+    } else if (NG == 4) {
+        uint32_t r[4];
+        lds128(addr, r);
+        out[0] = prmt(r[0], r[2], 0x5410u) & mask; out[1 % NG] = prmt(r[0], r[2], 0x7632u) & mask;
+        out[2 % NG] = prmt(r[1], r[3], 0x5410u) & mask; out[3 % NG] = prmt(r[1], r[3], 0x7632u) & mask;
+    } else {
+        uint32_t ra[4], rb[4];
+        lds128(addr, ra);
+        lds128(addr + 16, rb);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            out[(2 * w) % NG] = prmt(ra[w], rb[w], 0x5410u) & mask;
+            out[(2 * w + 1) % NG] = prmt(ra[w], rb[w], 0x7632u) & mask;
+        }
+    }
+}
+// the NG fp16 values of one token row as floats; `addr` = shared address of s[row][0]
+template <int NG>
+__device__ __forceinline__ void load_row_floats(uint32_t addr, float (&f)[NG]) {
+    if (NG == 1) {
+        unsigned short u;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u) : "r"(addr));
+        f[0] = __half2float(__ushort_as_half(u));
+    } else if (NG == 2) {
+        uint32_t w;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(addr));
+        const float2 v = __half22float2(u32_as_h2(w));
+        f[0] = v.x; f[NG - 1] = v.y;
+    } else {
+        uint32_t r[2];
+        lds64(addr, r);
+        const float2 a = __half22float2(u32_as_h2(r[0])), b = __half22float2(u32_as_h2(r[1]));
+        f[0] = a.x; f[1 % NG] = a.y; f[2 % NG] = b.x; f[3 % NG] = b.y;
+    }
+}
+
 constexpr uint32_t kMagic = 0x64006400u;     // half2(1024, 1024)
 constexpr uint32_t kH1152 = 0x64806480u;     // half2(1152, 1152)
 constexpr uint32_t kH1032 = 0x64086408u;     // half2(1032, 1032)
@@ -193,14 +247,20 @@ __device__ __forceinline__ uint32_t apply_scale(uint32_t c, uint32_t s2, uint32_
 //         (+ sum_token z[token][g] * p with zero-points, added to every channel of the group).
 // This removes 3 of every 4 fp16 instructions of the dequantisation; products of integer codes are
 // exact, so the result differs from the bit-faithful path only by the reference's own fp16 rounding
-// of code * scale (<= 2^-11 relative per element).  FAST = false keeps the bit-faithful path.
-template <int FMT, bool ASYM, bool OUTL, bool FAST>
-__global__ void __launch_bounds__(kMmaWarps * 32, (FAST && !OUTL) ? 4 : 1)
+// of code * scale (<= 2^-11 relative per element).  FAST = false is the bit-faithful path and the default;
+// FAST is opt-in (KvqAttnArgs.fast_dequant).
+// GS = quantisation group size (16 / 32 / 64 / 128 channels), NG = 128 / GS scales per token.
+template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
+__global__ void __launch_bounds__(kMmaWarps * 32, (FMT == KVQ_FMT_INT4 && !OUTL) ? 4 : 1)
 decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
     constexpr int RB = (FMT == KVQ_FMT_INT8) ? 128 : 64;      // payload bytes per token row
     constexpr int D = 128;
-    constexpr int STAGE_BYTES = mma_stage_bytes(FMT, ASYM, OUTL);
+    constexpr int NG = 128 / GS;                              // scale groups per token
+    constexpr int SCB = kTS * NG * 2;                         // bytes of one scale tile
+    constexpr int STAGE_BYTES = mma_stage_bytes(FMT, ASYM, OUTL, GS);
+    static_assert(GS == 16 || GS == 32 || GS == 64 || GS == 128, "group size");
+    static_assert(!FAST || GS >= 32, "the factored path needs whole 32-channel chunks inside one group");
     static_assert(!(ASYM && OUTL), "outlier side buffer is defined for symmetric formats");
     static_assert(!FAST || FMT == KVQ_FMT_INT4, "the factored-scale path exists for packed INT4");
     const AttnParams& p = mp.p;
@@ -243,9 +303,9 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     uint32_t qf[16];
     // FAST with zero-points: qs[e][G] = sum over the channels of group G of q[head 2t+e] (fp32);
     // oz[G][e] = zero-point part of the output of that head, shared by every channel of the group
-    float qs[2][4], oz[4][2];
+    float qs[2][NG], oz[NG][2];
 #pragma unroll
-    for (int G = 0; G < 4; ++G) { qs[0][G] = qs[1][G] = 0.f; oz[G][0] = oz[G][1] = 0.f; }
+    for (int G = 0; G < NG; ++G) { qs[0][G] = qs[1][G] = 0.f; oz[G][0] = oz[G][1] = 0.f; }
     {
         const bool hv = g < nh;
         const __half* qp = (const __half*)a.q + (long long)b * a.q_stride_b + (long long)(h0 + (hv ? g : 0)) * a.q_stride_h +
@@ -265,14 +325,14 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         }
         if (FAST && ASYM) {
 #pragma unroll
-            for (int G = 0; G < 4; ++G) {
-                float acc = 0.f;                                // this thread: 8 channels of group G of head g
+            for (int c = 0; c < 4; ++c) {                       // 32-channel chunk c lies in group (32 c) / GS
+                float acc = 0.f;                                // this thread: 8 channels of chunk c of head g
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc += __half2float(qv[8 * G + i]);
+                for (int i = 0; i < 8; ++i) acc += __half2float(qv[8 * c + i]);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);    // every lane of the quad: whole group of head g
-                qs[0][G] = __shfl_sync(0xffffffffu, acc, 4 * (2 * t));
-                qs[1][G] = __shfl_sync(0xffffffffu, acc, 4 * (2 * t + 1));
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);    // every lane of the quad: whole chunk of head g
+                qs[0][(32 * c) / GS] += __shfl_sync(0xffffffffu, acc, 4 * (2 * t));
+                qs[1][(32 * c) / GS] += __shfl_sync(0xffffffffu, acc, 4 * (2 * t + 1));
             }
         }
         if (FMT == KVQ_FMT_INT8) {
@@ -345,16 +405,19 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             tma_load_4d(sb, &kmap, bar, 0, tok0, kvh, b);
             tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
         }
-        // scale-like tiles: TS tokens x 8 B = 256 B = 16 lanes x 16 B each; 2 (or 4) tiles.
+        // scale-like tiles: TS tokens x NG fp16 = 4*NG chunks of 16 bytes per tile; 2 (or 4) tiles.
         // Only bytes of tokens inside the cache view are read; the rest is zero-filled.
-        {
-            const int which = lane >> 4;                 // 0: K side, 1: V side
-            const int tok = tok0 + 2 * (lane & 15);
-            const int nbytes = max(0, min(2, a.max_ctx - tok)) * 8;
-            const long long off = nbytes ? (long long)tok * 4 : 0;
-            const uint32_t dst = sb + 2 * kTS * RB + (lane & 15) * 16;
-            cp_async16(dst + which * (kTS * 8), (which ? vs_row : ks_row) + off, nbytes);
-            if (ASYM) cp_async16(dst + (2 + which) * (kTS * 8), (which ? vz_row : kz_row) + off, nbytes);
+        if (lane < 4 * NG) {
+            const int tok = tok0 + lane * 8 / NG;                  // first token of this 16-byte chunk
+            const int nbytes = max(0, min(16, (a.max_ctx - tok) * 2 * NG));
+            const long long off = nbytes ? (long long)tok * NG : 0;
+            const uint32_t dst = sb + 2 * kTS * RB + lane * 16;
+            cp_async16(dst, ks_row + off, nbytes);
+            cp_async16(dst + SCB, vs_row + off, nbytes);
+            if (ASYM) {
+                cp_async16(dst + 2 * SCB, kz_row + off, nbytes);
+                cp_async16(dst + 3 * SCB, vz_row + off, nbytes);
+            }
         }
         if (OUTL) {
             // side tiles: TS tokens x n_out fp16, contiguous; 4*n_out 16-byte chunks per side
@@ -365,7 +428,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 const int valid = max(0, min(kTS, a.max_ctx - tok0)) * n_out * 2;   // bytes inside the view
                 const int nbytes = max(0, min(16, valid - 16 * c));
                 const __half* src = (which ? vside_row : kside_row) + (nbytes ? (long long)tok0 * n_out + 8 * c : 0);
-                cp_async16(sb + 2 * kTS * RB + 2 * (kTS * 8) + which * 256 + 16 * c, src, nbytes);
+                cp_async16(sb + 2 * kTS * RB + 2 * SCB + which * 256 + 16 * c, src, nbytes);
             }
         }
         cp_async_mbar_arrive(bar);
@@ -401,10 +464,10 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         const uint32_t kb = wbase_u + st * STAGE_BYTES;
         const uint32_t vb = kb + kTS * RB;
         const uint32_t ksb = kb + 2 * kTS * RB;
-        const uint32_t vsb = ksb + kTS * 8;
-        const uint32_t kzb = ksb + 2 * kTS * 8;
-        const uint32_t vzb = ksb + 3 * kTS * 8;
-        const uint32_t kob = ksb + 2 * kTS * 8;            // outlier side tiles share the zero-point slots
+        const uint32_t vsb = ksb + SCB;
+        const uint32_t kzb = ksb + 2 * SCB;
+        const uint32_t vzb = ksb + 3 * SCB;
+        const uint32_t kob = ksb + 2 * SCB;                // outlier side tiles share the zero-point slots
         const uint32_t vob = kob + 256;
 
         // ================= q.K : logits for 2 sub-tiles of 16 tokens =================
@@ -412,46 +475,50 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         if (FAST) {
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
-                float sg[4][4];                                  // per-group integer dot products
+                float sg[NG][4];                                 // per-group integer dot products
 #pragma unroll
-                for (int G = 0; G < 4; ++G)
+                for (int G = 0; G < NG; ++G)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) sg[G][j] = 0.f;
 #pragma unroll
                 for (int gp = 0; gp < 2; ++gp) {
-                    uint32_t r[4];                               // rows g | g+8 of group 2gp, then of group 2gp+1
+                    uint32_t r[4];                               // rows g | g+8 of chunk 2gp, then of chunk 2gp+1
                     ldmatrix_x4(kb + ldsm_off[sub][gp], r);
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int G = 2 * gp + e;
+                        const int c = 2 * gp + e;                // 32-channel chunk; its group:
+                        constexpr int kDummy = 0; (void)kDummy;
+                        const int G = (32 * c) / GS;
                         const uint32_t w0 = r[2 * e], w1 = r[2 * e + 1];
                         mma16816(sg[G], nib_lo_to_h2(w0), nib_lo_to_h2(w1), nib_hi_to_h2(w0), nib_hi_to_h2(w1),
-                                 qf[4 * G], qf[4 * G + 1]);
+                                 qf[4 * c], qf[4 * c + 1]);
                         const uint32_t x0 = w0 >> 8, x1 = w1 >> 8;
                         mma16816(sg[G], nib_lo_to_h2(x0), nib_lo_to_h2(x1), nib_hi_to_h2(x0), nib_hi_to_h2(x1),
-                                 qf[4 * G + 2], qf[4 * G + 3]);
+                                 qf[4 * c + 2], qf[4 * c + 3]);
                     }
                 }
                 const int r0 = 16 * sub + g, r1 = r0 + 8;
-                uint32_t sa[2], sb2[2];
-                lds64(ksb + r0 * 8, sa);
-                lds64(ksb + r1 * 8, sb2);
-                const float2 a01 = __half22float2(u32_as_h2(sa[0])), a23 = __half22float2(u32_as_h2(sa[1]));
-                const float2 b01 = __half22float2(u32_as_h2(sb2[0])), b23 = __half22float2(u32_as_h2(sb2[1]));
-                sacc[sub][0] = fmaf(a01.x, sg[0][0], fmaf(a01.y, sg[1][0], fmaf(a23.x, sg[2][0], a23.y * sg[3][0])));
-                sacc[sub][1] = fmaf(a01.x, sg[0][1], fmaf(a01.y, sg[1][1], fmaf(a23.x, sg[2][1], a23.y * sg[3][1])));
-                sacc[sub][2] = fmaf(b01.x, sg[0][2], fmaf(b01.y, sg[1][2], fmaf(b23.x, sg[2][2], b23.y * sg[3][2])));
-                sacc[sub][3] = fmaf(b01.x, sg[0][3], fmaf(b01.y, sg[1][3], fmaf(b23.x, sg[2][3], b23.y * sg[3][3])));
-                if (ASYM) {
-                    lds64(kzb + r0 * 8, sa);
-                    lds64(kzb + r1 * 8, sb2);
-                    const float2 y01 = __half22float2(u32_as_h2(sa[0])), y23 = __half22float2(u32_as_h2(sa[1]));
-                    const float2 z01 = __half22float2(u32_as_h2(sb2[0])), z23 = __half22float2(u32_as_h2(sb2[1]));
+                float sa[NG], sb2[NG];                           // K scales of rows r0, r1
+                load_row_floats<NG>(ksb + r0 * 2 * NG, sa);
+                load_row_floats<NG>(ksb + r1 * 2 * NG, sb2);
+                sacc[sub][0] = sacc[sub][1] = sacc[sub][2] = sacc[sub][3] = 0.f;
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        sacc[sub][e] += fmaf(y01.x, qs[e][0], fmaf(y01.y, qs[e][1], fmaf(y23.x, qs[e][2], y23.y * qs[e][3])));
-                        sacc[sub][2 + e] += fmaf(z01.x, qs[e][0], fmaf(z01.y, qs[e][1], fmaf(z23.x, qs[e][2], z23.y * qs[e][3])));
-                    }
+                for (int G = 0; G < NG; ++G) {
+                    sacc[sub][0] = fmaf(sa[G], sg[G][0], sacc[sub][0]);
+                    sacc[sub][1] = fmaf(sa[G], sg[G][1], sacc[sub][1]);
+                    sacc[sub][2] = fmaf(sb2[G], sg[G][2], sacc[sub][2]);
+                    sacc[sub][3] = fmaf(sb2[G], sg[G][3], sacc[sub][3]);
+                }
+                if (ASYM) {
+                    load_row_floats<NG>(kzb + r0 * 2 * NG, sa);
+                    load_row_floats<NG>(kzb + r1 * 2 * NG, sb2);
+#pragma unroll
+                    for (int G = 0; G < NG; ++G)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            sacc[sub][e] = fmaf(sa[G], qs[e][G], sacc[sub][e]);
+                            sacc[sub][2 + e] = fmaf(sb2[G], qs[e][G], sacc[sub][2 + e]);
+                        }
                 }
             }
         }
@@ -461,18 +528,34 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
             const int r0 = 16 * sub + g, r1 = r0 + 8;
             // one group (= one scale) per thread per row
-            uint32_t s2[2], z2[2] = {0u, 0u};
+            // the thread's 32 channels [32t, 32t+32) lie in one group (GS >= 32) or in the two groups
+            // 2t, 2t+1 (GS == 16): s2[row][half], half = which 16-channel half of the slice
+            uint32_t s2[2][2], z2[2][2] = {{0u, 0u}, {0u, 0u}};
             {
-                unsigned short u0, u1;
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u0) : "r"(ksb + r0 * 8 + 2 * t));
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u1) : "r"(ksb + r1 * 8 + 2 * t));
-                s2[0] = prmt((uint32_t)u0, 0u, 0x1010u);
-                s2[1] = prmt((uint32_t)u1, 0u, 0x1010u);
-                if (ASYM) {
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u0) : "r"(kzb + r0 * 8 + 2 * t));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u1) : "r"(kzb + r1 * 8 + 2 * t));
-                    z2[0] = prmt((uint32_t)u0, 0u, 0x1010u);
-                    z2[1] = prmt((uint32_t)u1, 0u, 0x1010u);
+                constexpr int kFirst = 0; (void)kFirst;
+                const int gidx = (32 * t) / GS;                  // first group of the slice
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int r = rr ? r1 : r0;
+                    if (GS == 16) {
+                        uint32_t w;
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(ksb + (r * NG + gidx) * 2));
+                        s2[rr][0] = prmt(w, 0u, 0x1010u);
+                        s2[rr][1] = prmt(w, 0u, 0x3232u);
+                        if (ASYM) {
+                            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(kzb + (r * NG + gidx) * 2));
+                            z2[rr][0] = prmt(w, 0u, 0x1010u);
+                            z2[rr][1] = prmt(w, 0u, 0x3232u);
+                        }
+                    } else {
+                        unsigned short u;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u) : "r"(ksb + (r * NG + gidx) * 2));
+                        s2[rr][0] = s2[rr][1] = prmt((uint32_t)u, 0u, 0x1010u);
+                        if (ASYM) {
+                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(u) : "r"(kzb + (r * NG + gidx) * 2));
+                            z2[rr][0] = z2[rr][1] = prmt((uint32_t)u, 0u, 0x1010u);
+                        }
+                    }
                 }
             }
             if (FMT == KVQ_FMT_INT8) {
@@ -491,10 +574,11 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    uint32_t a0 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5140u), s2[0], z2[0]);
-                    uint32_t a1 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5140u), s2[1], z2[1]);
-                    uint32_t a2 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5342u), s2[0], z2[0]);
-                    uint32_t a3 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5342u), s2[1], z2[1]);
+                    const int hh = j >> 2;                           // channels 4j.. lie in half j / 4 of the slice
+                    uint32_t a0 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5140u), s2[0][hh], z2[0][hh]);
+                    uint32_t a1 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5140u), s2[1][hh], z2[1][hh]);
+                    uint32_t a2 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5342u), s2[0][hh], z2[0][hh]);
+                    uint32_t a3 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5342u), s2[1][hh], z2[1][hh]);
                     mma16816(sacc[sub], a0, a1, a2, a3, qf[2 * j], qf[2 * j + 1]);
                 }
             } else {
@@ -503,16 +587,17 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 lds128(kb + r1 * 64 + ((t ^ ((r1 >> 1) & 3)) << 4), w[1]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    uint32_t lo0 = apply_scale<ASYM>(nib_lo_to_h2(w[0][i]), s2[0], z2[0]);
-                    uint32_t lo1 = apply_scale<ASYM>(nib_lo_to_h2(w[1][i]), s2[1], z2[1]);
-                    uint32_t hi0 = apply_scale<ASYM>(nib_hi_to_h2(w[0][i]), s2[0], z2[0]);
-                    uint32_t hi1 = apply_scale<ASYM>(nib_hi_to_h2(w[1][i]), s2[1], z2[1]);
+                    const int hh = i >> 1;                           // channels 8i.. lie in half i / 2 of the slice
+                    uint32_t lo0 = apply_scale<ASYM>(nib_lo_to_h2(w[0][i]), s2[0][hh], z2[0][hh]);
+                    uint32_t lo1 = apply_scale<ASYM>(nib_lo_to_h2(w[1][i]), s2[1][hh], z2[1][hh]);
+                    uint32_t hi0 = apply_scale<ASYM>(nib_hi_to_h2(w[0][i]), s2[0][hh], z2[0][hh]);
+                    uint32_t hi1 = apply_scale<ASYM>(nib_hi_to_h2(w[1][i]), s2[1][hh], z2[1][hh]);
                     mma16816(sacc[sub], lo0, lo1, hi0, hi1, qf[4 * i], qf[4 * i + 1]);
                     const uint32_t w0 = w[0][i] >> 8, w1 = w[1][i] >> 8;
-                    lo0 = apply_scale<ASYM>(nib_lo_to_h2(w0), s2[0], z2[0]);
-                    lo1 = apply_scale<ASYM>(nib_lo_to_h2(w1), s2[1], z2[1]);
-                    hi0 = apply_scale<ASYM>(nib_hi_to_h2(w0), s2[0], z2[0]);
-                    hi1 = apply_scale<ASYM>(nib_hi_to_h2(w1), s2[1], z2[1]);
+                    lo0 = apply_scale<ASYM>(nib_lo_to_h2(w0), s2[0][hh], z2[0][hh]);
+                    lo1 = apply_scale<ASYM>(nib_lo_to_h2(w1), s2[1][hh], z2[1][hh]);
+                    hi0 = apply_scale<ASYM>(nib_hi_to_h2(w0), s2[0][hh], z2[0][hh]);
+                    hi1 = apply_scale<ASYM>(nib_hi_to_h2(w1), s2[1][hh], z2[1][hh]);
                     mma16816(sacc[sub], lo0, lo1, hi0, hi1, qf[4 * i + 2], qf[4 * i + 3]);
                 }
             }
@@ -606,7 +691,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             }
             if (FAST && ASYM) {
 #pragma unroll
-                for (int G = 0; G < 4; ++G) { oz[G][0] *= corr[0]; oz[G][1] *= corr[1]; }
+                for (int G = 0; G < NG; ++G) { oz[G][0] *= corr[0]; oz[G][1] *= corr[1]; }
             }
         }
 
@@ -615,9 +700,8 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 // fold the V scale of (token, group) into P: B fragments per group
-                uint32_t px[4], py[4];
+                uint32_t px[NG], py[NG];
                 {
-                    uint32_t r[4];
                     const int ta = 16 * sub + 2 * t;
                     uint32_t mxm = 0xffffffffu, mym = 0xffffffffu;
                     if (partial) {   // scales past the range may be anything (even NaN): force P' to 0 there
@@ -625,16 +709,13 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                         mxm = (tg < s1 ? 0x0000ffffu : 0u) | (tg + 1 < s1 ? 0xffff0000u : 0u);
                         mym = (tg + 8 < s1 ? 0x0000ffffu : 0u) | (tg + 9 < s1 ? 0xffff0000u : 0u);
                     }
-                    lds128(vsb + ta * 8, r);
-                    px[0] = hmul2_u(pb[sub][0], prmt(r[0], r[2], 0x5410u) & mxm);
-                    px[1] = hmul2_u(pb[sub][0], prmt(r[0], r[2], 0x7632u) & mxm);
-                    px[2] = hmul2_u(pb[sub][0], prmt(r[1], r[3], 0x5410u) & mxm);
-                    px[3] = hmul2_u(pb[sub][0], prmt(r[1], r[3], 0x7632u) & mxm);
-                    lds128(vsb + (ta + 8) * 8, r);
-                    py[0] = hmul2_u(pb[sub][1], prmt(r[0], r[2], 0x5410u) & mym);
-                    py[1] = hmul2_u(pb[sub][1], prmt(r[0], r[2], 0x7632u) & mym);
-                    py[2] = hmul2_u(pb[sub][1], prmt(r[1], r[3], 0x5410u) & mym);
-                    py[3] = hmul2_u(pb[sub][1], prmt(r[1], r[3], 0x7632u) & mym);
+                    load_scale_pairs<NG>(vsb + ta * 2 * NG, px, mxm);
+                    load_scale_pairs<NG>(vsb + (ta + 8) * 2 * NG, py, mym);
+#pragma unroll
+                    for (int G = 0; G < NG; ++G) {
+                        px[G] = hmul2_u(pb[sub][0], px[G]);
+                        py[G] = hmul2_u(pb[sub][1], py[G]);
+                    }
                 }
 #pragma unroll
                 for (int gp = 0; gp < 2; ++gp) {
@@ -642,29 +723,26 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                     ldmatrix_x4_trans(vb + ldsm_off[sub][gp], r);
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const int G = 2 * gp + e;
+                        const int c = 2 * gp + e;                // 32-channel chunk c, group (32 c) / GS
+                        const int G = (32 * c) / GS;
                         const uint32_t X = r[2 * e], Y = r[2 * e + 1];
-                        mma16816(o[2 * G], nib_lo_to_h2(X), nib_hi_to_h2(X), nib_lo_to_h2(Y), nib_hi_to_h2(Y), px[G], py[G]);
+                        mma16816(o[2 * c], nib_lo_to_h2(X), nib_hi_to_h2(X), nib_lo_to_h2(Y), nib_hi_to_h2(Y), px[G], py[G]);
                         const uint32_t X8 = X >> 8, Y8 = Y >> 8;
-                        mma16816(o[2 * G + 1], nib_lo_to_h2(X8), nib_hi_to_h2(X8), nib_lo_to_h2(Y8), nib_hi_to_h2(Y8),
+                        mma16816(o[2 * c + 1], nib_lo_to_h2(X8), nib_hi_to_h2(X8), nib_lo_to_h2(Y8), nib_hi_to_h2(Y8),
                                  px[G], py[G]);
                     }
                 }
                 if (ASYM) {
                     const int r0 = 16 * sub + g, r1 = r0 + 8;
-                    uint32_t za[2], zb[2];
-                    lds64(vzb + r0 * 8, za);
-                    lds64(vzb + r1 * 8, zb);
                     const bool ok0 = !partial || tok0 + r0 < s1, ok1 = !partial || tok0 + r1 < s1;
-                    float y[4], z[4];
-                    const float2 y01 = __half22float2(u32_as_h2(za[0])), y23 = __half22float2(u32_as_h2(za[1]));
-                    const float2 z01 = __half22float2(u32_as_h2(zb[0])), z23 = __half22float2(u32_as_h2(zb[1]));
-                    y[0] = ok0 ? y01.x : 0.f; y[1] = ok0 ? y01.y : 0.f; y[2] = ok0 ? y23.x : 0.f; y[3] = ok0 ? y23.y : 0.f;
-                    z[0] = ok1 ? z01.x : 0.f; z[1] = ok1 ? z01.y : 0.f; z[2] = ok1 ? z23.x : 0.f; z[3] = ok1 ? z23.y : 0.f;
+                    float y[NG], z[NG];
+                    load_row_floats<NG>(vzb + r0 * 2 * NG, y);
+                    load_row_floats<NG>(vzb + r1 * 2 * NG, z);
 #pragma unroll
-                    for (int G = 0; G < 4; ++G) {
-                        oz[G][0] = fmaf(pf[sub][0], y[G], fmaf(pf[sub][2], z[G], oz[G][0]));
-                        oz[G][1] = fmaf(pf[sub][1], y[G], fmaf(pf[sub][3], z[G], oz[G][1]));
+                    for (int G = 0; G < NG; ++G) {
+                        const float yv = ok0 ? y[G] : 0.f, zv = ok1 ? z[G] : 0.f;
+                        oz[G][0] = fmaf(pf[sub][0], yv, fmaf(pf[sub][2], zv, oz[G][0]));
+                        oz[G][1] = fmaf(pf[sub][1], yv, fmaf(pf[sub][3], zv, oz[G][1]));
                     }
                 }
             }
@@ -672,31 +750,24 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
         for (int sub = 0; sub < (FAST ? 0 : 2); ++sub) {
             // scales of tokens (2t, 2t+1) and (2t+8, 2t+9), paired per group
-            uint32_t sx[4], sy[4], zx[4] = {0, 0, 0, 0}, zy[4] = {0, 0, 0, 0};
+            uint32_t sx[NG], sy[NG], zx[NG], zy[NG];
             {
-                uint32_t r[4];
                 const int ta = 16 * sub + 2 * t;
-                lds128(vsb + ta * 8, r);
-                sx[0] = prmt(r[0], r[2], 0x5410u); sx[1] = prmt(r[0], r[2], 0x7632u);
-                sx[2] = prmt(r[1], r[3], 0x5410u); sx[3] = prmt(r[1], r[3], 0x7632u);
-                lds128(vsb + (ta + 8) * 8, r);
-                sy[0] = prmt(r[0], r[2], 0x5410u); sy[1] = prmt(r[0], r[2], 0x7632u);
-                sy[2] = prmt(r[1], r[3], 0x5410u); sy[3] = prmt(r[1], r[3], 0x7632u);
-                if (ASYM) {
-                    lds128(vzb + ta * 8, r);
-                    zx[0] = prmt(r[0], r[2], 0x5410u); zx[1] = prmt(r[0], r[2], 0x7632u);
-                    zx[2] = prmt(r[1], r[3], 0x5410u); zx[3] = prmt(r[1], r[3], 0x7632u);
-                    lds128(vzb + (ta + 8) * 8, r);
-                    zy[0] = prmt(r[0], r[2], 0x5410u); zy[1] = prmt(r[0], r[2], 0x7632u);
-                    zy[2] = prmt(r[1], r[3], 0x5410u); zy[3] = prmt(r[1], r[3], 0x7632u);
-                }
+                uint32_t mxm = 0xffffffffu, mym = 0xffffffffu;
                 if (partial) {
                     // tokens past the range may hold anything (even NaN scales): force them to 0 * 0
                     const int tg = tok0 + ta;
-                    const uint32_t mxm = (tg < s1 ? 0x0000ffffu : 0u) | (tg + 1 < s1 ? 0xffff0000u : 0u);
-                    const uint32_t mym = (tg + 8 < s1 ? 0x0000ffffu : 0u) | (tg + 9 < s1 ? 0xffff0000u : 0u);
+                    mxm = (tg < s1 ? 0x0000ffffu : 0u) | (tg + 1 < s1 ? 0xffff0000u : 0u);
+                    mym = (tg + 8 < s1 ? 0x0000ffffu : 0u) | (tg + 9 < s1 ? 0xffff0000u : 0u);
+                }
+                load_scale_pairs<NG>(vsb + ta * 2 * NG, sx, mxm);
+                load_scale_pairs<NG>(vsb + (ta + 8) * 2 * NG, sy, mym);
+                if (ASYM) {
+                    load_scale_pairs<NG>(vzb + ta * 2 * NG, zx, mxm);
+                    load_scale_pairs<NG>(vzb + (ta + 8) * 2 * NG, zy, mym);
+                } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) { sx[i] &= mxm; sy[i] &= mym; zx[i] &= mxm; zy[i] &= mym; }
+                    for (int G = 0; G < NG; ++G) zx[G] = zy[G] = 0u;
                 }
             }
             // ldmatrix source row for this lane: matrix (lane>>3): bit0 = token half, bit1 = chunk + 1
@@ -710,7 +781,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const uint32_t X = r[2 * e] ^ 0x80808080u, Y = r[2 * e + 1] ^ 0x80808080u;
-                        const int grp = (i + e) >> 1;
+                        const int grp = (16 * (i + e)) / GS;             // channels 16(i+e) .. +15
                         uint32_t a0 = apply_scale<ASYM>(i8pair_to_h2(X, 0x5240u), sx[grp], zx[grp]);
                         uint32_t a1 = apply_scale<ASYM>(i8pair_to_h2(X, 0x5341u), sx[grp], zx[grp]);
                         uint32_t a2 = apply_scale<ASYM>(i8pair_to_h2(Y, 0x5240u), sy[grp], zy[grp]);
@@ -726,18 +797,27 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const uint32_t X = r[2 * e], Y = r[2 * e + 1];
-                        const int grp = i + e;
-                        uint32_t a0 = apply_scale<ASYM>(nib_lo_to_h2(X), sx[grp], zx[grp]);
-                        uint32_t a1 = apply_scale<ASYM>(nib_hi_to_h2(X), sx[grp], zx[grp]);
-                        uint32_t a2 = apply_scale<ASYM>(nib_lo_to_h2(Y), sy[grp], zy[grp]);
-                        uint32_t a3 = apply_scale<ASYM>(nib_hi_to_h2(Y), sy[grp], zy[grp]);
-                        mma16816(o[2 * grp], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
+                        const int c = i + e;                             // 32-channel chunk; this thread's 4 channels
+                        // 32c + 4g .. +3 lie in group 2c + (g >> 2) when GS == 16, else in (32 c) / GS
+                        uint32_t ux, uy, vx, vy;
+                        if (GS == 16) {
+                            const bool up = (g >> 2) != 0;
+                            ux = up ? sx[(2 * c + 1) % NG] : sx[(2 * c) % NG]; uy = up ? sy[(2 * c + 1) % NG] : sy[(2 * c) % NG];
+                            vx = up ? zx[(2 * c + 1) % NG] : zx[(2 * c) % NG]; vy = up ? zy[(2 * c + 1) % NG] : zy[(2 * c) % NG];
+                        } else {
+                            ux = sx[(32 * c) / GS]; uy = sy[(32 * c) / GS]; vx = zx[(32 * c) / GS]; vy = zy[(32 * c) / GS];
+                        }
+                        uint32_t a0 = apply_scale<ASYM>(nib_lo_to_h2(X), ux, vx);
+                        uint32_t a1 = apply_scale<ASYM>(nib_hi_to_h2(X), ux, vx);
+                        uint32_t a2 = apply_scale<ASYM>(nib_lo_to_h2(Y), uy, vy);
+                        uint32_t a3 = apply_scale<ASYM>(nib_hi_to_h2(Y), uy, vy);
+                        mma16816(o[2 * c], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
                         const uint32_t X8 = X >> 8, Y8 = Y >> 8;
-                        a0 = apply_scale<ASYM>(nib_lo_to_h2(X8), sx[grp], zx[grp]);
-                        a1 = apply_scale<ASYM>(nib_hi_to_h2(X8), sx[grp], zx[grp]);
-                        a2 = apply_scale<ASYM>(nib_lo_to_h2(Y8), sy[grp], zy[grp]);
-                        a3 = apply_scale<ASYM>(nib_hi_to_h2(Y8), sy[grp], zy[grp]);
-                        mma16816(o[2 * grp + 1], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
+                        a0 = apply_scale<ASYM>(nib_lo_to_h2(X8), ux, vx);
+                        a1 = apply_scale<ASYM>(nib_hi_to_h2(X8), ux, vx);
+                        a2 = apply_scale<ASYM>(nib_lo_to_h2(Y8), uy, vy);
+                        a3 = apply_scale<ASYM>(nib_hi_to_h2(Y8), uy, vy);
+                        mma16816(o[2 * c + 1], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
                     }
                 }
             }
@@ -775,15 +855,17 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         // oz[G][e]: sum over this warp's tokens of p * zero-point for group G, head 2t+e; add it to the
         // 16 channels [16g, 16g+16) (all in group g/2) of both heads
 #pragma unroll
-        for (int G = 0; G < 4; ++G)
+        for (int G = 0; G < NG; ++G)
 #pragma unroll
             for (int e = 0; e < 2; ++e)
 #pragma unroll
                 for (int off = 4; off <= 16; off <<= 1) oz[G][e] += __shfl_xor_sync(0xffffffffu, oz[G][e], off);
         __syncwarp();
-        const int G = g >> 1;
-        const float add0 = G == 0 ? oz[0][0] : G == 1 ? oz[1][0] : G == 2 ? oz[2][0] : oz[3][0];
-        const float add1 = G == 0 ? oz[0][1] : G == 1 ? oz[1][1] : G == 2 ? oz[2][1] : oz[3][1];
+        const int Gme = (16 * g) / GS;                 // group of this lane's channels [16g, 16g+16)
+        float add0 = oz[0][0], add1 = oz[0][1];
+#pragma unroll
+        for (int G = 1; G < NG; ++G)
+            if (G == Gme) { add0 = oz[G][0]; add1 = oz[G][1]; }
         float* ra = red_acc + (size_t)warp * kHeadsPerCta * D;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {

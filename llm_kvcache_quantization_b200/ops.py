@@ -175,7 +175,7 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
                 outlier_idx=None, k_side=None, v_side=None,
                 splits: int = 0, out: Optional[torch.Tensor] = None,
                 return_partial: bool = False, max_ctx: Optional[int] = None, stages: int = 0,
-                packed_partial: Optional[torch.Tensor] = None, exact_dequant: Optional[bool] = None):
+                packed_partial: Optional[torch.Tensor] = None, fast_dequant: Optional[bool] = None):
     """Fused q_len==1 attention over a (quantized) cache.  q fp16 [B,Hq,D].
 
     Returns `out` fp16 [B,Hq,D]; with `return_partial` also the normalised
@@ -208,9 +208,9 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
         a.inv_tau = inv_tau.data_ptr()
     a.sm_scale = float(sm_scale)
     a.stages = int(stages)
-    if exact_dequant is None:      # KVQ_INT4_EXACT=1: bit-faithful INT4 dequantisation instead of factored scales
-        exact_dequant = os.environ.get("KVQ_INT4_EXACT", "0") == "1"
-    a.exact_dequant = 1 if exact_dequant else 0
+    if fast_dequant is None:       # KVQ_INT4_FAST=1: factored-scale INT4 path instead of bit-faithful dequantisation
+        fast_dequant = os.environ.get("KVQ_INT4_FAST", "0") == "1"
+    a.fast_dequant = 1 if fast_dequant else 0
     a.k = _cache_side(k_payload, k_scale, k_zp, k_side)
     a.v = _cache_side(v_payload, v_scale, v_zp, v_side)
     if outlier_idx is not None:
