@@ -191,13 +191,14 @@ KVQ_API int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream);
 KVQ_API int kvq_decode_attn_static(const KvqAttnArgs* args, kvq_stream_t stream);
 
 /* Host-side query, no launch: 1 if kvq_decode_attn would take the tensor-core TMA kernel for these
- * arguments (head_dim 128, group 32, int8 / packed int4, 16-byte aligned rows), 0 for the generic kernel. */
+ * arguments (head_dim 128, group 16/32/64/128, int8 / packed int4, 16-byte aligned rows), 0 for the generic kernel. */
 KVQ_API int kvq_decode_kernel_kind(const KvqAttnArgs* args);
 
 KVQ_API size_t kvq_decode_workspace_bytes(int32_t B, int32_t Hq, int32_t D, int32_t splits);
 /* Split count the library would choose for these arguments on the current device (host-side query,
- * no launch): the count whose last wave of CTAs is fullest given the resident CTAs per SM of the
- * kernel that would run, with at least one 128-token slice per split. */
+ * no launch): the count that minimises waves x (tokens per split rounded to 128, plus a fixed
+ * per-CTA cost of 128 tokens), where a wave is the resident CTAs per SM of the kernel that would
+ * run times the SM count. */
 KVQ_API int32_t kvq_decode_pick_splits(const KvqAttnArgs* args);
 
 typedef struct KvqCombineArgs {
