@@ -189,18 +189,19 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Payload [B, Hkv, S, row_bytes] as a 4-D byte tensor; box = (row_bytes, TS, 1, 1), swizzle = row width.
-// Rows at or beyond `s_extent` are zero-filled by the copy engine.
+// Payload [B, Hkv, S, row_bytes] as a 4-D byte tensor; box = (min(row_bytes, 128), TS, 1, 1), swizzle = box
+// width.  Rows at or beyond `s_extent` are zero-filled by the copy engine.
 static int make_payload_map(CUtensorMap* map, const KvqCacheSide& sd, int row_bytes, int s_extent, int hkv, int b) {
+    const int box_bytes = row_bytes > 128 ? 128 : row_bytes;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return KVQ_EUNSUPPORTED;
     cuuint64_t dims[4] = {(cuuint64_t)row_bytes, (cuuint64_t)s_extent, (cuuint64_t)hkv, (cuuint64_t)b};
     cuuint64_t strides[3] = {(cuuint64_t)sd.pay_stride_s, (cuuint64_t)sd.pay_stride_h, (cuuint64_t)sd.pay_stride_b};
-    cuuint32_t box[4] = {(cuuint32_t)row_bytes, (cuuint32_t)kTS, 1, 1};
+    cuuint32_t box[4] = {(cuuint32_t)box_bytes, (cuuint32_t)kTS, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(sd.payload), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? KVQ_OK : KVQ_EUNSUPPORTED;
 }
@@ -209,6 +210,7 @@ static bool mma_side_ok(const KvqCacheSide& s, int row_bytes, int hkv, int b, in
     if (s.pay_stride_s < row_bytes || (s.pay_stride_s & 15) || (s.pay_stride_h & 15) || (s.pay_stride_b & 15)) return false;
     if (hkv > 1 && s.pay_stride_h <= 0) return false;
     if (b > 1 && s.pay_stride_b <= 0) return false;
+    if (ng == 0) return true;                      // fp16 cache: payload only
     // scales [.., S, NG] with tokens contiguous and 16-byte aligned (b, h) rows
     if (s.sc_stride_s != ng || (s.sc_stride_h & 7) || (s.sc_stride_b & 7)) return false;
     if (((uintptr_t)s.scale & 15) || (s.zp && ((uintptr_t)s.zp & 15))) return false;
@@ -226,13 +228,15 @@ static bool mma_eligible(const AttnParams& p, bool asym) {
     const int gs = a.group_size;
     if (a.D != 128 || (gs != 16 && gs != 32 && gs != 64 && gs != 128)) return false;
     if (a.n_out > 0 && gs != 32) return false;
-    if (a.format != KVQ_FMT_INT8 && a.format != KVQ_FMT_INT4) return false;
-    if (a.format == KVQ_FMT_INT8 && asym) return false;
-    if (a.n_out < 0 || a.n_out > kMaxOut || (a.n_out > 0 && asym)) return false;
+    const bool f16 = a.format == KVQ_FMT_FP16;
+    if (!f16 && a.format != KVQ_FMT_INT8 && a.format != KVQ_FMT_INT4) return false;
+    if (a.format != KVQ_FMT_INT4 && asym) return false;
+    if (a.n_out < 0 || a.n_out > kMaxOut || (a.n_out > 0 && (asym || f16))) return false;
     if (a.max_ctx < 1) return false;
-    if (!a.k.payload || !a.v.payload || !a.k.scale || !a.v.scale) return false;
-    const int rb = a.format == KVQ_FMT_INT8 ? 128 : 64;
-    if (!mma_side_ok(a.k, rb, a.Hkv, a.B, a.n_out, 128 / gs) || !mma_side_ok(a.v, rb, a.Hkv, a.B, a.n_out, 128 / gs))
+    if (!a.k.payload || !a.v.payload || (!f16 && (!a.k.scale || !a.v.scale))) return false;
+    const int rb = f16 ? 256 : a.format == KVQ_FMT_INT8 ? 128 : 64;
+    const int ng = f16 ? 0 : 128 / gs;
+    if (!mma_side_ok(a.k, rb, a.Hkv, a.B, a.n_out, ng) || !mma_side_ok(a.v, rb, a.Hkv, a.B, a.n_out, ng))
         return false;
     if (((uintptr_t)a.q & 15) || (a.q_stride_b & 7) || (a.q_stride_h & 7)) return false;
     return true;
@@ -298,6 +302,7 @@ static int mma_dispatch(const AttnParams& p, bool asym, F&& f) {
     KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 32)                                                   \
     KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 64)                                                   \
     KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 128)
+    KVQ_MMA_CASE(KVQ_FMT_FP16, false, false, false, 128)
     KVQ_MMA_GS(KVQ_FMT_INT8, false, false)
     KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, false, 16)
     KVQ_MMA_CASE(KVQ_FMT_INT8, false, true, false, 32)
@@ -322,7 +327,7 @@ static const MmaConfig* mma_config_for(const AttnParams& p, bool asym) {
 
 template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
 static int launch_mma(MmaTag<FMT, ASYM, OUTL, FAST, GS> tag, const AttnParams& p, cudaStream_t st) {
-    constexpr int RB = FMT == KVQ_FMT_INT8 ? 128 : 64;
+    constexpr int RB = FMT == KVQ_FMT_FP16 ? 256 : FMT == KVQ_FMT_INT8 ? 128 : 64;
     const MmaConfig& cfg = mma_config(tag);
     if (cfg.rc) return cfg.rc;
     MmaParams mp;

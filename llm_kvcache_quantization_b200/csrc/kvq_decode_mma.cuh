@@ -1,8 +1,9 @@
 // Tensor-core split-K decode-attention kernel for sm_100a.
 //
-// Shapes: head_dim 128, group size 32 (one fp16 scale per 32 channels per token),
-// INT8 or nibble-packed INT4 payload, optional fp16 zero-points, <= 8 query heads
-// per KV head per CTA.  Everything else goes to the generic kernel.
+// Shapes: head_dim 128; INT8 or nibble-packed INT4 payload with one fp16 scale per group of
+// 16 / 32 / 64 / 128 channels per token, optional fp16 zero-points, optional fp16 outlier
+// side channels; or an unquantised fp16 cache.  <= 8 query heads per KV head per CTA.
+// Everything else goes to the generic kernel.
 //
 // Structure
 //  * grid = (KV split, kv head [x head chunk], batch row); 4 warps per CTA.  Every warp
@@ -64,6 +65,8 @@ constexpr int kMaxOut = 4;           // fp16 outlier channels per kv head the te
 __host__ __device__ constexpr int mma_stage_bytes(int fmt, bool asym, bool outl, int gs) {
     // K tile, V tile, then 2 (4 with zero-points) scale tiles of TS x (128/gs) fp16, then, with outliers,
     // K and V side tiles of TS x kMaxOut fp16 (256 B each); rounded up to the swizzle period
+    // (fp16 cache: K and V tiles of TS x 256 B, each as two 128-byte-wide halves; no scales)
+    if (fmt == KVQ_FMT_FP16) return 2 * kTS * 256;
     const int payload = 2 * kTS * (fmt == KVQ_FMT_INT8 ? 128 : 64);
     const int scb = kTS * (128 / gs) * 2;
     const int raw = payload + (asym ? 4 : 2) * scb + (outl ? 512 : 0);
@@ -254,7 +257,8 @@ template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
 __global__ void __launch_bounds__(kMmaWarps * 32, (FMT == KVQ_FMT_INT4 && !OUTL) ? 4 : 1)
 decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
-    constexpr int RB = (FMT == KVQ_FMT_INT8) ? 128 : 64;      // payload bytes per token row
+    constexpr bool F16 = FMT == KVQ_FMT_FP16;                 // unquantised cache: no scales, no dequantisation
+    constexpr int RB = F16 ? 256 : (FMT == KVQ_FMT_INT8) ? 128 : 64;   // payload bytes per token row
     constexpr int D = 128;
     constexpr int NG = 128 / GS;                              // scale groups per token
     constexpr int SCB = kTS * NG * 2;                         // bytes of one scale tile
@@ -263,6 +267,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     static_assert(!FAST || GS >= 32, "the factored path needs whole 32-channel chunks inside one group");
     static_assert(!(ASYM && OUTL), "outlier side buffer is defined for symmetric formats");
     static_assert(!FAST || FMT == KVQ_FMT_INT4, "the factored-scale path exists for packed INT4");
+    static_assert(!F16 || (!ASYM && !OUTL && GS == 128), "the fp16 cache has neither scales nor side channels");
     const AttnParams& p = mp.p;
     const KvqAttnArgs& a = p.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -306,7 +311,22 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     float qs[2][NG], oz[NG][2];
 #pragma unroll
     for (int G = 0; G < NG; ++G) { qs[0][G] = qs[1][G] = 0.f; oz[G][0] = oz[G][1] = 0.f; }
-    {
+    if (F16) {
+        // natural B-fragment order: k-chunk j <-> channels 16j + {2t, 2t+1} and 16j + 8 + {2t, 2t+1}
+        const bool hv = g < nh;
+        const uint32_t* q32 = reinterpret_cast<const uint32_t*>(
+            (const __half*)a.q + (long long)b * a.q_stride_b + (long long)(h0 + (hv ? g : 0)) * a.q_stride_h);
+        const __half tau = (a.inv_tau && hv) ? __float2half_rn(a.inv_tau[h0 + g]) : __float2half(1.0f);
+        const __half2 tau2 = __half2half2(tau);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t w0 = q32[8 * j + t], w1 = q32[8 * j + 4 + t];
+            if (!hv) w0 = w1 = 0u;
+            if (a.inv_tau) { w0 = hmul2_u(w0, h2_as_u32(tau2)); w1 = hmul2_u(w1, h2_as_u32(tau2)); }
+            qf[2 * j] = w0;
+            qf[2 * j + 1] = w1;
+        }
+    } else {
         const bool hv = g < nh;
         const __half* qp = (const __half*)a.q + (long long)b * a.q_stride_b + (long long)(h0 + (hv ? g : 0)) * a.q_stride_h +
                            (FAST ? 8 * t : 32 * t);
@@ -402,12 +422,19 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         const uint32_t bar = bar0 + 8 * st;
         if (lane == 0) {
             mbar_expect_tx(bar, 2 * kTS * RB);
-            tma_load_4d(sb, &kmap, bar, 0, tok0, kvh, b);
-            tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
+            if (F16) {   // a 256-byte row travels as two 128-byte-wide boxes (the widest swizzle span)
+                tma_load_4d(sb, &kmap, bar, 0, tok0, kvh, b);
+                tma_load_4d(sb + kTS * 128, &kmap, bar, 128, tok0, kvh, b);
+                tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
+                tma_load_4d(sb + kTS * RB + kTS * 128, &vmap, bar, 128, tok0, kvh, b);
+            } else {
+                tma_load_4d(sb, &kmap, bar, 0, tok0, kvh, b);
+                tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
+            }
         }
         // scale-like tiles: TS tokens x NG fp16 = 4*NG chunks of 16 bytes per tile; 2 (or 4) tiles.
         // Only bytes of tokens inside the cache view are read; the rest is zero-filled.
-        if (lane < 4 * NG) {
+        if (!F16 && lane < 4 * NG) {
             const int tok = tok0 + lane * 8 / NG;                  // first token of this 16-byte chunk
             const int nbytes = max(0, min(16, (a.max_ctx - tok) * 2 * NG));
             const long long off = nbytes ? (long long)tok * NG : 0;
@@ -522,8 +549,24 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 }
             }
         }
+        if (F16) {
 #pragma unroll
-        for (int sub = 0; sub < (FAST ? 0 : 2); ++sub) {
+            for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
+                // ldmatrix row of this lane: matrix (lane>>3): bit 0 = token half, bit 1 = second 8-channel chunk
+                const int lrow = 16 * sub + ((lane >> 3) & 1) * 8 + (lane & 7);
+                const uint32_t rowb = kb + lrow * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {                   // k-chunk j: channels 16j .. 16j+15
+                    uint32_t r[4];
+                    ldmatrix_x4(rowb + (j >> 2) * (kTS * 128) + (((2 * (j & 3) + (lane >> 4)) ^ (lrow & 7)) << 4), r);
+                    mma16816(sacc[sub], r[0], r[1], r[2], r[3], qf[2 * j], qf[2 * j + 1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int sub = 0; sub < ((FAST || F16) ? 0 : 2); ++sub) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
             const int r0 = 16 * sub + g, r1 = r0 + 8;
@@ -747,8 +790,28 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 }
             }
         }
+        if (F16) {
 #pragma unroll
-        for (int sub = 0; sub < (FAST ? 0 : 2); ++sub) {
+            for (int sub = 0; sub < 2; ++sub) {
+                uint32_t mxm = 0xffffffffu, mym = 0xffffffffu;
+                if (partial) {   // rows past the range may hold anything (even NaN): zero them, P is 0 there
+                    const int tg = tok0 + 16 * sub + 2 * t;
+                    mxm = (tg < s1 ? 0x0000ffffu : 0u) | (tg + 1 < s1 ? 0xffff0000u : 0u);
+                    mym = (tg + 8 < s1 ? 0x0000ffffu : 0u) | (tg + 9 < s1 ? 0xffff0000u : 0u);
+                }
+                // transposing load: matrix (lane>>3): bit 0 = second 8-channel chunk, bit 1 = token half
+                const int vrow = 16 * sub + (lane >> 4) * 8 + (lane & 7);
+                const uint32_t rowb = vb + vrow * 128;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {                   // m-block i: channels 16i .. 16i+15
+                    uint32_t r[4];
+                    ldmatrix_x4_trans(rowb + (i >> 2) * (kTS * 128) + (((2 * (i & 3) + ((lane >> 3) & 1)) ^ (vrow & 7)) << 4), r);
+                    mma16816(o[i], r[0] & mxm, r[1] & mxm, r[2] & mym, r[3] & mym, pb[sub][0], pb[sub][1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int sub = 0; sub < ((FAST || F16) ? 0 : 2); ++sub) {
             // scales of tokens (2t, 2t+1) and (2t+8, 2t+9), paired per group
             uint32_t sx[NG], sy[NG], zx[NG], zy[NG];
             {
@@ -843,7 +906,8 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         int d0, d1;                                               // channels of fragment rows g, g+8
-        if (FMT == KVQ_FMT_INT8) { d0 = 16 * i + 2 * g; d1 = d0 + 1; }
+        if (F16) { d0 = 16 * i + g; d1 = d0 + 8; }
+        else if (FMT == KVQ_FMT_INT8) { d0 = 16 * i + 2 * g; d1 = d0 + 1; }
         else { const int base = 32 * (i >> 1) + 4 * g + 2 * (i & 1); d0 = base + 1; d1 = base; }
         float* ra = red_acc + (size_t)warp * kHeadsPerCta * D;
         ra[(2 * t) * D + d0] = o[i][0];
