@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define KVQ_ABI_VERSION 1
+#define KVQ_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define KVQ_API __attribute__((visibility("default")))
@@ -92,6 +92,20 @@ typedef struct KvqAppendArgs {
     int64_t write_pos;        /* first cache slot to write                                */
     const int32_t* write_pos_dev; /* if not NULL the slot is read on the device instead   */
     KvqAppendSide k, v;
+    /* Optional rotary embedding fused in front of the quantizer (rope_cos == NULL: off).  K is rotated
+     * before it is quantized, V is not; with q_src the query rows are rotated by the same launch and
+     * written to q_out (the attention kernel's q).  Rotate-half convention with fp16 arithmetic rounded
+     * per operation, RN16(RN16(x cos) + RN16(rot(x) sin)), as _apply_rope does
+     * (src/engine/patch_model.py:223-278); channels >= rotary_dim pass through. */
+    const void* rope_cos;     /* fp16 [B or 1, T, rotary_dim]                             */
+    const void* rope_sin;
+    int64_t rope_stride_b, rope_stride_t;               /* elements; stride_b 0 = shared by the batch */
+    int32_t rotary_dim;       /* even, <= D                                               */
+    int32_t Hq;               /* query heads in q_src                                     */
+    const void* q_src;        /* fp16 [B, Hq, T, D] before rotation, or NULL              */
+    int64_t q_stride_b, q_stride_h, q_stride_t;         /* elements                      */
+    void*   q_out;            /* fp16 [B, Hq, T, D] after rotation                        */
+    int64_t qo_stride_b, qo_stride_h, qo_stride_t;      /* elements                      */
 } KvqAppendArgs;
 
 /*
@@ -221,6 +235,29 @@ typedef struct KvqCombineArgs {
  * online-softmax merge of src/kernels/triton_decode_attn_int8.py:247-283.
  */
 KVQ_API int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream);
+
+/*
+ * Dequantise a cache (or a slice of one) back to fp16 [B, Hkv, S, D].
+ * Stands in for INT8KVCache.get_kv (src/cache/int8_cache.py:490-542), INT4KVCache.get_kv and
+ * to_tuple, i.e. dequantize_symmetric_int8 / dequantize_symmetric_int4
+ * (src/quant/int8_basic.py:167-246, src/quant/int4_basic.py:162-227, after unpack_int4
+ * src/quant/int4_basic.py:275-303) and dequantize_asymmetric (src/quant/asymmetric_quant.py:144-196):
+ *   value = RN16(fp16(code) * scale)  [ + zero_point, rounded again ];  outlier channels take the
+ *   fp16 side value.  K and V are converted in one launch; v.payload == NULL converts K only.
+ */
+typedef struct KvqDequantArgs {
+    int32_t format;              /* KVQ_FMT_INT8 or KVQ_FMT_INT4 (nibble-packed)             */
+    int32_t B, Hkv, S, D;
+    int32_t group_size;          /* channels per scale; -1 = D                               */
+    int32_t n_out;
+    const int16_t* outlier_idx;  /* [Hkv, n_out] or NULL                                     */
+    KvqCacheSide k, v;
+    void* k_out;                 /* fp16, 16-byte aligned                                    */
+    void* v_out;
+    int64_t out_stride_b, out_stride_h, out_stride_s;   /* elements, multiples of 8; D contiguous */
+} KvqDequantArgs;
+
+KVQ_API int kvq_dequantize(const KvqDequantArgs* args, kvq_stream_t stream);
 
 /*
  * Device-side error flag (synchronises the device): 0 = clean, 1 = a bounded wait on a

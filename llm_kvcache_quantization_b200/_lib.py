@@ -43,6 +43,10 @@ class KvqAppendArgs(C.Structure):
         ("n_out", _i32), ("outlier_idx", _vp),
         ("write_pos", _i64), ("write_pos_dev", _vp),
         ("k", KvqAppendSide), ("v", KvqAppendSide),
+        ("rope_cos", _vp), ("rope_sin", _vp), ("rope_stride_b", _i64), ("rope_stride_t", _i64),
+        ("rotary_dim", _i32), ("Hq", _i32),
+        ("q_src", _vp), ("q_stride_b", _i64), ("q_stride_h", _i64), ("q_stride_t", _i64),
+        ("q_out", _vp), ("qo_stride_b", _i64), ("qo_stride_h", _i64), ("qo_stride_t", _i64),
     ]
 
 
@@ -81,6 +85,16 @@ class KvqCombineArgs(C.Structure):
     ]
 
 
+class KvqDequantArgs(C.Structure):
+    _fields_ = [
+        ("format", _i32), ("B", _i32), ("Hkv", _i32), ("S", _i32), ("D", _i32), ("group_size", _i32),
+        ("n_out", _i32), ("outlier_idx", _vp),
+        ("k", KvqCacheSide), ("v", KvqCacheSide),
+        ("k_out", _vp), ("v_out", _vp),
+        ("out_stride_b", _i64), ("out_stride_h", _i64), ("out_stride_s", _i64),
+    ]
+
+
 # every symbol include/kvq.h declares: (name, restype, argtypes)
 EXPORTS = (
     ("kvq_quantize_append", C.c_int, (C.POINTER(KvqAppendArgs), _vp)),
@@ -89,6 +103,7 @@ EXPORTS = (
     ("kvq_decode_workspace_bytes", C.c_size_t, (_i32, _i32, _i32, _i32)),
     ("kvq_decode_pick_splits", _i32, (C.POINTER(KvqAttnArgs),)),
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
+    ("kvq_dequantize", C.c_int, (C.POINTER(KvqDequantArgs), _vp)),
     ("kvq_debug_error_flag", C.c_int, (C.c_int,)),
     ("kvq_decode_kernel_kind", C.c_int, (C.POINTER(KvqAttnArgs),)),
     ("kvq_strerror", C.c_char_p, (C.c_int,)),

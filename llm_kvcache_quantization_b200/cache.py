@@ -173,6 +173,31 @@ class _CacheBase:
         if layer_id == 0:
             self._seq_len = target_len
 
+    @staticmethod
+    def _rope_tables(cos: Tensor, sin: Tensor, batch: int, tokens: int, device):
+        """cos / sin of rank 2-4 (as HF hands them to the attention module) -> fp16 [B or 1, T, rotary_dim]."""
+        out = []
+        for t in (cos, sin):
+            if t.ndim > 4:
+                raise ValueError(f"Unexpected cos/sin rank {t.ndim}; expected 2-4.")
+            if t.ndim == 4:
+                t = t[:, 0]
+            if t.ndim == 2:
+                t = t[None]
+            if t.shape[0] not in (1, batch) or t.shape[1] != tokens:
+                raise ValueError(f"cos/sin shape {tuple(t.shape)} does not match batch {batch}, tokens {tokens}")
+            out.append(t.to(device=device, dtype=torch.float16).contiguous())
+        return out[0], out[1]
+
+    def supports_fused_rope(self) -> bool:
+        """True when append_rotary can rotate inside the quantizer launch."""
+        return True
+
+    def append_rotary(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+        """Rotate q and k (rotate-half RoPE, the arithmetic of src/engine/patch_model.py:223-278),
+        append k (rotated) and v, all in ONE launch; returns the rotated q [B,Hq,T,D] fp16."""
+        raise NotImplementedError
+
     def get_seq_len(self) -> int:
         return self._seq_len
 
@@ -228,6 +253,19 @@ class FP16KVCache(_CacheBase):
         ops.quantize_append(FMT_FP16, SCALE_STATIC, k.to(torch.float16), v.to(torch.float16),
                             bufs["k"], bufs["v"], None, None, old, D)
         self._finish_append(layer_id, old + T)
+
+    def append_rotary(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+        self._check_append(layer_id, k, v)
+        B, H, T, D = k.shape
+        old = self._layer_seq_lens[layer_id]
+        self._ensure_capacity(layer_id, B, H, D, old + T)
+        bufs = self._bufs[layer_id]
+        c16, s16 = self._rope_tables(cos, sin, B, T, k.device)
+        q_rot = ops.quantize_append(FMT_FP16, SCALE_STATIC, k.to(torch.float16), v.to(torch.float16),
+                                    bufs["k"], bufs["v"], None, None, old, D, rope_cos=c16, rope_sin=s16,
+                                    q=q.to(torch.float16))
+        self._finish_append(layer_id, old + T)
+        return q_rot
 
     def get_kv(self, layer_id: int) -> Tuple[Tensor, Tensor]:
         k, v = self._layer_view(layer_id, ("k", "v"))
@@ -350,7 +388,8 @@ class _QuantCache(_CacheBase):
     def _rescue_threshold(self, x: Tensor, G: int) -> Optional[Tensor]:
         return None
 
-    def _append_impl(self, layer_id: int, k: Tensor, v: Tensor, extra_flags: int = 0) -> None:
+    def _append_impl(self, layer_id: int, k: Tensor, v: Tensor, extra_flags: int = 0, rope=None):
+        """`rope = (q, cos, sin)`: rotate q and k inside the launch; returns the rotated q."""
         self._check_append(layer_id, k, v)
         for nm, sc in (("static_k_scale", self.static_k_scale), ("static_v_scale", self.static_v_scale)):
             if sc is not None and layer_id >= len(sc):
@@ -364,6 +403,11 @@ class _QuantCache(_CacheBase):
             quant._check_quantize_input(k, "append(k)")
             quant._check_quantize_input(v, "append(v)")
         B, H, T, D = k.shape
+        if rope is not None:
+            if extra_flags & F_RESCUE_THR:
+                raise ValueError("outlier_rescue_ratio in (0,1) needs a quantile of the rotated keys before the "
+                                 "launch; rotate in torch and call append() instead")
+            c16, s16 = self._rope_tables(rope[1], rope[2], B, T, k.device)
         G = self._num_groups(D)
         gs = D // G
         old = self._layer_seq_lens[layer_id]
@@ -394,11 +438,14 @@ class _QuantCache(_CacheBase):
             policy = SCALE_DYNAMIC_PCT
             p = float(self.clip_percentile)
             kw.update(quantile=(max(min(p / 100.0, 1.0), 0.0) if p < 100.0 else 1.0))
-        ops.quantize_append(self._fmt, policy, k, v, bufs["k"], bufs["v"], bufs["ks"], bufs["vs"], old, gs,
-                            flags=flags, adaptive_margin=float(self.adaptive_static_margin), **kw)
+        if rope is not None:
+            kw.update(rope_cos=c16, rope_sin=s16, q=rope[0].to(torch.float16))
+        q_rot = ops.quantize_append(self._fmt, policy, k, v, bufs["k"], bufs["v"], bufs["ks"], bufs["vs"], old, gs,
+                                    flags=flags, adaptive_margin=float(self.adaptive_static_margin), **kw)
         self._finish_append(layer_id, old + T)
-        if self.validate_inputs and policy == SCALE_STATIC:
+        if self.validate_inputs and policy == SCALE_STATIC and rope is None:
             self._warn_if_clipped(layer_id, k, v, old, T)
+        return q_rot
 
     def _warn_if_clipped(self, layer_id, k, v, old, T) -> None:
         bufs = self._bufs[layer_id]
@@ -479,6 +526,9 @@ class INT8KVCache(_QuantCache):
         """Quantize and append (src/cache/int8_cache.py:350-488)."""
         self._append_impl(layer_id, k, v)
 
+    def append_rotary(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+        return self._append_impl(layer_id, k, v, rope=(q, cos, sin))
+
     def get_int8_tensors(self, layer_id: int) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
         """(k_int8, v_int8, k_scale, v_scale) views of the valid tokens; scales are fp16."""
         return self._layer_view(layer_id, ("k", "v", "ks", "vs"))
@@ -487,9 +537,9 @@ class INT8KVCache(_QuantCache):
         k, v, ks, vs = self.get_int8_tensors(layer_id)
         if k.shape[2] == 0:
             logger.warning("get_kv(layer_id=%d) returning zero-length tensors.", layer_id)
-        # fp32 product then one rounding, as the reference's fp32-scale dequant (int8_cache.py:536-542)
-        return (quant.dequantize_symmetric_int8(k, ks.float()).to(self.dtype),
-                quant.dequantize_symmetric_int8(v, vs.float()).to(self.dtype))
+        # one rounding of the exact product code * scale, as the reference's dequant (int8_cache.py:536-542)
+        kd, vd = ops.dequantize(FMT_INT8, k, v, ks, vs)
+        return kd.to(self.dtype), vd.to(self.dtype)
 
     @classmethod
     def from_tuple(cls, past_key_values, device="cuda", clip_percentile: float = 99.9,
@@ -568,6 +618,9 @@ class INT4KVCache(_QuantCache):
                 warnings.warn(
                     f"KVC-031: mixed_rescue=True has no effect at layer {layer_id} because no static "
                     "scale is provided.", RuntimeWarning)
+        self._append_impl(layer_id, k, v, extra_flags=self._rescue_flags())
+
+    def _rescue_flags(self) -> int:
         flags = 0
         if self.mixed_rescue:
             flags |= F_MIXED_RESCUE
@@ -575,7 +628,13 @@ class INT4KVCache(_QuantCache):
             flags |= F_MIXED_RESCUE          # max(static, dynamic) everywhere (int4_cache.py:380-381)
         elif self.outlier_rescue_ratio > 0.0:
             flags |= F_RESCUE_THR
-        self._append_impl(layer_id, k, v, extra_flags=flags)
+        return flags
+
+    def supports_fused_rope(self) -> bool:
+        return not (self._rescue_flags() & F_RESCUE_THR)
+
+    def append_rotary(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+        return self._append_impl(layer_id, k, v, extra_flags=self._rescue_flags(), rope=(q, cos, sin))
 
     def get_int4_tensors(self, layer_id: int) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
         """(k_packed, v_packed, k_scale, v_scale) views; payload [B,Hkv,S,D/2], scales fp16."""
@@ -583,21 +642,14 @@ class INT4KVCache(_QuantCache):
 
     def get_kv(self, layer_id: int) -> Tuple[Tensor, Tensor]:
         t = self.get_decode_tensors(layer_id)
-        k, v = quant.unpack_int4(t["k"]), quant.unpack_int4(t["v"])
-        if self.asymmetric:
-            kd = quant.dequantize_asymmetric_groupwise(k, t["ks"], t["kz"])
-            vd = quant.dequantize_asymmetric_groupwise(v, t["vs"], t["vz"])
-        else:
-            kd = quant.dequantize_symmetric_int4(k, t["ks"].float())
-            vd = quant.dequantize_symmetric_int4(v, t["vs"].float())
-        kd, vd = kd.to(self.dtype), vd.to(self.dtype)
-        if self.outlier_idx is not None:
-            idx = t["outlier_idx"].to(kd.device).long()
-            B, H, S, _ = kd.shape
-            gather = idx[None, :, None, :].expand(B, H, S, idx.shape[-1])
-            kd = kd.scatter(-1, gather, t["kside"].to(self.dtype))
-            vd = vd.scatter(-1, gather, t["vside"].to(self.dtype))
-        return kd, vd
+        if t["k"].shape[2] == 0:
+            logger.warning("get_kv(layer_id=%d) returning zero-length tensors.", layer_id)
+        oidx = t.get("outlier_idx")
+        if oidx is not None:
+            oidx = oidx.to(device=t["k"].device, dtype=torch.int16).contiguous()
+        kd, vd = ops.dequantize(FMT_INT4, t["k"], t["v"], t["ks"], t["vs"], k_zp=t.get("kz"), v_zp=t.get("vz"),
+                                outlier_idx=oidx, k_side=t.get("kside"), v_side=t.get("vside"))
+        return kd.to(self.dtype), vd.to(self.dtype)
 
     @classmethod
     def from_tuple(cls, past_key_values, device="cuda", clip_percentile: float = 99.9,

@@ -10,6 +10,9 @@
 //   asym   rng = max(max-min, 9.1553e-4); s = rng/15; zp = min + 8 s;
 //          c = clamp(rint((x - zp)/s), -8, 7)      (src/quant/asymmetric_quant.py:98-141)
 //   percentile = torch.quantile's sorted lerp, evaluated as one fma.
+//   rotary embedding (optional, K side and the query): rotate-half in fp16, every operation rounded
+//          as the eager torch ops are: RN16(RN16(x cos) + RN16(rot(x) sin)), rot(x) = (-x[d + r/2], x[d - r/2])
+//          (src/engine/patch_model.py:223-278).
 // This translation unit must be compiled WITHOUT fast-math: it relies on IEEE
 // fp32 division and fp16 subnormals.
 //
@@ -31,9 +34,20 @@ struct QuantParams {
     KvqAppendArgs a;
     int G;
     int nsides;   // 2, or 1 when the V side is absent (v.src == NULL)
+    long long q_items;   // B * Hq * T * G work items that rotate the query (0 = none)
 };
 
 __device__ __forceinline__ float h2f(__half h) { return __half2float(h); }
+
+// One channel of a head row after rotate-half RoPE.  `row` points at channel 0 of the head row,
+// `cs` / `sn` at channel 0 of the cos / sin row of this (batch, token).
+__device__ __forceinline__ __half rope_one(const __half* row, const __half* cs, const __half* sn, int rd, int d) {
+    const __half x = row[d];
+    if (d >= rd) return x;
+    const int hf = rd >> 1;
+    const __half partner = d < hf ? __hneg(row[d + hf]) : row[d - hf];
+    return __hadd_rn(__hmul_rn(x, cs[d]), __hmul_rn(partner, sn[d]));
+}
 
 // torch.quantile(|x|, q) over n sorted values: rank = q*(n-1) in fp32, fma lerp.
 __device__ float group_quantile(const float* v, int n, float q) {
@@ -67,7 +81,22 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
     const int gs = GS ? GS : a.group_size;
     const long long per_side = (long long)a.B * a.Hkv * a.T * G;
     long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= p.nsides * per_side) return;
+    if (gid >= p.nsides * per_side) {
+        // ---- query rows: rotate and store, nothing to quantize
+        gid -= p.nsides * per_side;
+        if (gid >= p.q_items) return;
+        const int g = (int)(gid % G);
+        long long r = gid / G;
+        const int t = (int)(r % a.T); r /= a.T;
+        const int h = (int)(r % a.Hq);
+        const int b = (int)(r / a.Hq);
+        const __half* row = (const __half*)a.q_src + b * a.q_stride_b + h * a.q_stride_h + t * a.q_stride_t;
+        const __half* cs = (const __half*)a.rope_cos + b * a.rope_stride_b + t * a.rope_stride_t;
+        const __half* sn = (const __half*)a.rope_sin + b * a.rope_stride_b + t * a.rope_stride_t;
+        __half* dst = (__half*)a.q_out + b * a.qo_stride_b + h * a.qo_stride_h + t * a.qo_stride_t;
+        for (int i = g * gs; i < (g + 1) * gs; ++i) dst[i] = rope_one(row, cs, sn, a.rotary_dim, i);
+        return;
+    }
     const int sidx = gid >= per_side;
     if (sidx) gid -= per_side;
     const KvqAppendSide& sd = sidx ? a.v : a.k;
@@ -81,11 +110,17 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
 
     const __half* src = (const __half*)sd.src + b * sd.src_stride_b + h * sd.src_stride_h +
                         t * sd.src_stride_t + g * gs;
+    // rotary embedding applies to the K side only
+    const bool rope = a.rope_cos != nullptr && sidx == 0;
+    const __half* rcos = rope ? (const __half*)a.rope_cos + b * a.rope_stride_b + t * a.rope_stride_t : nullptr;
+    const __half* rsin = rope ? (const __half*)a.rope_sin + b * a.rope_stride_b + t * a.rope_stride_t : nullptr;
     char* pay = (char*)sd.payload + b * sd.pay_stride_b + h * sd.pay_stride_h + pos * sd.pay_stride_s;
 
     if (FMT == KVQ_FMT_FP16) {
         __half* dst = (__half*)pay + g * gs;
-        if (GS) {
+        if (rope) {
+            for (int i = 0; i < gs; ++i) dst[i] = rope_one(src - g * gs, rcos, rsin, a.rotary_dim, g * gs + i);
+        } else if (GS) {
 #pragma unroll
             for (int i = 0; i < (GS ? GS : 8); i += 8) *(uint4*)(dst + i) = *(const uint4*)(src + i);
         } else {
@@ -108,13 +143,40 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
         }
     }
 
+    if (GS && rope && g * gs < a.rotary_dim) {
+        // the launcher only takes this path when rotary_dim is a multiple of 2 * GS: the partner
+        // channels are one whole group, rotary_dim / 2 away
+        const int hf = a.rotary_dim >> 1;
+        const bool low = g * gs < hf;
+        const __half* prt = src + (low ? hf : -hf);
+        const __half* cs = rcos + g * gs;
+        const __half* sn = rsin + g * gs;
+#pragma unroll
+        for (int i = 0; i < (GS ? GS : 8); i += 8) {
+            const uint4 pv = *(const uint4*)(prt + i), cv = *(const uint4*)(cs + i), sv = *(const uint4*)(sn + i);
+            const __half* ph = reinterpret_cast<const __half*>(&pv);
+            const __half* ch = reinterpret_cast<const __half*>(&cv);
+            const __half* sh = reinterpret_cast<const __half*>(&sv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const __half x = __float2half_rn(xr[GS ? i + j : 0]);            // exact: it came from fp16
+                const __half partner = low ? __hneg(ph[j]) : ph[j];
+                xr[GS ? i + j : 0] = h2f(__hadd_rn(__hmul_rn(x, ch[j]), __hmul_rn(partner, sh[j])));
+            }
+        }
+    }
+    // the value the quantizer sees for channel i of this group, before outlier handling
+    auto raw = [&](int i) -> __half {
+        return rope ? rope_one(src - g * gs, rcos, rsin, a.rotary_dim, g * gs + i) : src[i];
+    };
+
     // outlier channels of this head that fall in this group: copy raw, treat as 0
     const int16_t* oidx = a.n_out ? a.outlier_idx + h * a.n_out : nullptr;
     if (oidx && sd.side) {
         __half* side = (__half*)sd.side + b * sd.side_stride_b + h * sd.side_stride_h + pos * sd.side_stride_s;
         for (int j = 0; j < a.n_out; ++j) {
             int ch = oidx[j] - g * gs;
-            if (ch >= 0 && ch < gs) side[j] = src[ch];
+            if (ch >= 0 && ch < gs) side[j] = raw(ch);
         }
     }
     if (GS && oidx) {
@@ -131,7 +193,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
             for (int j = 0; j < a.n_out; ++j)
                 if (oidx[j] == g * gs + i) return 0.0f;
         }
-        return h2f(src[i]);
+        return h2f(raw(i));
     };
 
     const long long sc_off = b * sd.sc_stride_b + h * sd.sc_stride_h + pos * sd.sc_stride_s + g;
@@ -245,7 +307,7 @@ static bool side_vec_ok(const KvqAppendSide& s) {
 
 template <int FMT, int POLICY, int GS>
 static int launch_gs(const QuantParams& p, cudaStream_t st) {
-    const long long threads = (long long)p.nsides * p.a.B * p.a.Hkv * p.a.T * p.G;
+    const long long threads = (long long)p.nsides * p.a.B * p.a.Hkv * p.a.T * p.G + p.q_items;
     if (threads == 0) return KVQ_OK;
     const int block = 128;
     const long long grid = (threads + block - 1) / block;
@@ -257,7 +319,10 @@ static int launch_gs(const QuantParams& p, cudaStream_t st) {
 template <int FMT, int POLICY>
 static int launch(const QuantParams& p, cudaStream_t st) {
     const bool dyn_sort = POLICY == KVQ_SCALE_DYNAMIC_PCT && p.a.quantile < 1.0f;   // needs the sortable copy
-    if (p.a.group_size == 32 && !dyn_sort && side_vec_ok(p.a.k) && side_vec_ok(p.a.v))
+    const KvqAppendArgs& a = p.a;
+    const bool rope_vec_ok = !a.rope_cos || ((a.rotary_dim % 64) == 0 && ((((uintptr_t)a.rope_cos | (uintptr_t)a.rope_sin) & 15) == 0) &&
+                                             (a.rope_stride_b & 7) == 0 && (a.rope_stride_t & 7) == 0);
+    if (p.a.group_size == 32 && !dyn_sort && side_vec_ok(p.a.k) && side_vec_ok(p.a.v) && rope_vec_ok)
         return launch_gs<FMT, POLICY, 32>(p, st);
     return launch_gs<FMT, POLICY, 0>(p, st);
 }
@@ -295,6 +360,14 @@ extern "C" int kvq_quantize_append(const KvqAppendArgs* args, kvq_stream_t strea
     p.a.group_size = gs;
     p.G = a.D / gs;
     p.nsides = a.v.src ? 2 : 1;
+    p.q_items = 0;
+    if (a.rope_cos || a.rope_sin) {
+        if (!a.rope_cos || !a.rope_sin || a.rotary_dim <= 0 || (a.rotary_dim & 1) || a.rotary_dim > a.D) return KVQ_EINVAL;
+    }
+    if (a.q_src) {
+        if (!a.rope_cos || !a.q_out || a.Hq <= 0) return KVQ_EINVAL;
+        p.q_items = (long long)a.B * a.Hq * a.T * p.G;
+    }
     if (!side_ok(a.k, p.a) || (p.nsides == 2 && !side_ok(a.v, p.a))) return KVQ_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
 #define KVQ_DISPATCH(F, P) if (a.format == F && a.policy == P) return launch<F, P>(p, st);

@@ -281,10 +281,15 @@ def _fused_forward_impl(self, hidden_states, cache_wrapper, attention_mask=None,
     if cos is None or sin is None:
         raise RuntimeError("Failed to obtain RoPE cos/sin for fused decode. "
                            "Check transformers version/model API (position_ids/position_embeddings).")
-    query_states, key_states = _apply_rope(query_states, key_states, cos, sin)
     inv_tau = _layer_inv_tau(engine, layer_idx, q_heads, query_states.device)
-
-    engine.append(layer_idx, key_states, value_states)
+    fused_rope = (getattr(engine, "supports_fused_rope", None) is not None and engine.supports_fused_rope()
+                  and query_states.dtype == torch.float16 and os.environ.get("KVQ_NO_FUSED_ROPE", "0") != "1")
+    if fused_rope:
+        # RoPE of q and k, quantization of k and v and the cache write: one launch
+        query_states = engine.append_rotary(layer_idx, query_states, key_states, value_states, cos, sin)
+    else:
+        query_states, key_states = _apply_rope(query_states, key_states, cos, sin)
+        engine.append(layer_idx, key_states, value_states)
 
     q_kernel = query_states.squeeze(2)
     sm_scale = float(getattr(self, "scaling", 1.0 / (head_dim ** 0.5)))

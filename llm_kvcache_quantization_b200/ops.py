@@ -110,10 +110,16 @@ def quantize_append(fmt: int, policy: int, k_new: torch.Tensor, v_new: torch.Ten
                     k_zp=None, v_zp=None, k_scale_f32=None, v_scale_f32=None,
                     k_static=None, v_static=None, flags: int = 0, adaptive_margin: float = 1.0,
                     quantile: float = 1.0, k_rescue_thr=None, v_rescue_thr=None,
-                    outlier_idx=None, k_side=None, v_side=None) -> None:
+                    outlier_idx=None, k_side=None, v_side=None,
+                    rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
+                    q: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None):
     """Quantize `k_new`, `v_new` ([B,Hkv,T,D] fp16) into cache slots
     [write_pos, write_pos+T) of the given payload / scale buffers in one launch (`v_new=None`: K side only).
-    `write_pos` is an int or an int32 device tensor (read on the device)."""
+    `write_pos` is an int or an int32 device tensor (read on the device).
+
+    With `rope_cos` / `rope_sin` (fp16 [B or 1, T, rotary_dim]) the same launch applies rotate-half
+    RoPE to K before quantizing it and, when `q` ([B,Hq,T,D] fp16, before rotation) is given, to the
+    query; the rotated query is returned (`q_out` or a new tensor)."""
     dev = _require_cuda(k_new, v_new, k_payload, v_payload, k_scale, v_scale)
     if k_new.dtype != torch.float16 or (v_new is not None and v_new.dtype != torch.float16):
         raise ValueError("quantize_append expects fp16 K/V")
@@ -143,9 +149,41 @@ def quantize_append(fmt: int, policy: int, k_new: torch.Tensor, v_new: torch.Ten
     a.k = _append_side(k_new, k_payload, k_scale, k_zp, k_scale_f32, k_side, k_static, k_rescue_thr)
     if v_new is not None:
         a.v = _append_side(v_new, v_payload, v_scale, v_zp, v_scale_f32, v_side, v_static, v_rescue_thr)
+    if (rope_cos is None) != (rope_sin is None):
+        raise ValueError("rope_cos and rope_sin go together")
+    if q is not None and rope_cos is None:
+        raise ValueError("a query is only taken together with rope_cos / rope_sin")
+    if rope_cos is not None:
+        for name, t in (("rope_cos", rope_cos), ("rope_sin", rope_sin)):
+            if t.dtype != torch.float16 or t.ndim != 3 or t.stride(-1) != 1 or t.shape[1] != T or \
+                    t.shape[0] not in (1, B) or not t.is_cuda:
+                raise ValueError(f"{name} must be an fp16 CUDA tensor [B or 1, T, rotary_dim]")
+        if rope_cos.shape != rope_sin.shape or rope_cos.stride() != rope_sin.stride():
+            raise ValueError("rope_cos / rope_sin must share shape and strides")
+        rd = rope_cos.shape[-1]
+        if rd % 2 or rd > D:
+            raise ValueError(f"RoPE dim {rd} must be even and <= head_dim {D}")
+        a.rope_cos, a.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
+        a.rope_stride_b = 0 if rope_cos.shape[0] == 1 else rope_cos.stride(0)
+        a.rope_stride_t = rope_cos.stride(1)
+        a.rotary_dim = rd
+        if q is not None:
+            if q.dtype != torch.float16 or q.ndim != 4 or q.shape[0] != B or q.shape[2] != T or q.shape[3] != D or \
+                    q.stride(-1) != 1:
+                raise ValueError("q must be fp16 [B, Hq, T, D], contiguous in head_dim")
+            if q_out is None:
+                q_out = torch.empty((B, q.shape[1], T, D), dtype=torch.float16, device=dev)
+            elif q_out.shape != q.shape or q_out.dtype != torch.float16 or q_out.stride(-1) != 1:
+                raise ValueError("q_out must match q")
+            a.Hq = q.shape[1]
+            a.q_src = q.data_ptr()
+            a.q_stride_b, a.q_stride_h, a.q_stride_t = q.stride(0), q.stride(1), q.stride(2)
+            a.q_out = q_out.data_ptr()
+            a.qo_stride_b, a.qo_stride_h, a.qo_stride_t = q_out.stride(0), q_out.stride(1), q_out.stride(2)
     with torch.cuda.device(dev):
         rc = _lib.load().kvq_quantize_append(C.byref(a), _stream_ptr(dev))
     _lib.check("kvq_quantize_append", rc)
+    return q_out
 
 
 # --------------------------------------------------------------------------- attention
@@ -259,6 +297,42 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     if return_partial:
         return out, part
     return out
+
+
+def dequantize(fmt: int, k_payload: torch.Tensor, v_payload: Optional[torch.Tensor], k_scale: torch.Tensor,
+               v_scale: Optional[torch.Tensor], *, k_zp=None, v_zp=None, outlier_idx=None, k_side=None, v_side=None):
+    """Quantized cache views -> fp16 [B,Hkv,S,D] (K and V in one launch; V optional).
+    Values are RN16(code * scale) (+ zero-point, rounded again); outlier channels take the side value."""
+    dev = _require_cuda(k_payload, v_payload, k_scale, v_scale)
+    if k_payload.dtype != torch.int8 or k_scale.dtype != torch.float16:
+        raise ValueError("dequantize expects an int8 payload and fp16 scales")
+    B, H, S, Dp = k_payload.shape
+    D = Dp * 2 if fmt == _lib.FMT_INT4 else Dp
+    a = _lib.KvqDequantArgs()
+    a.format, a.B, a.Hkv, a.S, a.D = fmt, B, H, S, D
+    a.group_size = D // k_scale.shape[-1]
+    if k_payload.stride(-1) != 1 or (v_payload is not None and v_payload.stride(-1) != 1):
+        raise ValueError("payload last dimension must be contiguous")
+    a.k = _cache_side(k_payload, k_scale, k_zp, k_side)
+    k_out = torch.empty((B, H, S, D), dtype=torch.float16, device=dev)
+    a.k_out = k_out.data_ptr()
+    v_out = None
+    if v_payload is not None:
+        if v_payload.shape != k_payload.shape:
+            raise ValueError("k / v payload shapes differ")
+        a.v = _cache_side(v_payload, v_scale, v_zp, v_side)
+        v_out = torch.empty_like(k_out)
+        a.v_out = v_out.data_ptr()
+    a.out_stride_b, a.out_stride_h, a.out_stride_s = k_out.stride(0), k_out.stride(1), k_out.stride(2)
+    if outlier_idx is not None:
+        if outlier_idx.dtype != torch.int16 or not outlier_idx.is_contiguous() or outlier_idx.shape[0] != H:
+            raise ValueError("outlier_idx must be a contiguous int16 [Hkv, n_out] tensor")
+        a.n_out = outlier_idx.shape[1]
+        a.outlier_idx = outlier_idx.data_ptr()
+    with torch.cuda.device(dev):
+        rc = _lib.load().kvq_dequantize(C.byref(a), _stream_ptr(dev))
+    _lib.check("kvq_dequantize", rc)
+    return k_out, v_out
 
 
 def decode_kernel_kind(fmt: int, q, k_payload, v_payload, k_scale, v_scale, *, k_zp=None, v_zp=None,

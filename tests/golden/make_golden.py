@@ -7,7 +7,7 @@ Usage (only where the reference checkout is available):
 
 The reference's own classes and functions are imported unmodified
 (`INT8KVCache`, `INT4KVCache`, `quantize_asymmetric`, `pack_int4`,
-`_decode_attn_int8_torch_ref`) and driven on seeded inputs on CPU; inputs and
+`_decode_attn_int8_torch_ref`, `_apply_rope`) and driven on seeded inputs on CPU; inputs and
 outputs are stored as small `.npz` files.  The fixtures travel with the
 repository, the reference does not.
 """
@@ -38,12 +38,47 @@ def gen_kv(gen, b, h, s, d, outlier_ch=0, outlier_mag=20.0, chan_std=False):
     return x.to(torch.float16)
 
 
+def make_rope():
+    """Rotate-half RoPE of the patched forward (src/engine/patch_model.py:223-278) in fp16 on CPU:
+    full and partial rotary dims, cos/sin of rank 2, 3 and 4, batch-shared and per-row tables."""
+    from src.engine.patch_model import _apply_rope
+    gen = torch.Generator().manual_seed(20261126)
+    out = {}
+    cases = (("full_r3", 2, 12, 2, 3, 128, 128, 3), ("partial_r3", 2, 6, 2, 1, 128, 64, 3),
+             ("shared_r2", 1, 4, 4, 5, 128, 128, 2), ("decode_r4", 3, 14, 2, 1, 128, 128, 4),
+             ("d64_r3", 2, 4, 2, 2, 64, 64, 3))
+    for name, b, hq, hkv, t, d, rd, rank in cases:
+        q = (torch.randn(b, hq, t, d, generator=gen) * 2).half()
+        k = (torch.randn(b, hkv, t, d, generator=gen) * 2).half()
+        pos = torch.randint(0, 4096, (b, t), generator=gen).float()
+        inv_freq = 1.0 / (10000.0 ** (torch.arange(0, rd, 2).float() / rd))
+        ang = pos[..., None] * inv_freq                       # [b, t, rd/2]
+        emb = torch.cat([ang, ang], dim=-1)
+        cos, sin = emb.cos().half(), emb.sin().half()         # [b, t, rd]
+        if rank == 2:
+            cos_in, sin_in = cos[0], sin[0]                   # [t, rd], shared by the batch (b == 1)
+        elif rank == 4:
+            cos_in, sin_in = cos[:, None], sin[:, None]
+        else:
+            cos_in, sin_in = cos, sin
+        q_emb, k_emb = _apply_rope(q, k, cos_in, sin_in)
+        out[f"{name}_q"] = _np(q); out[f"{name}_k"] = _np(k)
+        out[f"{name}_cos"] = _np(cos_in); out[f"{name}_sin"] = _np(sin_in)
+        out[f"{name}_q_out"] = _np(q_emb); out[f"{name}_k_out"] = _np(k_emb)
+    np.savez_compressed(os.path.join(HERE, "rope.npz"), **out)
+    print("rope.npz", os.path.getsize(os.path.join(HERE, "rope.npz")) // 1024, "KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default="", help="'rope' regenerates rope.npz alone")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     warnings.simplefilter("ignore")
+    if args.only == "rope":
+        make_rope()
+        return
 
     from src.cache.int8_cache import INT8KVCache
     from src.cache.int4_cache import INT4KVCache
@@ -178,6 +213,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "attention.npz"), **att)
     for f in ("quantizers.npz", "pack_int4.npz", "attention.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
+    make_rope()
 
 
 if __name__ == "__main__":

@@ -31,7 +31,7 @@ def test_header_symbols_all_exported(lib):
 
 
 def test_abi_version_and_strerror(lib):
-    assert lib.kvq_abi_version() == 1
+    assert lib.kvq_abi_version() == 2
     assert lib.kvq_strerror(0) == b"ok"
     assert b"invalid" in lib.kvq_strerror(-1)
 
@@ -55,6 +55,7 @@ def test_struct_sizes_match_header(lib):
     # all fields are 4- or 8-byte scalars/pointers: natural alignment, no packing pragma
     assert ctypes.sizeof(_lib.KvqCacheSide) == 13 * 8
     assert ctypes.sizeof(_lib.KvqCombineArgs) == 4 * 4 + 10 * 8
+    assert ctypes.sizeof(_lib.KvqDequantArgs) == 8 * 4 + 8 + 2 * 13 * 8 + 5 * 8
 
 
 def test_cpu_tensors_raise_value_error():

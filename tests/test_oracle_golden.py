@@ -138,3 +138,17 @@ def test_lse_merge_matches_full():
         parts.append((o.astype(np.float32), m, l))
     merged = O.lse_merge([p[0] for p in parts], [p[1] for p in parts], [p[2] for p in parts])
     assert np.allclose(merged.astype(np.float32), full.astype(np.float32), atol=2e-3, rtol=1e-2)
+
+
+ROPE_CASES = ("full_r3", "partial_r3", "shared_r2", "decode_r4", "d64_r3")
+
+
+@pytest.mark.parametrize("name", ROPE_CASES)
+def test_rope_matches_reference(golden_dir, name):
+    """Rotate-half RoPE restated in numpy fp16 == the reference's _apply_rope, bit for bit."""
+    z = np.load(os.path.join(golden_dir, "rope.npz"))
+    for which in ("q", "k"):
+        got = O.apply_rope(z[f"{name}_{which}"], z[f"{name}_cos"], z[f"{name}_sin"])
+        ref = z[f"{name}_{which}_out"]
+        assert got.dtype == np.float16 and got.shape == ref.shape
+        assert np.array_equal(got.view(np.uint16), ref.view(np.uint16)), f"{name} {which}"
