@@ -10,6 +10,9 @@ Default workload is configuration 2 of BASELINE.json (Qwen2.5-1.5B geometry, 28
 layers, batch 16, context 8192, INT4 asymmetric group-32 with fp16 scale and
 zero-point).  With N > 1 the batch is sharded by sequence: every rank owns its own
 batch of sequences and its own cache, no collective on the data path (weak scaling).
+The single-sequence workload c5 with N > 1 shards the KV sequence instead: every rank
+scans its contiguous chunk, the packed partials cross NVLink in one NCCL all-gather per
+layer and are merged on every rank (strong scaling: the total work is fixed).
 
 Prints ONE JSON line (rank 0).
 """
@@ -323,6 +326,145 @@ def workload_config(wl, name):
             else "L2 flushed between timed iterations by a 256 MB write"}
 
 
+
+# --------------------------------------------------------------------------- sequence sharding (one long sequence)
+def run_sequence_sharded(args, wl, dev, dist, rank, world):
+    """KV-sequence sharding of a single long sequence over `world` GPUs: rank r owns a contiguous
+    chunk of tokens, the owner of position S appends the new token, every rank runs the fused
+    decode over its chunk into a packed normalised partial, ONE NCCL all-gather per layer moves the
+    partials, and every rank merges them.  The whole step (kernels and collectives) is one CUDA graph."""
+    import torch
+    from llm_kvcache_quantization_b200 import ops, _lib, parallel as P
+
+    L, B, Hq, Hkv, S, kind, n_out = (wl[k] for k in ("layers", "B", "Hq", "Hkv", "S", "kind", "n_out"))
+    sh = P.SequenceSharding(world=world, max_seq_len=S + 1)
+    lo, hi = sh.token_range(rank)
+    n_old = sh.local_len(rank, S)                    # cached tokens of this rank before the step
+    owner = sh.owner_of(S) == rank                   # this rank stores the new token
+    n_att = n_old + (1 if owner else 0)
+    local = dict(wl, S=n_old)
+    # same seed on every rank for q / k_new / v_new would need a shared generator; the inputs of a step are
+    # replicated in a real deployment, here rank 0's are broadcast
+    cache, q, k_new, v_new, inv_tau = build_workload(local, dev, seed=1234 + rank, extra_slots=8)
+    for t in (q, k_new, v_new, inv_tau):
+        dist.broadcast(t, src=0)
+    fmt = _lib.FMT_INT8 if kind.startswith("int8") else _lib.FMT_INT4
+    out = torch.empty(L, B, Hq, D, dtype=torch.float16, device=dev)
+    send = torch.empty(B, Hq, D + 2, dtype=torch.float32, device=dev)
+    recv = torch.empty(world, B, Hq, D + 2, dtype=torch.float32, device=dev)
+    P.check_partial_shapes(send.shape)
+    layers = []
+    for l in range(L):
+        b = cache._bufs[l]
+        tens = dict(b)
+        tens["outlier_idx"] = None if cache.outlier_idx is None else cache.outlier_idx[l].contiguous()
+        app = dict(k_zp=b.get("kz"), v_zp=b.get("vz"))
+        if kind == "int4_asym":
+            policy = _lib.SCALE_ASYM_MINMAX
+        elif kind == "int8_dyn":
+            policy = _lib.SCALE_DYNAMIC_PCT
+            app.update(quantile=1.0)
+        else:
+            policy = _lib.SCALE_STATIC
+            app.update(k_static=cache._static_table("k", l, Hkv, G, dev), v_static=cache._static_table("v", l, Hkv, G, dev))
+        if tens["outlier_idx"] is not None:
+            app.update(outlier_idx=tens["outlier_idx"], k_side=b["kside"], v_side=b["vside"])
+        layers.append((b, tens, policy, app))
+
+    def step(scan_only=False):
+        for l, (b, tens, policy, app) in enumerate(layers):
+            if scan_only:
+                extra = {}
+                if tens.get("kz") is not None:
+                    extra.update(k_zp=tens["kz"][:, :, :n_att], v_zp=tens["vz"][:, :, :n_att])
+                if tens["outlier_idx"] is not None:
+                    extra.update(outlier_idx=tens["outlier_idx"], k_side=tens["kside"][:, :, :n_att],
+                                 v_side=tens["vside"][:, :, :n_att])
+                ops.decode_attn(fmt, q[l], tens["k"][:, :, :n_att], tens["v"][:, :, :n_att], tens["ks"][:, :, :n_att],
+                                tens["vs"][:, :, :n_att], None, 1.0 / D ** 0.5, head_dim=D, inv_tau=inv_tau[l],
+                                out=out[l], stages=1, **extra)
+                continue
+            if owner:
+                ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], n_old, GS, **app)
+            P.sharded_decode(fmt, q[l], tens, n_att, 1.0 / D ** 0.5, send=send, recv=recv, inv_tau=inv_tau[l], out=out[l])
+
+    g_step = capture(step)
+    splits = ops.last_splits()
+    g_scan = capture(lambda: step(scan_only=True))
+    time_graph(g_step, args.warmup, dist)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    ms = time_graph(g_step, args.steps, dist)
+    time_graph(g_scan, 3, dist)
+    ms_scan = time_graph(g_scan, args.steps, dist)
+    clocks = sampler.stop()
+
+    # end to end with host buffers: upload q / k / v of the token, replay, download the merged output
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k_new, v_new))
+    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def host_step():
+        q.copy_(hq, non_blocking=True); k_new.copy_(hk, non_blocking=True); v_new.copy_(hv, non_blocking=True)
+        g_step.replay()
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        host_step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier(); torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        host_step()
+    e1.record(); torch.cuda.synchronize()
+    t = torch.tensor([ms, ms_scan, e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_scan, ems = (float(x) for x in t)
+    ms_per_step = ms / args.steps
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    alg_bytes = B * Hkv * sh.chunk * bytes_per_token_head(kind, n_out)       # the largest shard
+    scan_us = ms_scan / (args.steps * L) * 1e3
+    achieved = alg_bytes / (scan_us * 1e-6) / 1e9
+    if rank == 0:
+        line = {
+            "metric": "decode_tokens_per_s", "value": B / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": dict(workload_config(wl, args.workload), parallelism=f"sequence-sharded x{world}",
+                           chunk_tokens=sh.chunk, splits=splits,
+                           collective="one NCCL all-gather of [B,Hq,D+2] fp32 per layer",
+                           step=f"CUDA graph (kernels + NCCL all-gather) of {L}x(append on the owner, split-K scan, "
+                                "combine, all-gather, merge)"),
+            "us_per_layer": ms_per_step * 1e3 / L,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": alg_bytes * NCU_TRAFFIC_RATIO.get(kind, 1.0),
+                         "traffic_source": "ncu capture of the same kernel (profiles/), scaled by token-heads",
+                         "peak_source": peak_src, "kernel": "decode split-K scan (largest shard, per GPU)",
+                         "us_per_launch": scan_us, "algorithmic_bytes_per_launch": alg_bytes,
+                         "frac_of_8TBps": achieved / 8000.0},
+            "cpu_baseline": None,
+            "e2e": {"value": B / (ems / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": (q.numel() + k_new.numel() + v_new.numel()) * 2,
+                    "d2h_bytes_per_step": out.numel() * 2, "ms_per_step": ems / args.steps,
+                    "api": "pinned H2D of q/k/v on every rank, one CUDA graph (sharded_decode per layer), pinned D2H"},
+            "gpu_launches": args.steps * L * 4, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    # Tearing the process group down while captured graphs still hold its collectives did not return in a
+    # two-GPU run: drain, agree that every rank is done, drop the graphs, and leave without the teardown.
+    torch.cuda.synchronize()
+    dist.barrier()
+    del g_step, g_scan
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 # --------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -345,21 +487,26 @@ def main():
         run_reference_arm(args, wl)
         return
 
-    import torch
-    import llm_kvcache_quantization_b200 as kvq
-    from llm_kvcache_quantization_b200 import ops
-
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    import torch
+    import llm_kvcache_quantization_b200 as kvq
+    from llm_kvcache_quantization_b200 import ops
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist_mod.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a collective that a peer never joins ends with an error after two minutes instead of waiting forever
+        dist_mod.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
         dist = dist_mod
+
+    if world > 1 and wl["B"] == 1:
+        run_sequence_sharded(args, wl, dev, dist, rank, world)
+        return
 
     L, B, Hq, Hkv, S = wl["layers"], wl["B"], wl["Hq"], wl["Hkv"], wl["S"]
     e2e_slots = args.steps + args.warmup + 8
