@@ -237,6 +237,39 @@ typedef struct KvqCombineArgs {
 KVQ_API int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream);
 
 /*
+ * Sequence-sharded decode, fused exchange: merge this rank's KV splits (the partials that
+ * kvq_decode_attn with stages = 1 left in `workspace`), store the normalised partial of every
+ * (batch, head) row into every rank's receive buffer with plain peer stores over NVLink, wait
+ * (bounded) for the other ranks' rows, and merge the `world` partials into `out` - one launch in
+ * place of combine + all-gather + kvq_lse_combine.  No counterpart in the reference (single GPU).
+ *
+ * Every rank owns one receive buffer of kvq_exchange_bytes(...) bytes, zero-filled before the first
+ * use and mapped into every peer (`peer_base[q]` = rank q's buffer as seen from this process; CUDA
+ * IPC / symmetric memory; peer_base[rank] is the local buffer).  `slots` independent exchanges
+ * (e.g. one per layer) share the buffer; `*epoch` must be >= 1, equal on all ranks, and advance by
+ * one between two uses of the same slot.  Ranks must launch the same sequence of exchanges.
+ * One process per GPU: a rank never waits for work of its own GPU.
+ */
+#define KVQ_MAX_PEERS 16
+typedef struct KvqExchangeArgs {
+    int32_t B, Hq, D, splits;
+    const void* workspace;       /* split-K partials of this rank                            */
+    size_t  workspace_bytes;
+    int32_t rank, world;         /* world <= KVQ_MAX_PEERS                                   */
+    void* const* peer_base;      /* HOST array [world] of device pointers                    */
+    int32_t slot, slots;
+    const int32_t* epoch;        /* device int32                                             */
+    uint64_t wait_ns;            /* bound of the wait for peers; 0 = one second              */
+    int32_t* status;             /* device int32 or NULL: set to 1 when a wait expired       */
+    void*   out;                 /* fp16 [B, Hq, D]                                          */
+    int64_t out_stride_b, out_stride_h;                 /* elements                      */
+} KvqExchangeArgs;
+
+/* Bytes of one rank's receive buffer; *flags_offset (optional) = where its flag words start. */
+KVQ_API size_t kvq_exchange_bytes(int32_t B, int32_t Hq, int32_t D, int32_t slots, int32_t world, size_t* flags_offset);
+KVQ_API int kvq_combine_exchange(const KvqExchangeArgs* args, kvq_stream_t stream);
+
+/*
  * Dequantise a cache (or a slice of one) back to fp16 [B, Hkv, S, D].
  * Stands in for INT8KVCache.get_kv (src/cache/int8_cache.py:490-542), INT4KVCache.get_kv and
  * to_tuple, i.e. dequantize_symmetric_int8 / dequantize_symmetric_int4

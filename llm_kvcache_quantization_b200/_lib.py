@@ -95,6 +95,21 @@ class KvqDequantArgs(C.Structure):
     ]
 
 
+MAX_PEERS = 16
+
+
+class KvqExchangeArgs(C.Structure):
+    _fields_ = [
+        ("B", _i32), ("Hq", _i32), ("D", _i32), ("splits", _i32),
+        ("workspace", _vp), ("workspace_bytes", C.c_size_t),
+        ("rank", _i32), ("world", _i32),
+        ("peer_base", C.POINTER(_vp)),
+        ("slot", _i32), ("slots", _i32),
+        ("epoch", _vp), ("wait_ns", C.c_uint64), ("status", _vp),
+        ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
+    ]
+
+
 # every symbol include/kvq.h declares: (name, restype, argtypes)
 EXPORTS = (
     ("kvq_quantize_append", C.c_int, (C.POINTER(KvqAppendArgs), _vp)),
@@ -103,6 +118,8 @@ EXPORTS = (
     ("kvq_decode_workspace_bytes", C.c_size_t, (_i32, _i32, _i32, _i32)),
     ("kvq_decode_pick_splits", _i32, (C.POINTER(KvqAttnArgs),)),
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
+    ("kvq_exchange_bytes", C.c_size_t, (_i32, _i32, _i32, _i32, _i32, C.POINTER(C.c_size_t))),
+    ("kvq_combine_exchange", C.c_int, (C.POINTER(KvqExchangeArgs), _vp)),
     ("kvq_dequantize", C.c_int, (C.POINTER(KvqDequantArgs), _vp)),
     ("kvq_debug_error_flag", C.c_int, (C.c_int,)),
     ("kvq_decode_kernel_kind", C.c_int, (C.POINTER(KvqAttnArgs),)),

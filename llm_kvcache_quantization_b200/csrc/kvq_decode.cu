@@ -21,11 +21,11 @@ namespace kvq {
 // channels), and the four warps are added through shared memory.  The loop over
 // splits is latency-bound when run serially; this form keeps it near one round trip.
 // ---------------------------------------------------------------------------
+// Shared front half: leaves the four warps' weighted sums in red[w][0..D) and their
+// denominators in red[w][D]; returns the global max (log2 domain) of the row.
 template <int EPL>   // channels per lane = D / 32
-__global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p) {
-    pdl_wait();                   // the split kernel's partials
+__device__ __forceinline__ float combine_partials(const AttnParams& p, int b, int h, float (*red)[EPL * 32 + 1]) {
     const KvqAttnArgs& a = p.a;
-    const int h = blockIdx.x, b = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int D = EPL * 32;
     const long long row0 = ((long long)b * a.Hq + h) * p.splits;
@@ -66,11 +66,21 @@ __global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p)
             }
         }
     }
-    __shared__ float red[4][D + 1];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) red[warp][lane * EPL + e] = acc[e];
     if (lane == 0) red[warp][D] = L;
     __syncthreads();
+    return M;
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p) {
+    pdl_wait();                   // the split kernel's partials
+    const KvqAttnArgs& a = p.a;
+    const int h = blockIdx.x, b = blockIdx.y;
+    constexpr int D = EPL * 32;
+    __shared__ float red[4][D + 1];
+    const float M = combine_partials<EPL>(p, b, h, red);
     for (int d = threadIdx.x; d < D; d += 128) {
         const float o = red[0][d] + red[1][d] + red[2][d] + red[3][d];
         const float Lt = red[0][D] + red[1][D] + red[2][D] + red[3][D];
@@ -86,6 +96,114 @@ __global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p)
                 a.part_l[idx * sm] = Lt;
             }
         }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Combine fused with the cross-GPU exchange of a sequence-sharded decode: one kernel per
+// rank merges its KV splits into the normalised partial of every (batch, head) row, stores
+// that partial straight into every rank's receive buffer over NVLink (plain peer stores),
+// raises a per-row flag on every rank, waits for the same row of every other rank, and
+// merges the `world` partials into the fp16 output.  It replaces three launches and a
+// library collective (combine, all-gather, merge) by one launch whose transfer overlaps the
+// other rows' arithmetic.
+//
+// Receive buffer of a rank (identical layout on every rank, peer-mapped):
+//   data  fp32 [2 parity][slots][world src][B][Hq][D + 2]   rows [o (D) | m | l]
+//   flags int32 [2 parity][slots][world src][B][Hq]          = epoch of the row's last write
+// `epoch` (device int, >= 1) is advanced once per decode step by the host side; parity =
+// epoch & 1 double-buffers the rows so that a rank one step ahead never overwrites a row a
+// slower rank still reads.  Progress never depends on another CTA of the same GPU: a CTA
+// pushes before it waits, and waits only for remote CTAs.  The wait is bounded by
+// `wait_ns`; on expiry the CTA raises *status and finishes with what it has.
+// ---------------------------------------------------------------------------
+struct ExchangeParams {
+    AttnParams p;
+    KvqExchangeArgs x;
+    float* recv[KVQ_MAX_PEERS];
+    int* flags[KVQ_MAX_PEERS];
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(128) combine_exchange_kernel(const ExchangeParams ep) {
+    pdl_wait();
+    const AttnParams& p = ep.p;
+    const KvqExchangeArgs& x = ep.x;
+    const KvqAttnArgs& a = p.a;
+    const int h = blockIdx.x, b = blockIdx.y;
+    constexpr int D = EPL * 32;
+    constexpr int W = D + 2;
+    __shared__ float red[4][D + 1];
+    __shared__ float pm[KVQ_MAX_PEERS], pl[KVQ_MAX_PEERS];
+    const float M = combine_partials<EPL>(p, b, h, red);
+
+    const int epoch = *x.epoch;
+    const long long rows = (long long)a.B * a.Hq;
+    const long long slot_base = ((long long)(epoch & 1) * x.slots + x.slot) * x.world;     // in units of `rows`
+    const long long my_row = (slot_base + x.rank) * rows + (long long)b * a.Hq + h;
+
+    // ---- push this rank's normalised partial of the row to every rank (itself included)
+    const float Lt = red[0][D] + red[1][D] + red[2][D] + red[3][D];
+    for (int d = threadIdx.x; d < D; d += 128) {
+        const float o = red[0][d] + red[1][d] + red[2][d] + red[3][d];
+        const float r = (Lt > 0.f) ? o / Lt : 0.f;
+        for (int q = 0; q < x.world; ++q) ep.recv[q][my_row * W + d] = r;
+    }
+    if (threadIdx.x < x.world) {
+        float* dst = ep.recv[threadIdx.x] + my_row * W + D;
+        dst[0] = (Lt > 0.f) ? M * 0.6931471805599453f : -INFINITY;
+        dst[1] = Lt;
+    }
+    __syncthreads();
+    if (threadIdx.x < x.world) {
+        __threadfence_system();
+        st_release_sys(ep.flags[threadIdx.x] + my_row, epoch);
+    }
+
+    // ---- wait for the same row from every rank (bounded), then merge
+    if (threadIdx.x < x.world) {
+        const long long src_row = (slot_base + threadIdx.x) * rows + (long long)b * a.Hq + h;
+        const int* f = ep.flags[x.rank] + src_row;
+        const unsigned long long t0 = global_ns();
+        bool ok = true;
+        while (ld_acquire_sys(f) != epoch) {
+            if (global_ns() - t0 > x.wait_ns) { ok = false; break; }
+            __nanosleep(100);
+        }
+        if (!ok && x.status) atomicExch(x.status, 1);
+        const float* src = ep.recv[x.rank] + src_row * W + D;
+        pm[threadIdx.x] = ok ? __ldcg(src) : -INFINITY;
+        pl[threadIdx.x] = ok ? __ldcg(src + 1) : 0.f;
+    }
+    __syncthreads();
+    float Mx = -INFINITY;
+    for (int q = 0; q < x.world; ++q)
+        if (pl[q] > 0.f) Mx = fmaxf(Mx, pm[q]);
+    for (int d = threadIdx.x; d < D; d += 128) {
+        float num = 0.f, den = 0.f;
+        for (int q = 0; q < x.world; ++q) {
+            if (pl[q] > 0.f) {
+                const float w = pl[q] * expf(pm[q] - Mx);
+                num += __ldcg(ep.recv[x.rank] + ((slot_base + q) * rows + (long long)b * a.Hq + h) * W + d) * w;
+                den += w;
+            }
+        }
+        const float r = den > 0.f ? num / den : 0.f;
+        ((__half*)x.out)[b * x.out_stride_b + h * x.out_stride_h + d] = __float2half_rn(r);
     }
 }
 
@@ -537,6 +655,52 @@ extern "C" int kvq_decode_attn_static(const KvqAttnArgs* args, kvq_stream_t stre
     a.workspace = ws;
     a.workspace_bytes = KVQ_STATIC_WS_BYTES;
     return kvq_decode_attn(&a, stream);
+}
+
+extern "C" size_t kvq_exchange_bytes(int32_t B, int32_t Hq, int32_t D, int32_t slots, int32_t world, size_t* flags_offset) {
+    if (B <= 0 || Hq <= 0 || D <= 0 || slots <= 0 || world <= 0) return 0;
+    const size_t rows = (size_t)2 * slots * world * B * Hq;
+    size_t data = rows * (D + 2) * sizeof(float);
+    data = (data + 255) & ~(size_t)255;
+    if (flags_offset) *flags_offset = data;
+    return data + ((rows * sizeof(int32_t) + 255) & ~(size_t)255);
+}
+
+extern "C" int kvq_combine_exchange(const KvqExchangeArgs* args, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!args) return KVQ_EINVAL;
+    const KvqExchangeArgs& x = *args;
+    if (x.B < 0 || x.Hq <= 0 || x.splits <= 0 || x.slots <= 0 || x.slot < 0 || x.slot >= x.slots) return KVQ_EINVAL;
+    if (x.world < 1 || x.world > KVQ_MAX_PEERS || x.rank < 0 || x.rank >= x.world) return KVQ_EINVAL;
+    if (x.D != 64 && x.D != 128 && x.D != 256) return KVQ_EUNSUPPORTED;
+    if (x.B == 0) return KVQ_OK;
+    if (!x.peer_base || !x.epoch || !x.out || !x.workspace) return KVQ_EINVAL;
+    const size_t need = kvq_decode_workspace_bytes(x.B, x.Hq, x.D, x.splits);
+    if (x.workspace_bytes < need || (((uintptr_t)x.workspace) & 15)) return KVQ_EWORKSPACE;
+    size_t flags_off = 0;
+    kvq_exchange_bytes(x.B, x.Hq, x.D, x.slots, x.world, &flags_off);
+    ExchangeParams ep;
+    ep.x = x;
+    ep.p.a = KvqAttnArgs();
+    ep.p.a.B = x.B; ep.p.a.Hq = x.Hq; ep.p.a.D = x.D;
+    ep.p.splits = x.splits;
+    const size_t o_bytes = ((size_t)x.B * x.Hq * x.splits * x.D * sizeof(float) + 255) & ~(size_t)255;
+    ep.p.ws_o = (float*)x.workspace;
+    ep.p.ws_ml = (float*)((char*)x.workspace + o_bytes);
+    for (int q = 0; q < KVQ_MAX_PEERS; ++q) {
+        char* base = q < x.world ? (char*)x.peer_base[q] : nullptr;
+        if (q < x.world && (!base || ((uintptr_t)base & 15))) return KVQ_EINVAL;
+        ep.recv[q] = (float*)base;
+        ep.flags[q] = base ? (int*)(base + flags_off) : nullptr;
+    }
+    if (ep.x.wait_ns == 0) ep.x.wait_ns = 1000000000ull;       // one second
+    dim3 grid(x.Hq, x.B);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x.D) {
+        case 64: return launch_pdl(combine_exchange_kernel<2>, grid, dim3(128), 0, st, ep);
+        case 128: return launch_pdl(combine_exchange_kernel<4>, grid, dim3(128), 0, st, ep);
+        default: return launch_pdl(combine_exchange_kernel<8>, grid, dim3(128), 0, st, ep);
+    }
 }
 
 extern "C" int kvq_debug_error_flag(int reset) {

@@ -299,6 +299,58 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     return out
 
 
+def neutral_partial(B: int, Hq: int, D: int, dev) -> None:
+    """Fill the split-K workspace with ONE empty split per (batch, head) row (o = 0, m = -inf, l = 0):
+    what a rank without cached tokens hands to `combine_exchange`."""
+    need = int(_lib.load().kvq_decode_workspace_bytes(B, Hq, D, 1))
+    ws = get_workspace(torch.device(dev), need)
+    o_bytes = (B * Hq * D * 4 + 255) & ~255
+    ws[:o_bytes].zero_()
+    ml = ws[o_bytes:o_bytes + B * Hq * 8].view(torch.float32).view(B * Hq, 2)
+    ml[:, 0] = float("-inf")
+    ml[:, 1] = 0.0
+
+
+def exchange_bytes(B: int, Hq: int, D: int, slots: int, world: int):
+    """(total bytes, offset of the flag words) of one rank's receive buffer of the fused exchange."""
+    off = C.c_size_t(0)
+    total = int(_lib.load().kvq_exchange_bytes(B, Hq, D, slots, world, C.byref(off)))
+    return total, int(off.value)
+
+
+def combine_exchange(peer_ptrs, rank: int, slot: int, slots: int, epoch: torch.Tensor, out: torch.Tensor, *,
+                     splits: int, status: Optional[torch.Tensor] = None, wait_ns: int = 0) -> torch.Tensor:
+    """Second half of a sequence-sharded decode_attn(..., stages=1) call on this rank: merge the KV
+    splits left in the workspace, exchange the normalised partial with every peer by direct stores
+    into their receive buffers (`peer_ptrs[q]` = rank q's buffer mapped into this process), wait for
+    theirs and write the merged fp16 `out` [B,Hq,D].  One launch; `epoch` is a device int32 >= 1."""
+    dev = _require_cuda(out, epoch)
+    B, Hq, D = out.shape
+    world = len(peer_ptrs)
+    if out.dtype != torch.float16 or out.stride(-1) != 1:
+        raise ValueError("out must be an fp16 [B,Hq,D] tensor, contiguous in head_dim")
+    if epoch.dtype != torch.int32 or (status is not None and status.dtype != torch.int32):
+        raise ValueError("epoch / status must be int32 device tensors")
+    x = _lib.KvqExchangeArgs()
+    x.B, x.Hq, x.D, x.splits = B, Hq, D, int(splits)
+    need = int(_lib.load().kvq_decode_workspace_bytes(B, Hq, D, x.splits))
+    ws = get_workspace(dev, need)
+    x.workspace, x.workspace_bytes = ws.data_ptr(), ws.numel()
+    x.rank, x.world = int(rank), world
+    arr = (C.c_void_p * world)(*[int(p) for p in peer_ptrs])
+    x.peer_base = C.cast(arr, C.POINTER(C.c_void_p))
+    x.slot, x.slots = int(slot), int(slots)
+    x.epoch = epoch.data_ptr()
+    x.wait_ns = int(wait_ns)
+    x.status = status.data_ptr() if status is not None else None
+    x.out = out.data_ptr()
+    x.out_stride_b, x.out_stride_h = out.stride(0), out.stride(1)
+    with torch.cuda.device(dev):
+        rc = _lib.load().kvq_combine_exchange(C.byref(x), _stream_ptr(dev))
+    _lib.check("kvq_combine_exchange", rc)
+    return out
+
+
 def dequantize(fmt: int, k_payload: torch.Tensor, v_payload: Optional[torch.Tensor], k_scale: torch.Tensor,
                v_scale: Optional[torch.Tensor], *, k_zp=None, v_zp=None, outlier_idx=None, k_side=None, v_side=None):
     """Quantized cache views -> fp16 [B,Hkv,S,D] (K and V in one launch; V optional).

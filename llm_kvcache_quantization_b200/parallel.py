@@ -11,7 +11,9 @@ Two ways the path shards (neither exists in the reference, which is single-GPU):
       M = max_r m_r;  out = sum_r o_r l_r e^{m_r - M} / sum_r l_r e^{m_r - M}
   Remote partials land in this GPU's own receive buffer before the merge kernel reads them.
 
-The collective goes through `torch.distributed` (NCCL on GPUs; gloo for the host-side tests).
+The collective goes through `torch.distributed` (NCCL on GPUs; gloo for the host-side tests), or,
+with `PeerExchange`, through the library's own fused kernel: combine + peer stores over NVLink +
+merge in one launch per layer, no library collective on the data path.
 """
 from __future__ import annotations
 
@@ -111,3 +113,66 @@ def sharded_decode(fmt: int, q: torch.Tensor, tensors: dict, local_len: int, sm_
                     out=scratch, packed_partial=send, **extra)
     gather_partials(send, group=group, out=recv)
     return ops.lse_combine_packed(recv, out=scratch)
+
+
+class PeerExchange:
+    """Receive buffers of the fused combine-and-exchange kernel, one per rank, mapped into every peer
+    through torch's symmetric memory (CUDA IPC under the hood; NVLink multicast is not used and its
+    binding is switched off).  `slots` independent exchanges per decode step (one per layer).
+
+        xchg = PeerExchange(B, Hq, D, slots=L)          # collective: every rank, same arguments
+        per step:   xchg.advance()                       # once, before the first layer
+        per layer:  xchg.decode(fmt, q, tensors, local_len, sm_scale, slot=l, out=out[l], ...)
+
+    Every rank must issue the same sequence of calls.  A peer that never arrives makes the kernel give
+    up after `wait_ns` (default one second), set `status` to 1 and return; the context stays usable."""
+
+    def __init__(self, B: int, Hq: int, D: int, slots: int, group=None, device=None, wait_ns: int = 0):
+        import os
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        from . import ops
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.B, self.Hq, self.D, self.slots = B, Hq, D, slots
+        self.wait_ns = int(wait_ns)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        total, self.flags_offset = ops.exchange_bytes(B, Hq, D, slots, self.world)
+        self.buf = symm.empty(total // 4, dtype=torch.float32, device=dev)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, self.group.group_name)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=self.group)             # nobody stores into a buffer that is still being cleared
+
+    def advance(self) -> None:
+        """Next decode step (device-side, capturable)."""
+        self.epoch.add_(1)
+
+    def decode(self, fmt: int, q: torch.Tensor, tensors: dict, local_len: int, sm_scale: float, *, slot: int,
+               out: torch.Tensor, inv_tau=None) -> torch.Tensor:
+        """Sequence-sharded decode attention of one layer: split-K scan of the local chunk, then the
+        fused combine / exchange / merge.  Same contract as `sharded_decode`."""
+        from . import ops
+        n = local_len
+        extra = {}
+        if tensors.get("kz") is not None:
+            extra.update(k_zp=tensors["kz"][:, :, :n], v_zp=tensors["vz"][:, :, :n])
+        if tensors.get("outlier_idx") is not None:
+            extra.update(outlier_idx=tensors["outlier_idx"].contiguous(), k_side=tensors["kside"][:, :, :n],
+                         v_side=tensors["vside"][:, :, :n])
+        if n > 0:
+            ops.decode_attn(fmt, q, tensors["k"][:, :, :n], tensors["v"][:, :, :n], tensors["ks"][:, :, :n],
+                            tensors["vs"][:, :, :n], None, sm_scale, head_dim=q.shape[-1], inv_tau=inv_tau, out=out,
+                            stages=1, **extra)
+            splits = ops.last_splits()
+        else:
+            # an empty shard contributes the neutral partial: one split with l = 0
+            splits = 1
+            ops.neutral_partial(q.shape[0], q.shape[1], q.shape[2], q.device)
+        return ops.combine_exchange(self.peer_ptrs, self.rank, slot, self.slots, self.epoch, out, splits=splits,
+                                    status=self.status, wait_ns=self.wait_ns)

@@ -1,5 +1,6 @@
 """Two-GPU checks (skipped on a single-GPU box): sequence-sharded decode with one NCCL all-gather of
-the packed partials per layer, against the same attention computed on one GPU."""
+the packed partials per layer, against the same attention computed on one GPU; and the library's
+fused combine / peer-store exchange / merge kernel against the NCCL path."""
 import os
 import socket
 
@@ -61,6 +62,27 @@ def _worker(rank, world, port, ret):
             err = (out.float() - ref.float()).abs()
             ret["max_err"] = float(err.max())
             ret["ok"] = bool((err <= 2e-3 + 1e-2 * ref.float().abs()).all())
+        # the library's own exchange: combine + peer stores over NVLink + merge in one launch.  Five
+        # steps reuse both parities of the receive buffer; the query changes every step.
+        xchg = P.PeerExchange(B, Hq, D, slots=2)
+        out2 = torch.empty(2, B, Hq, D, dtype=torch.float16, device=dev)
+        worst, good = 0.0, True
+        for step in range(5):
+            qs = (q * (1.0 + 0.25 * step)).to(dev)
+            xchg.advance()
+            for slot in range(2):
+                xchg.decode(_lib.FMT_INT4, qs if slot == 0 else -qs, t, n_local, 0.088, slot=slot, out=out2[slot],
+                            inv_tau=tau.to(dev))
+            torch.cuda.synchronize()
+            for slot in range(2):
+                want = P.sharded_decode(_lib.FMT_INT4, qs if slot == 0 else -qs, t, n_local, 0.088, send=send, recv=recv,
+                                        inv_tau=tau.to(dev))
+                err = (out2[slot].float() - want.float()).abs()
+                worst = max(worst, float(err.max()))
+                good = good and bool((err <= 1e-3 + 2e-3 * want.float().abs()).all())
+        torch.cuda.synchronize()
+        ret[f"xchg_ok_{rank}"] = good and int(xchg.status.item()) == 0
+        ret[f"xchg_err_{rank}"] = worst
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -73,3 +95,4 @@ def test_sequence_sharded_decode_two_gpus():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert ret.get("ok") is True, dict(ret)
+    assert ret.get("xchg_ok_0") is True and ret.get("xchg_ok_1") is True, dict(ret)
