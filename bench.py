@@ -194,13 +194,29 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
             att.update(outlier_idx=oidx, k_side=view["kside"], v_side=view["vside"])
         layers.append((b, view, policy, app, att))
 
+    # The append of a layer runs on a second stream, concurrently with the split-K scan of the old tokens
+    # (tail_tokens = 1); the combine stage waits for both and attends the new token from the cache.
+    overlap = with_append and stages == 0 and os.environ.get("KVQ_BENCH_NO_OVERLAP", "0") != "1"
+    side = torch.cuda.Stream(device=dev) if overlap else None
+
+    def attend(l, view, att, **kw):
+        ops.decode_attn(fmt, q[l], view["k"], view["v"], view["ks"], view["vs"], ctx, 1.0 / D ** 0.5,
+                        head_dim=D, inv_tau=inv_tau[l], splits=splits, out=out[l], max_ctx=S + 1, **att, **kw)
+
     def step():
         for l, (b, view, policy, app, att) in enumerate(layers):
+            if overlap:
+                main = torch.cuda.current_stream(dev)
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], S, GS, **app)
+                attend(l, view, att, stages=1, tail_tokens=1)
+                main.wait_stream(side)
+                attend(l, view, att, stages=2, tail_tokens=1)
+                continue
             if with_append:
                 ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], S, GS, **app)
-            ops.decode_attn(fmt, q[l], view["k"], view["v"], view["ks"], view["vs"], ctx, 1.0 / D ** 0.5,
-                            head_dim=D, inv_tau=inv_tau[l], splits=splits, out=out[l], max_ctx=S + 1,
-                            stages=stages, **att)
+            attend(l, view, att, stages=stages)
     return step, (lambda: ops.last_splits())
 
 
@@ -353,6 +369,8 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
     send = torch.empty(B, Hq, D + 2, dtype=torch.float32, device=dev)
     recv = torch.empty(world, B, Hq, D + 2, dtype=torch.float32, device=dev)
     P.check_partial_shapes(send.shape)
+    fused = args.collective == "fused"
+    xchg = P.PeerExchange(B, Hq, D, slots=L) if fused else None
     layers = []
     for l in range(L):
         b = cache._bufs[l]
@@ -372,6 +390,8 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
         layers.append((b, tens, policy, app))
 
     def step(scan_only=False):
+        if fused and not scan_only:
+            xchg.advance()
         for l, (b, tens, policy, app) in enumerate(layers):
             if scan_only:
                 extra = {}
@@ -384,9 +404,19 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
                                 tens["vs"][:, :, :n_att], None, 1.0 / D ** 0.5, head_dim=D, inv_tau=inv_tau[l],
                                 out=out[l], stages=1, **extra)
                 continue
+            do_append = None
             if owner:
-                ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], n_old, GS, **app)
-            P.sharded_decode(fmt, q[l], tens, n_att, 1.0 / D ** 0.5, send=send, recv=recv, inv_tau=inv_tau[l], out=out[l])
+                do_append = (lambda l=l, b=b, policy=policy, app=app: ops.quantize_append(
+                    fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], n_old, GS, **app))
+            if fused:
+                # on the owner the append runs beside the scan; the exchange kernel attends the new token
+                xchg.decode(fmt, q[l], tens, n_att, 1.0 / D ** 0.5, slot=l, out=out[l], inv_tau=inv_tau[l],
+                            append=do_append)
+            else:
+                if owner:
+                    do_append()
+                P.sharded_decode(fmt, q[l], tens, n_att, 1.0 / D ** 0.5, send=send, recv=recv, inv_tau=inv_tau[l],
+                                 out=out[l])
 
     g_step = capture(step)
     splits = ops.last_splits()
@@ -436,9 +466,14 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": dict(workload_config(wl, args.workload), parallelism=f"sequence-sharded x{world}",
                            chunk_tokens=sh.chunk, splits=splits,
-                           collective="one NCCL all-gather of [B,Hq,D+2] fp32 per layer",
-                           step=f"CUDA graph (kernels + NCCL all-gather) of {L}x(append on the owner, split-K scan, "
-                                "combine, all-gather, merge)"),
+                           collective=("fused kernel: combine + peer stores of [B,Hq,D+2] fp32 over NVLink + merge, "
+                                       "one launch per layer" if fused else
+                                       "one NCCL all-gather of [B,Hq,D+2] fp32 per layer"),
+                           step=(f"CUDA graph of {L}x(append on the owner, split-K scan, fused combine/exchange/merge)"
+                                 if fused else
+                                 f"CUDA graph (kernels + NCCL all-gather) of {L}x(append on the owner, split-K scan, "
+                                 "combine, all-gather, merge)"),
+                           exchange_status=(int(xchg.status.item()) if fused else None)),
             "us_per_layer": ms_per_step * 1e3 / L,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": alg_bytes * NCU_TRAFFIC_RATIO.get(kind, 1.0),
@@ -451,7 +486,7 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
                     "h2d_bytes_per_step": (q.numel() + k_new.numel() + v_new.numel()) * 2,
                     "d2h_bytes_per_step": out.numel() * 2, "ms_per_step": ems / args.steps,
                     "api": "pinned H2D of q/k/v on every rank, one CUDA graph (sharded_decode per layer), pinned D2H"},
-            "gpu_launches": args.steps * L * 4, "clocks": clocks,
+            "gpu_launches": args.steps * L * (3 if fused else 4), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     # Tearing the process group down while captured graphs still hold its collectives did not return in a
@@ -476,6 +511,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
+    ap.add_argument("--collective", default="fused", choices=("fused", "nccl"),
+                    help="sequence-sharded mode: the library's fused combine/peer-store/merge kernel, or "
+                         "combine + NCCL all-gather + merge")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.layers > 0:
@@ -607,8 +645,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": dict(workload_config(wl, args.workload), parallelism=f"batch-sharded x{world}", splits=splits,
-                           step="CUDA graph of 28x(quantize-append, split-K scan, combine)" if L == 28 else
-                           f"CUDA graph of {L}x(quantize-append, split-K scan, combine)"),
+                           step=f"CUDA graph of {L}x(quantize-append || split-K scan of the old tokens, then combine "
+                                "incl. the new token)"),
             "us_per_layer": ms_per_step * 1e3 / L,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": args.steps * L * 3, "clocks": clocks,

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define KVQ_ABI_VERSION 2
+#define KVQ_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define KVQ_API __attribute__((visibility("default")))
@@ -153,6 +153,11 @@ typedef struct KvqAttnArgs {
                                  outside the integer products (about 10 % faster; differs from the reference's
                                  fp16-rounded code*scale by <= 2^-11 relative per element, which can exceed the
                                  2e-3 / 1e-2 tolerance on data with unquantised x20 outlier channels).             */
+    int32_t tail_tokens;      /* 0 or 1.  1: the LAST token of every row's context is not read by the split
+                                 kernel (stage 1) but by the combine (stage 2), straight from the cache.  The
+                                 split kernel then does not depend on the kernel that appends that token: a
+                                 caller may run stage 1 and kvq_quantize_append concurrently (two streams) and
+                                 stage 2 after both.  Same result up to summation order.                       */
     void*   workspace;        /* >= kvq_decode_workspace_bytes(...)                       */
     size_t  workspace_bytes;
     void*   out;              /* fp16 [B, Hq, D] or NULL                                  */
@@ -239,8 +244,9 @@ KVQ_API int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream);
 /*
  * Sequence-sharded decode, fused exchange: merge this rank's KV splits (the partials that
  * kvq_decode_attn with stages = 1 left in `workspace`), store the normalised partial of every
- * (batch, head) row into every rank's receive buffer with plain peer stores over NVLink, wait
- * (bounded) for the other ranks' rows, and merge the `world` partials into `out` - one launch in
+ * (batch, head) row into every rank's receive buffer with plain 8-byte peer stores over NVLink
+ * (value + epoch stamp in one store: no fence, no separate flag), wait (bounded) for the other
+ * ranks' rows, and merge the `world` partials into `out` - one launch in
  * place of combine + all-gather + kvq_lse_combine.  No counterpart in the reference (single GPU).
  *
  * Every rank owns one receive buffer of kvq_exchange_bytes(...) bytes, zero-filled before the first
@@ -263,10 +269,14 @@ typedef struct KvqExchangeArgs {
     int32_t* status;             /* device int32 or NULL: set to 1 when a wait expired       */
     void*   out;                 /* fp16 [B, Hq, D]                                          */
     int64_t out_stride_b, out_stride_h;                 /* elements                      */
+    const KvqAttnArgs* tail_attn; /* HOST pointer or NULL.  The arguments of the stage-1 call when that call ran with
+                                     tail_tokens = 1: this rank's last token is then attended here, from the cache,
+                                     before the partial is sent (the rank that appended the new token).            */
 } KvqExchangeArgs;
 
-/* Bytes of one rank's receive buffer; *flags_offset (optional) = where its flag words start. */
-KVQ_API size_t kvq_exchange_bytes(int32_t B, int32_t Hq, int32_t D, int32_t slots, int32_t world, size_t* flags_offset);
+/* Bytes of one rank's receive buffer: 2 x slots x world x B x Hq x (D + 2) words of 8 bytes
+ * (fp32 value + epoch stamp), rounded up to 256. */
+KVQ_API size_t kvq_exchange_bytes(int32_t B, int32_t Hq, int32_t D, int32_t slots, int32_t world);
 KVQ_API int kvq_combine_exchange(const KvqExchangeArgs* args, kvq_stream_t stream);
 
 /*

@@ -68,7 +68,7 @@ class KvqAttnArgs(C.Structure):
         ("k", KvqCacheSide), ("v", KvqCacheSide),
         ("n_out", _i32), ("outlier_idx", _vp),
         ("context_lens", _vp),
-        ("splits", _i32), ("stages", _i32), ("fast_dequant", _i32),
+        ("splits", _i32), ("stages", _i32), ("fast_dequant", _i32), ("tail_tokens", _i32),
         ("workspace", _vp), ("workspace_bytes", C.c_size_t),
         ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
         ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),
@@ -107,6 +107,7 @@ class KvqExchangeArgs(C.Structure):
         ("slot", _i32), ("slots", _i32),
         ("epoch", _vp), ("wait_ns", C.c_uint64), ("status", _vp),
         ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
+        ("tail_attn", C.POINTER(KvqAttnArgs)),
     ]
 
 
@@ -118,7 +119,7 @@ EXPORTS = (
     ("kvq_decode_workspace_bytes", C.c_size_t, (_i32, _i32, _i32, _i32)),
     ("kvq_decode_pick_splits", _i32, (C.POINTER(KvqAttnArgs),)),
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
-    ("kvq_exchange_bytes", C.c_size_t, (_i32, _i32, _i32, _i32, _i32, C.POINTER(C.c_size_t))),
+    ("kvq_exchange_bytes", C.c_size_t, (_i32, _i32, _i32, _i32, _i32)),
     ("kvq_combine_exchange", C.c_int, (C.POINTER(KvqExchangeArgs), _vp)),
     ("kvq_dequantize", C.c_int, (C.POINTER(KvqDequantArgs), _vp)),
     ("kvq_debug_error_flag", C.c_int, (C.c_int,)),

@@ -15,14 +15,26 @@ namespace kvq {
 // ---------------------------------------------------------------------------
 // In-GPU combine over KV splits: unnormalised partials (o, m, l) -> fp16 output
 // and, optionally, a normalised partial (o/l, m in natural-log units, l) for a
-// cross-GPU merge.  grid = (Hq, B), block = 4 warps.  Every warp first finds the
+// cross-GPU merge.  grid = (Hq, B), block = 8 warps.  Every warp first finds the
 // global max over all splits (lane s reads split s), then warp w sums the splits
-// w, w+4, ... with four independent loads in flight per lane (a lane owns D/32
-// channels), and the four warps are added through shared memory.  The loop over
+// w, w+8, ... with four independent loads in flight per lane (a lane owns D/32
+// channels), and the eight warps are added through shared memory.  The loop over
 // splits is latency-bound when run serially; this form keeps it near one round trip.
 // ---------------------------------------------------------------------------
-// Shared front half: leaves the four warps' weighted sums in red[w][0..D) and their
+// Shared front half: leaves the warps' weighted sums in red[w][0..D) and their
 // denominators in red[w][D]; returns the global max (log2 domain) of the row.
+constexpr int kCombineWarps = 8;
+constexpr int kCombineThreads = kCombineWarps * 32;
+
+// sum over the warps' rows of `red` at column c
+template <int N>
+__device__ __forceinline__ float red_sum(const float (*red)[N], int c) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCombineWarps; ++w) v += red[w][c];
+    return v;
+}
+
 template <int EPL>   // channels per lane = D / 32
 __device__ __forceinline__ float combine_partials(const AttnParams& p, int b, int h, float (*red)[EPL * 32 + 1]) {
     const KvqAttnArgs& a = p.a;
@@ -41,12 +53,12 @@ __device__ __forceinline__ float combine_partials(const AttnParams& p, int b, in
     for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
     float L = 0.f;
     const float* o_base = p.ws_o + row0 * D + lane * EPL;
-    for (int s0 = warp; s0 < p.splits; s0 += 16) {
+    for (int s0 = warp; s0 < p.splits; s0 += 4 * kCombineWarps) {
         float2 mv[4];
         float ov[4][EPL];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int s = s0 + 4 * u;
+            const int s = s0 + kCombineWarps * u;
             mv[u] = s < p.splits ? ml[s] : make_float2(-INFINITY, 0.f);
             if (s < p.splits) {
                 if (EPL == 4) *reinterpret_cast<float4*>(ov[u]) = *reinterpret_cast<const float4*>(o_base + (long long)s * D);
@@ -73,17 +85,75 @@ __device__ __forceinline__ float combine_partials(const AttnParams& p, int b, in
     return M;
 }
 
+// One channel of one cached token, dequantised exactly as the split kernels do (any format; runtime
+// dispatch - the combine stage touches a single token per row).
+__device__ __forceinline__ float cached_value(const KvqAttnArgs& a, const KvqCacheSide& cs, int b, int kvh, int t, int d) {
+    const char* row = (const char*)cs.payload + b * cs.pay_stride_b + kvh * cs.pay_stride_h + (long long)t * cs.pay_stride_s;
+    if (a.format == KVQ_FMT_FP16) return __half2float(((const __half*)row)[d]);
+    for (int j = 0; j < a.n_out; ++j)
+        if ((int)a.outlier_idx[kvh * a.n_out + j] == d)
+            return __half2float(((const __half*)cs.side)[b * cs.side_stride_b + kvh * cs.side_stride_h +
+                                                         (long long)t * cs.side_stride_s + j]);
+    int code;
+    if (a.format == KVQ_FMT_INT8) code = ((const int8_t*)row)[d];
+    else {
+        const unsigned byte = ((const uint8_t*)row)[d >> 1];
+        code = (int)((d & 1) ? (byte & 15u) : (byte >> 4)) - 8;
+    }
+    const long long so = b * cs.sc_stride_b + kvh * cs.sc_stride_h + (long long)t * cs.sc_stride_s + d / a.group_size;
+    __half v = __hmul_rn(__int2half_rn(code), ((const __half*)cs.scale)[so]);
+    if (cs.zp) v = __hadd_rn(v, ((const __half*)cs.zp)[so]);
+    return __half2float(v);
+}
+
+// The last token of the row's context, attended here instead of in the split kernel (tail_tokens = 1).
+// Thread d owns channel d.  In: the merged splits as (M log2-domain max, o_d weighted sum, Lt denominator);
+// out: the same triple with the token folded in.  Called by every thread of the CTA (it synchronises).
 template <int EPL>
-__global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p) {
+__device__ __forceinline__ void fold_tail(const AttnParams& p, int b, int h, float* scratch, float& M, float& o_d, float& Lt) {
+    const KvqAttnArgs& a = p.a;
+    constexpr int D = EPL * 32;
+    int ctx = a.context_lens ? a.context_lens[b] : a.max_ctx;
+    ctx = max(0, min(ctx, a.max_ctx));
+    if (ctx < 1) return;                                  // uniform over the CTA
+    const int t = ctx - 1, kvh = h / p.n_rep, d = threadIdx.x;
+    float prod = 0.f, vd = 0.f;
+    if (d < D) {
+        __half qv = ((const __half*)a.q)[b * a.q_stride_b + h * a.q_stride_h + d];
+        if (a.inv_tau) qv = __hmul(qv, __float2half_rn(a.inv_tau[h]));
+        prod = __half2float(qv) * cached_value(a, a.k, b, kvh, t, d);
+        vd = cached_value(a, a.v, b, kvh, t, d);
+    }
+    prod = warp_sum(prod);
+    __syncthreads();                                      // scratch may still be read as `red`
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = prod;
+    __syncthreads();
+    float dot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCombineWarps; ++w) dot += scratch[w];
+    const float sv = dot * a.sm_scale * kLog2e;
+    const float Mn = fmaxf(M, sv);
+    const float wm = (Lt > 0.f) ? exp2f(M - Mn) : 0.f;
+    const float wt = exp2f(sv - Mn);
+    o_d = o_d * wm + wt * vd;
+    Lt = Lt * wm + wt;
+    M = Mn;
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(kCombineThreads) combine_splits_kernel(const AttnParams p) {
+    pdl_launch_dependents();      // the next kernel of the stream may be set up; it waits for this one itself
     pdl_wait();                   // the split kernel's partials
     const KvqAttnArgs& a = p.a;
     const int h = blockIdx.x, b = blockIdx.y;
     constexpr int D = EPL * 32;
-    __shared__ float red[4][D + 1];
-    const float M = combine_partials<EPL>(p, b, h, red);
-    for (int d = threadIdx.x; d < D; d += 128) {
-        const float o = red[0][d] + red[1][d] + red[2][d] + red[3][d];
-        const float Lt = red[0][D] + red[1][D] + red[2][D] + red[3][D];
+    __shared__ float red[kCombineWarps][D + 1];
+    __shared__ float tail_scratch[kCombineWarps];
+    float M = combine_partials<EPL>(p, b, h, red);
+    float o = threadIdx.x < D ? red_sum(red, threadIdx.x) : 0.f;      // kCombineThreads >= D: one channel per thread
+    float Lt = red_sum(red, D);
+    if (a.tail_tokens) fold_tail<EPL>(p, b, h, tail_scratch, M, o, Lt);
+    for (int d = threadIdx.x; d < D; d += kCombineThreads) {
         const float r = (Lt > 0.f) ? o / Lt : 0.f;
         if (a.out) ((__half*)a.out)[b * a.out_stride_b + h * a.out_stride_h + d] = __float2half_rn(r);
         if (a.part_o) {
@@ -109,28 +179,28 @@ __global__ void __launch_bounds__(128) combine_splits_kernel(const AttnParams p)
 // other rows' arithmetic.
 //
 // Receive buffer of a rank (identical layout on every rank, peer-mapped):
-//   data  fp32 [2 parity][slots][world src][B][Hq][D + 2]   rows [o (D) | m | l]
-//   flags int32 [2 parity][slots][world src][B][Hq]          = epoch of the row's last write
-// `epoch` (device int, >= 1) is advanced once per decode step by the host side; parity =
-// epoch & 1 double-buffers the rows so that a rank one step ahead never overwrites a row a
-// slower rank still reads.  Progress never depends on another CTA of the same GPU: a CTA
-// pushes before it waits, and waits only for remote CTAs.  The wait is bounded by
-// `wait_ns`; on expiry the CTA raises *status and finishes with what it has.
+//   8-byte words [2 parity][slots][world src][B][Hq][D + 2], word = (fp32 value, epoch), rows [o (D) | m | l]
+// Every word carries its own validity stamp and travels as ONE 8-byte store, so no fence and no
+// separate flag is needed: the receiver spins on each word until its stamp equals the current epoch
+// (the low-latency protocol of collective libraries).  `epoch` (device int, >= 1) is advanced once
+// per decode step by the host side; parity = epoch & 1 double-buffers the rows so that a rank one
+// step ahead never overwrites a word a slower rank still waits for.  Progress never depends on
+// another CTA of the same GPU: a CTA pushes before it waits, and waits only for remote CTAs.  The
+// wait is bounded by `wait_ns`; on expiry the thread raises *status and continues with a zero.
 // ---------------------------------------------------------------------------
 struct ExchangeParams {
     AttnParams p;
     KvqExchangeArgs x;
-    float* recv[KVQ_MAX_PEERS];
-    int* flags[KVQ_MAX_PEERS];
+    unsigned long long* recv[KVQ_MAX_PEERS];
 };
 
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ void st_word(unsigned long long* p, float v, int stamp) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(stamp) : "memory");
 }
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void ld_word(const unsigned long long* p, float& v, int& stamp) {
+    unsigned lo;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(stamp) : "l"(p) : "memory");
+    v = __uint_as_float(lo);
 }
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -139,7 +209,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 template <int EPL>
-__global__ void __launch_bounds__(128) combine_exchange_kernel(const ExchangeParams ep) {
+__global__ void __launch_bounds__(kCombineThreads) combine_exchange_kernel(const ExchangeParams ep) {
+    pdl_launch_dependents();
     pdl_wait();
     const AttnParams& p = ep.p;
     const KvqExchangeArgs& x = ep.x;
@@ -147,78 +218,88 @@ __global__ void __launch_bounds__(128) combine_exchange_kernel(const ExchangePar
     const int h = blockIdx.x, b = blockIdx.y;
     constexpr int D = EPL * 32;
     constexpr int W = D + 2;
-    __shared__ float red[4][D + 1];
+    static_assert(D <= kCombineThreads, "one channel per thread");
+    __shared__ float red[kCombineWarps][D + 1];
     __shared__ float pm[KVQ_MAX_PEERS], pl[KVQ_MAX_PEERS];
-    const float M = combine_partials<EPL>(p, b, h, red);
+    __shared__ float tail_scratch[kCombineWarps];
+    float M = combine_partials<EPL>(p, b, h, red);
+    float o = threadIdx.x < D ? red_sum(red, threadIdx.x) : 0.f;      // one channel per thread
+    float Lt = red_sum(red, D);
+    if (a.tail_tokens) fold_tail<EPL>(p, b, h, tail_scratch, M, o, Lt);
 
     const int epoch = *x.epoch;
     const long long rows = (long long)a.B * a.Hq;
     const long long slot_base = ((long long)(epoch & 1) * x.slots + x.slot) * x.world;     // in units of `rows`
-    const long long my_row = (slot_base + x.rank) * rows + (long long)b * a.Hq + h;
+    const long long row_in_slot = (long long)b * a.Hq + h;
 
     // ---- push this rank's normalised partial of the row to every rank (itself included)
-    const float Lt = red[0][D] + red[1][D] + red[2][D] + red[3][D];
-    for (int d = threadIdx.x; d < D; d += 128) {
-        const float o = red[0][d] + red[1][d] + red[2][d] + red[3][d];
+    {
         const float r = (Lt > 0.f) ? o / Lt : 0.f;
-        for (int q = 0; q < x.world; ++q) ep.recv[q][my_row * W + d] = r;
-    }
-    if (threadIdx.x < x.world) {
-        float* dst = ep.recv[threadIdx.x] + my_row * W + D;
-        dst[0] = (Lt > 0.f) ? M * 0.6931471805599453f : -INFINITY;
-        dst[1] = Lt;
-    }
-    __syncthreads();
-    if (threadIdx.x < x.world) {
-        __threadfence_system();
-        st_release_sys(ep.flags[threadIdx.x] + my_row, epoch);
+        const float m_nat = (Lt > 0.f) ? M * 0.6931471805599453f : -INFINITY;
+        const long long my_row = (slot_base + x.rank) * rows + row_in_slot;
+        for (int w = threadIdx.x; w < W; w += kCombineThreads) {
+            const float val = w < D ? r : (w == D ? m_nat : Lt);       // w < D implies w == threadIdx.x
+            for (int q = 0; q < x.world; ++q) st_word(ep.recv[q] + my_row * W + w, val, epoch);
+        }
     }
 
-    // ---- wait for the same row from every rank (bounded), then merge
-    if (threadIdx.x < x.world) {
-        const long long src_row = (slot_base + threadIdx.x) * rows + (long long)b * a.Hq + h;
-        const int* f = ep.flags[x.rank] + src_row;
-        const unsigned long long t0 = global_ns();
-        bool ok = true;
-        while (ld_acquire_sys(f) != epoch) {
-            if (global_ns() - t0 > x.wait_ns) { ok = false; break; }
-            __nanosleep(100);
+    // ---- collect the same row from every rank: spin on each word's stamp (bounded)
+    float vals[KVQ_MAX_PEERS];
+    const unsigned long long t0 = global_ns();
+    bool expired = false;
+    for (int w = threadIdx.x; w < W; w += kCombineThreads) {
+#pragma unroll
+        for (int q = 0; q < KVQ_MAX_PEERS; ++q) {
+            if (q >= x.world) break;
+            const unsigned long long* src = ep.recv[x.rank] + ((slot_base + q) * rows + row_in_slot) * W + w;
+            float v;
+            int stamp;
+            ld_word(src, v, stamp);
+            while (stamp != epoch && !expired) {
+                if (global_ns() - t0 > x.wait_ns) { expired = true; break; }
+                __nanosleep(40);
+                ld_word(src, v, stamp);
+            }
+            if (stamp != epoch) v = 0.f;                               // l = 0 removes the rank from the merge
+            if (w < D) vals[q] = v;
+            else if (w == D) pm[q] = v;
+            else pl[q] = v;
         }
-        if (!ok && x.status) atomicExch(x.status, 1);
-        const float* src = ep.recv[x.rank] + src_row * W + D;
-        pm[threadIdx.x] = ok ? __ldcg(src) : -INFINITY;
-        pl[threadIdx.x] = ok ? __ldcg(src + 1) : 0.f;
     }
+    if (expired && x.status) atomicExch(x.status, 1);
     __syncthreads();
     float Mx = -INFINITY;
     for (int q = 0; q < x.world; ++q)
         if (pl[q] > 0.f) Mx = fmaxf(Mx, pm[q]);
-    for (int d = threadIdx.x; d < D; d += 128) {
+    if (threadIdx.x < D) {
         float num = 0.f, den = 0.f;
-        for (int q = 0; q < x.world; ++q) {
+#pragma unroll
+        for (int q = 0; q < KVQ_MAX_PEERS; ++q) {
+            if (q >= x.world) break;
             if (pl[q] > 0.f) {
-                const float w = pl[q] * expf(pm[q] - Mx);
-                num += __ldcg(ep.recv[x.rank] + ((slot_base + q) * rows + (long long)b * a.Hq + h) * W + d) * w;
-                den += w;
+                const float wgt = pl[q] * expf(pm[q] - Mx);
+                num += vals[q] * wgt;
+                den += wgt;
             }
         }
         const float r = den > 0.f ? num / den : 0.f;
-        ((__half*)x.out)[b * x.out_stride_b + h * x.out_stride_h + d] = __float2half_rn(r);
+        ((__half*)x.out)[b * x.out_stride_b + h * x.out_stride_h + threadIdx.x] = __float2half_rn(r);
     }
 }
 
 static int launch_combine(const AttnParams& p, cudaStream_t st) {
     dim3 grid(p.a.Hq, p.a.B);
     switch (p.a.D) {
-        case 64: return launch_pdl(combine_splits_kernel<2>, grid, dim3(128), 0, st, p);
-        case 128: return launch_pdl(combine_splits_kernel<4>, grid, dim3(128), 0, st, p);
-        case 256: return launch_pdl(combine_splits_kernel<8>, grid, dim3(128), 0, st, p);
+        case 64: return launch_pdl(combine_splits_kernel<2>, grid, dim3(kCombineThreads), 0, st, p);
+        case 128: return launch_pdl(combine_splits_kernel<4>, grid, dim3(kCombineThreads), 0, st, p);
+        case 256: return launch_pdl(combine_splits_kernel<8>, grid, dim3(kCombineThreads), 0, st, p);
         default: return KVQ_EUNSUPPORTED;
     }
 }
 
 // Merge of P normalised partials (one per sequence shard).  grid = (Hq, B).
 __global__ void lse_combine_kernel(const KvqCombineArgs c) {
+    pdl_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const long long BH = (long long)c.B * c.Hq;
     const long long idx = (long long)b * c.Hq + h;
@@ -578,6 +659,7 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     if (rc) return rc;
     if ((a.q_stride_b & 1) || (a.q_stride_h & 1) || (((uintptr_t)a.q) & 3)) return KVQ_EINVAL;
     if (a.stages < 0 || a.stages > 2) return KVQ_EINVAL;
+    if (a.tail_tokens < 0 || a.tail_tokens > 1) return KVQ_EINVAL;
 
     const bool mma = mma_eligible(p, asym);
     p.splits = a.splits > 0 ? a.splits : pick_splits_internal(p, asym, mma);
@@ -657,13 +739,10 @@ extern "C" int kvq_decode_attn_static(const KvqAttnArgs* args, kvq_stream_t stre
     return kvq_decode_attn(&a, stream);
 }
 
-extern "C" size_t kvq_exchange_bytes(int32_t B, int32_t Hq, int32_t D, int32_t slots, int32_t world, size_t* flags_offset) {
+extern "C" size_t kvq_exchange_bytes(int32_t B, int32_t Hq, int32_t D, int32_t slots, int32_t world) {
     if (B <= 0 || Hq <= 0 || D <= 0 || slots <= 0 || world <= 0) return 0;
-    const size_t rows = (size_t)2 * slots * world * B * Hq;
-    size_t data = rows * (D + 2) * sizeof(float);
-    data = (data + 255) & ~(size_t)255;
-    if (flags_offset) *flags_offset = data;
-    return data + ((rows * sizeof(int32_t) + 255) & ~(size_t)255);
+    const size_t words = (size_t)2 * slots * world * B * Hq * (D + 2);
+    return (words * sizeof(unsigned long long) + 255) & ~(size_t)255;
 }
 
 extern "C" int kvq_combine_exchange(const KvqExchangeArgs* args, kvq_stream_t stream) {
@@ -677,12 +756,21 @@ extern "C" int kvq_combine_exchange(const KvqExchangeArgs* args, kvq_stream_t st
     if (!x.peer_base || !x.epoch || !x.out || !x.workspace) return KVQ_EINVAL;
     const size_t need = kvq_decode_workspace_bytes(x.B, x.Hq, x.D, x.splits);
     if (x.workspace_bytes < need || (((uintptr_t)x.workspace) & 15)) return KVQ_EWORKSPACE;
-    size_t flags_off = 0;
-    kvq_exchange_bytes(x.B, x.Hq, x.D, x.slots, x.world, &flags_off);
     ExchangeParams ep;
     ep.x = x;
     ep.p.a = KvqAttnArgs();
     ep.p.a.B = x.B; ep.p.a.Hq = x.Hq; ep.p.a.D = x.D;
+    ep.p.n_rep = 1;
+    if (x.tail_attn && x.tail_attn->tail_tokens) {
+        // the stage-1 call left this rank's last token to this kernel: same validation, same derived values
+        bool asym = false;
+        int rc = fill_params(*x.tail_attn, ep.p, asym);
+        if (rc) return rc;
+        const KvqAttnArgs& t = *x.tail_attn;
+        if (t.B != x.B || t.Hq != x.Hq || t.D != x.D || t.tail_tokens != 1 || !t.q) return KVQ_EINVAL;
+        if (t.n_out < 0 || (t.n_out > 0 && (!t.outlier_idx || asym))) return KVQ_EINVAL;
+        if ((rc = validate_side(t.k, t, asym)) != 0 || (rc = validate_side(t.v, t, asym)) != 0) return rc;
+    }
     ep.p.splits = x.splits;
     const size_t o_bytes = ((size_t)x.B * x.Hq * x.splits * x.D * sizeof(float) + 255) & ~(size_t)255;
     ep.p.ws_o = (float*)x.workspace;
@@ -690,16 +778,15 @@ extern "C" int kvq_combine_exchange(const KvqExchangeArgs* args, kvq_stream_t st
     for (int q = 0; q < KVQ_MAX_PEERS; ++q) {
         char* base = q < x.world ? (char*)x.peer_base[q] : nullptr;
         if (q < x.world && (!base || ((uintptr_t)base & 15))) return KVQ_EINVAL;
-        ep.recv[q] = (float*)base;
-        ep.flags[q] = base ? (int*)(base + flags_off) : nullptr;
+        ep.recv[q] = (unsigned long long*)base;
     }
     if (ep.x.wait_ns == 0) ep.x.wait_ns = 1000000000ull;       // one second
     dim3 grid(x.Hq, x.B);
     cudaStream_t st = (cudaStream_t)stream;
     switch (x.D) {
-        case 64: return launch_pdl(combine_exchange_kernel<2>, grid, dim3(128), 0, st, ep);
-        case 128: return launch_pdl(combine_exchange_kernel<4>, grid, dim3(128), 0, st, ep);
-        default: return launch_pdl(combine_exchange_kernel<8>, grid, dim3(128), 0, st, ep);
+        case 64: return launch_pdl(combine_exchange_kernel<2>, grid, dim3(kCombineThreads), 0, st, ep);
+        case 128: return launch_pdl(combine_exchange_kernel<4>, grid, dim3(kCombineThreads), 0, st, ep);
+        default: return launch_pdl(combine_exchange_kernel<8>, grid, dim3(kCombineThreads), 0, st, ep);
     }
 }
 

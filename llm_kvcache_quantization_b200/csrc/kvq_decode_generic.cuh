@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(128) decode_split_generic_kernel(const AttnPar
     const int gs = a.group_size;
 
     int ctx = a.context_lens ? a.context_lens[b] : a.max_ctx;
-    ctx = max(0, min(ctx, a.max_ctx));
+    ctx = max(0, min(ctx, a.max_ctx) - a.tail_tokens);      // the tail belongs to the combine stage
     int s0, s1;
     split_range(ctx, p.splits, split, 32, s0, s1);
 

@@ -299,7 +299,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     pdl_wait();
 
     int ctx = a.context_lens ? a.context_lens[b] : a.max_ctx;
-    ctx = max(0, min(ctx, a.max_ctx));
+    ctx = max(0, min(ctx, a.max_ctx) - a.tail_tokens);      // the tail belongs to the combine stage
     int s0, s1;
     split_range(ctx, p.splits, split, kTS, s0, s1);
 

@@ -76,6 +76,7 @@ __device__ float group_quantile(const float* v, int n, float q) {
 template <int FMT, int POLICY, int GS>
 __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams p) {
     pdl_launch_dependents();      // the decode kernel that follows may start its prologue now
+    pdl_wait();                   // launched early itself: the kernel before it may still produce the new tokens
     const KvqAppendArgs& a = p.a;
     const int G = p.G;
     const int gs = GS ? GS : a.group_size;
@@ -312,8 +313,7 @@ static int launch_gs(const QuantParams& p, cudaStream_t st) {
     const int block = 128;
     const long long grid = (threads + block - 1) / block;
     if (grid > 0x7fffffffLL) return KVQ_EINVAL;
-    quantize_append_kernel<FMT, POLICY, GS><<<(unsigned)grid, block, 0, st>>>(p);
-    return check_launch();
+    return launch_pdl(quantize_append_kernel<FMT, POLICY, GS>, dim3((unsigned)grid), dim3(block), 0, st, p);
 }
 
 template <int FMT, int POLICY>

@@ -213,7 +213,8 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
                 outlier_idx=None, k_side=None, v_side=None,
                 splits: int = 0, out: Optional[torch.Tensor] = None,
                 return_partial: bool = False, max_ctx: Optional[int] = None, stages: int = 0,
-                packed_partial: Optional[torch.Tensor] = None, fast_dequant: Optional[bool] = None):
+                packed_partial: Optional[torch.Tensor] = None, fast_dequant: Optional[bool] = None,
+                tail_tokens: int = 0, exchange: Optional[dict] = None):
     """Fused q_len==1 attention over a (quantized) cache.  q fp16 [B,Hq,D].
 
     Returns `out` fp16 [B,Hq,D]; with `return_partial` also the normalised
@@ -221,6 +222,9 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     sequence-sharded merge.  `packed_partial` (fp32 [B,Hq,D+2], contiguous) receives the
     same partial as one buffer `[o (D) | m | l]` per (b, h) - the send buffer of the
     sequence-sharded all-gather.  No host synchronisation happens here.
+
+    `exchange` (sequence sharding, see `parallel.PeerExchange`): the combine stage becomes the fused
+    combine / peer-store exchange / merge kernel, and `out` receives the attention over ALL ranks' tokens.
     """
     dev = _require_cuda(q, k_payload, v_payload, k_scale, v_scale, context_lens)
     if q.dtype != torch.float16:
@@ -249,6 +253,7 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     if fast_dequant is None:       # KVQ_INT4_FAST=1: factored-scale INT4 path instead of bit-faithful dequantisation
         fast_dequant = os.environ.get("KVQ_INT4_FAST", "0") == "1"
     a.fast_dequant = 1 if fast_dequant else 0
+    a.tail_tokens = int(tail_tokens)   # 1: the last token of each row is attended by the combine stage (see kvq.h)
     a.k = _cache_side(k_payload, k_scale, k_zp, k_side)
     a.v = _cache_side(v_payload, v_scale, v_zp, v_side)
     if outlier_idx is not None:
@@ -285,7 +290,18 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
             a.part_o, a.part_m, a.part_l = pp.data_ptr(), pp.data_ptr() + 4 * D, pp.data_ptr() + 4 * (D + 1)
             a.part_o_stride = a.part_ml_stride = D + 2
             part = (pp[..., :D], pp[..., D], pp[..., D + 1])
-        if B > 0 and a.max_ctx > 0:
+        if exchange is not None:
+            if return_partial or packed_partial is not None or not (B > 0 and a.max_ctx > 0):
+                raise ValueError("exchange needs a non-empty local chunk and no partial outputs")
+            rc = 0
+            if a.stages != 2:
+                a.stages = 1
+                rc = lib.kvq_decode_attn(C.byref(a), _stream_ptr(dev))
+            if rc == 0 and int(stages) != 1:
+                combine_exchange(exchange["peer_ptrs"], exchange["rank"], exchange["slot"], exchange["slots"],
+                                 exchange["epoch"], out, splits=a.splits, status=exchange.get("status"),
+                                 wait_ns=exchange.get("wait_ns", 0), tail_attn=a if a.tail_tokens else None)
+        elif B > 0 and a.max_ctx > 0:
             rc = lib.kvq_decode_attn(C.byref(a), _stream_ptr(dev))
         else:
             # nothing cached (an empty sequence shard): zeros, and the neutral partial (l = 0, m = -inf)
@@ -311,15 +327,14 @@ def neutral_partial(B: int, Hq: int, D: int, dev) -> None:
     ml[:, 1] = 0.0
 
 
-def exchange_bytes(B: int, Hq: int, D: int, slots: int, world: int):
-    """(total bytes, offset of the flag words) of one rank's receive buffer of the fused exchange."""
-    off = C.c_size_t(0)
-    total = int(_lib.load().kvq_exchange_bytes(B, Hq, D, slots, world, C.byref(off)))
-    return total, int(off.value)
+def exchange_bytes(B: int, Hq: int, D: int, slots: int, world: int) -> int:
+    """Bytes of one rank's receive buffer of the fused exchange."""
+    return int(_lib.load().kvq_exchange_bytes(B, Hq, D, slots, world))
 
 
 def combine_exchange(peer_ptrs, rank: int, slot: int, slots: int, epoch: torch.Tensor, out: torch.Tensor, *,
-                     splits: int, status: Optional[torch.Tensor] = None, wait_ns: int = 0) -> torch.Tensor:
+                     splits: int, status: Optional[torch.Tensor] = None, wait_ns: int = 0,
+                     tail_attn=None) -> torch.Tensor:
     """Second half of a sequence-sharded decode_attn(..., stages=1) call on this rank: merge the KV
     splits left in the workspace, exchange the normalised partial with every peer by direct stores
     into their receive buffers (`peer_ptrs[q]` = rank q's buffer mapped into this process), wait for
@@ -345,6 +360,8 @@ def combine_exchange(peer_ptrs, rank: int, slot: int, slots: int, epoch: torch.T
     x.status = status.data_ptr() if status is not None else None
     x.out = out.data_ptr()
     x.out_stride_b, x.out_stride_h = out.stride(0), out.stride(1)
+    if tail_attn is not None:          # the KvqAttnArgs of the stage-1 call (tail_tokens = 1)
+        x.tail_attn = C.pointer(tail_attn)
     with torch.cuda.device(dev):
         rc = _lib.load().kvq_combine_exchange(C.byref(x), _stream_ptr(dev))
     _lib.check("kvq_combine_exchange", rc)

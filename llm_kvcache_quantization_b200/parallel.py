@@ -139,13 +139,14 @@ class PeerExchange:
         self.B, self.Hq, self.D, self.slots = B, Hq, D, slots
         self.wait_ns = int(wait_ns)
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        total, self.flags_offset = ops.exchange_bytes(B, Hq, D, slots, self.world)
+        total = ops.exchange_bytes(B, Hq, D, slots, self.world)
         self.buf = symm.empty(total // 4, dtype=torch.float32, device=dev)
         self.buf.zero_()
         self.handle = symm.rendezvous(self.buf, self.group.group_name)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._side = None
         torch.cuda.synchronize(dev)
         dist.barrier(group=self.group)             # nobody stores into a buffer that is still being cleared
 
@@ -154,25 +155,44 @@ class PeerExchange:
         self.epoch.add_(1)
 
     def decode(self, fmt: int, q: torch.Tensor, tensors: dict, local_len: int, sm_scale: float, *, slot: int,
-               out: torch.Tensor, inv_tau=None) -> torch.Tensor:
+               out: torch.Tensor, inv_tau=None, append=None) -> torch.Tensor:
         """Sequence-sharded decode attention of one layer: split-K scan of the local chunk, then the
-        fused combine / exchange / merge.  Same contract as `sharded_decode`."""
+        fused combine / exchange / merge.  Same contract as `sharded_decode`.
+
+        `append` (only on the rank that stores the new token): a callable that launches the
+        quantize-append of that token; it then runs on a second stream beside the scan of the older
+        tokens, and the exchange kernel attends the new token from the cache (`local_len` counts it)."""
         from . import ops
         n = local_len
+        spec = dict(peer_ptrs=self.peer_ptrs, rank=self.rank, slot=slot, slots=self.slots, epoch=self.epoch,
+                    status=self.status, wait_ns=self.wait_ns)
+        if n <= 0:
+            if append is not None:
+                raise ValueError("the appending rank holds at least the new token")
+            # an empty shard contributes the neutral partial: one split with l = 0
+            ops.neutral_partial(q.shape[0], q.shape[1], q.shape[2], q.device)
+            return ops.combine_exchange(self.peer_ptrs, self.rank, slot, self.slots, self.epoch, out, splits=1,
+                                        status=self.status, wait_ns=self.wait_ns)
         extra = {}
         if tensors.get("kz") is not None:
             extra.update(k_zp=tensors["kz"][:, :, :n], v_zp=tensors["vz"][:, :, :n])
         if tensors.get("outlier_idx") is not None:
             extra.update(outlier_idx=tensors["outlier_idx"].contiguous(), k_side=tensors["kside"][:, :, :n],
                          v_side=tensors["vside"][:, :, :n])
-        if n > 0:
-            ops.decode_attn(fmt, q, tensors["k"][:, :, :n], tensors["v"][:, :, :n], tensors["ks"][:, :, :n],
-                            tensors["vs"][:, :, :n], None, sm_scale, head_dim=q.shape[-1], inv_tau=inv_tau, out=out,
-                            stages=1, **extra)
-            splits = ops.last_splits()
-        else:
-            # an empty shard contributes the neutral partial: one split with l = 0
-            splits = 1
-            ops.neutral_partial(q.shape[0], q.shape[1], q.shape[2], q.device)
-        return ops.combine_exchange(self.peer_ptrs, self.rank, slot, self.slots, self.epoch, out, splits=splits,
-                                    status=self.status, wait_ns=self.wait_ns)
+        scale = (None, None) if tensors.get("ks") is None else (tensors["ks"][:, :, :n], tensors["vs"][:, :, :n])
+
+        def attend(**kw):
+            return ops.decode_attn(fmt, q, tensors["k"][:, :, :n], tensors["v"][:, :, :n], scale[0], scale[1], None,
+                                   sm_scale, head_dim=q.shape[-1], inv_tau=inv_tau, out=out, exchange=spec,
+                                   **extra, **kw)
+        if append is None:
+            return attend()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=q.device)
+        main = torch.cuda.current_stream(q.device)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            append()
+        attend(stages=1, tail_tokens=1)
+        main.wait_stream(self._side)
+        return attend(stages=2, tail_tokens=1)

@@ -9,6 +9,10 @@ the reference's decode loop (src/engine/generate_loop.py:1320-1498, src/cache/in
 
 The cache must be preallocated (`cache.reserve`) because graph replay needs stable addresses;
 lengths live on the device (`write_pos_dev`, `context_lens`) and are advanced inside the graph.
+
+With `overlap_append` (default) the append of a layer runs on a second stream concurrently with the
+split-K scan of the same layer: the scan skips the new token (`tail_tokens = 1`) and the combine
+stage, which waits for both, attends it straight from the cache.  The append leaves the critical path.
 """
 from __future__ import annotations
 
@@ -22,7 +26,7 @@ from .cache import FP16KVCache, INT4KVCache, INT8KVCache
 
 class GraphedKVStackStep:
     def __init__(self, cache, num_q_heads: int, sm_scale: float, inv_tau: Optional[torch.Tensor] = None,
-                 capacity: Optional[int] = None):
+                 capacity: Optional[int] = None, overlap_append: bool = True):
         if not isinstance(cache, (INT8KVCache, INT4KVCache, FP16KVCache)):
             raise TypeError("GraphedKVStackStep needs one of this package's caches")
         self.cache = cache
@@ -56,6 +60,22 @@ class GraphedKVStackStep:
         self.host_out = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
         self.graph = None
         self.launches_per_step = 0
+        self.overlap_append = bool(overlap_append)
+        self._side = torch.cuda.Stream(device=dev) if self.overlap_append else None
+
+    def _append_then_attend(self, append, attend) -> None:
+        """`append()` launches the quantize-append, `attend(**kw)` the decode attention."""
+        if not self.overlap_append:
+            append()
+            attend()
+            return
+        main = torch.cuda.current_stream(self.device)
+        self._side.wait_stream(main)                  # this token's k / v and the position counter are ready
+        with torch.cuda.stream(self._side):
+            append()
+        attend(stages=1, tail_tokens=1)               # scan of the old tokens, independent of the append
+        main.wait_stream(self._side)
+        attend(stages=2, tail_tokens=1)               # combine + the new token
 
     # one layer: append at the device-side position, then attend over pos+1 tokens
     def _layer(self, l: int) -> None:
@@ -65,11 +85,12 @@ class GraphedKVStackStep:
         view = {n: t[:, :, :cap] for n, t in b.items()}
         fmt = c._fmt
         if fmt == _lib.FMT_FP16:
-            ops.quantize_append(fmt, _lib.SCALE_STATIC, self.k_new[l], self.v_new[l], b["k"], b["v"], None, None,
-                                self.pos, self.D)
-            ops.decode_attn(fmt, self.q[l], view["k"], view["v"], None, None, self.ctx, self.sm_scale,
-                            head_dim=self.D, inv_tau=None if self.inv_tau is None else self.inv_tau[l], out=self.out[l],
-                            max_ctx=cap)
+            self._append_then_attend(
+                lambda: ops.quantize_append(fmt, _lib.SCALE_STATIC, self.k_new[l], self.v_new[l], b["k"], b["v"],
+                                            None, None, self.pos, self.D),
+                lambda **kw: ops.decode_attn(fmt, self.q[l], view["k"], view["v"], None, None, self.ctx, self.sm_scale,
+                                             head_dim=self.D, inv_tau=None if self.inv_tau is None else self.inv_tau[l],
+                                             out=self.out[l], max_ctx=cap, **kw))
             return
         G = b["ks"].shape[-1]
         gs = self.D // G
@@ -97,12 +118,14 @@ class GraphedKVStackStep:
             oidx = c.outlier_idx[l].to(self.device).contiguous()
             app.update(outlier_idx=oidx, k_side=b["kside"], v_side=b["vside"])
             att.update(outlier_idx=oidx, k_side=view["kside"], v_side=view["vside"])
-        ops.quantize_append(fmt, policy, self.k_new[l], self.v_new[l], b["k"], b["v"], b["ks"], b["vs"], self.pos, gs,
-                            flags=flags, adaptive_margin=float(c.adaptive_static_margin),
-                            k_scale_f32=b.get("ks32"), v_scale_f32=b.get("vs32"), **app)
-        ops.decode_attn(fmt, self.q[l], view["k"], view["v"], view["ks"], view["vs"], self.ctx, self.sm_scale,
-                        head_dim=self.D, inv_tau=None if self.inv_tau is None else self.inv_tau[l], out=self.out[l],
-                        max_ctx=cap, **att)
+        self._append_then_attend(
+            lambda: ops.quantize_append(fmt, policy, self.k_new[l], self.v_new[l], b["k"], b["v"], b["ks"], b["vs"],
+                                        self.pos, gs, flags=flags, adaptive_margin=float(c.adaptive_static_margin),
+                                        k_scale_f32=b.get("ks32"), v_scale_f32=b.get("vs32"), **app),
+            lambda **kw: ops.decode_attn(fmt, self.q[l], view["k"], view["v"], view["ks"], view["vs"], self.ctx,
+                                         self.sm_scale, head_dim=self.D,
+                                         inv_tau=None if self.inv_tau is None else self.inv_tau[l], out=self.out[l],
+                                         max_ctx=cap, **att, **kw))
 
     def _body(self) -> None:
         for l in range(self.L):

@@ -31,7 +31,7 @@ def test_header_symbols_all_exported(lib):
 
 
 def test_abi_version_and_strerror(lib):
-    assert lib.kvq_abi_version() == 2
+    assert lib.kvq_abi_version() == 3
     assert lib.kvq_strerror(0) == b"ok"
     assert b"invalid" in lib.kvq_strerror(-1)
 
@@ -56,16 +56,14 @@ def test_struct_sizes_match_header(lib):
     assert ctypes.sizeof(_lib.KvqCacheSide) == 13 * 8
     assert ctypes.sizeof(_lib.KvqCombineArgs) == 4 * 4 + 10 * 8
     assert ctypes.sizeof(_lib.KvqDequantArgs) == 8 * 4 + 8 + 2 * 13 * 8 + 5 * 8
-    assert ctypes.sizeof(_lib.KvqExchangeArgs) == 4 * 4 + 2 * 8 + 2 * 4 + 8 + 2 * 4 + 6 * 8
+    assert ctypes.sizeof(_lib.KvqExchangeArgs) == 4 * 4 + 2 * 8 + 2 * 4 + 8 + 2 * 4 + 7 * 8
 
 
 def test_exchange_buffer_layout(lib):
-    off = ctypes.c_size_t(0)
-    total = lib.kvq_exchange_bytes(1, 40, 128, 48, 8, ctypes.byref(off))
+    total = lib.kvq_exchange_bytes(1, 40, 128, 48, 8)
     rows = 2 * 48 * 8 * 1 * 40
-    assert off.value == (rows * 130 * 4 + 255) // 256 * 256
-    assert total == off.value + (rows * 4 + 255) // 256 * 256
-    assert lib.kvq_exchange_bytes(0, 40, 128, 1, 2, None) == 0
+    assert total == (rows * 130 * 8 + 255) // 256 * 256
+    assert lib.kvq_exchange_bytes(0, 40, 128, 1, 2) == 0
 
 
 def test_cpu_tensors_raise_value_error():

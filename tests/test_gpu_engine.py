@@ -95,15 +95,19 @@ def test_torch_ref_impl_agrees_with_fused(tiny_model):
     assert torch.allclose(outs["triton_fused"], outs["torch_ref"], atol=2e-2, rtol=2e-2)
 
 
-def test_graphed_stack_step_equals_eager_layer_calls():
-    """The captured whole-stack step (device-side position, cache growing inside the graph) must give
-    bit-identical caches and outputs to eager per-layer append + fused decode, over several steps."""
+@pytest.mark.parametrize("overlap", (False, True))
+def test_graphed_stack_step_equals_eager_layer_calls(overlap):
+    """The captured whole-stack step (device-side position, cache growing inside the graph) against eager
+    per-layer append + fused decode, over several steps: bit-identical caches always; outputs bit-identical
+    in the serial form, and within the attention tolerance when the append runs beside the scan and the new
+    token is attended by the combine stage (another summation order)."""
     import llm_kvcache_quantization_b200 as kvq
     from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
     g = torch.Generator().manual_seed(5)
     L, B, Hq, Hkv, S, D, steps = 3, 2, 12, 2, 200, 128, 4
     for make in (lambda: kvq.INT4KVCache(L, device=DEV, group_size=32, asymmetric=True, max_seq_len=S + 8),
-                 lambda: kvq.INT8KVCache(L, device=DEV, group_size=32, clip_percentile=100.0, max_seq_len=S + 8)):
+                 lambda: kvq.INT8KVCache(L, device=DEV, group_size=32, clip_percentile=100.0, max_seq_len=S + 8),
+                 lambda: kvq.FP16KVCache(L, device=DEV, max_seq_len=S + 8)):
         ca, cb = make(), make()
         for l in range(L):
             k = torch.randn(B, Hkv, S, D, generator=g).half().to(DEV)
@@ -112,7 +116,7 @@ def test_graphed_stack_step_equals_eager_layer_calls():
                 c.reserve(l, B, Hkv, D, S + 8)
                 c.append(l, k, v)
         tau = torch.empty(L, Hq).uniform_(0.8, 1.2, generator=g).to(DEV)
-        st = GraphedKVStackStep(ca, Hq, 0.088, inv_tau=tau)
+        st = GraphedKVStackStep(ca, Hq, 0.088, inv_tau=tau, overlap_append=overlap)
         for _ in range(steps):
             hq = torch.randn(L, B, Hq, D, generator=g).half()
             hk = torch.randn(L, B, Hkv, 1, D, generator=g).half()
@@ -121,9 +125,17 @@ def test_graphed_stack_step_equals_eager_layer_calls():
             for l in range(L):
                 cb.append(l, hk[l].to(DEV), hv[l].to(DEV))
                 ref = cb.fused_decode(l, hq[l].to(DEV), 0.088, inv_tau=tau[l])
-                assert torch.equal(got[l].to(DEV), ref), (l, (got[l].to(DEV).float() - ref.float()).abs().max())
+                err = (got[l].to(DEV).float() - ref.float()).abs()
+                if overlap:
+                    assert bool((err <= 2e-3 + 1e-2 * ref.float().abs()).all()), (l, float(err.max()))
+                else:
+                    assert torch.equal(got[l].to(DEV), ref), (l, float(err.max()))
         assert ca.get_seq_len() == cb.get_seq_len() == S + steps
         for l in range(L):
+            if isinstance(ca, kvq.FP16KVCache):
+                for x, y in zip(ca.get_kv(l), cb.get_kv(l)):
+                    assert torch.equal(x, y)
+                continue
             ta, tb = ca.get_decode_tensors(l), cb.get_decode_tensors(l)
             for n in ("k", "v", "ks", "vs"):
                 assert torch.equal(ta[n], tb[n])

@@ -67,12 +67,24 @@ def _worker(rank, world, port, ret):
         xchg = P.PeerExchange(B, Hq, D, slots=2)
         out2 = torch.empty(2, B, Hq, D, dtype=torch.float16, device=dev)
         worst, good = 0.0, True
+        local.reserve(0, B, Hkv, D, sh.chunk + 32)
+        t = {n: b for n, b in local._bufs[0].items()}
+        t["outlier_idx"] = idx.to(dev)
+        is_owner = sh.owner_of(S) == rank
         for step in range(5):
             qs = (q * (1.0 + 0.25 * step)).to(dev)
+            # one more token per step, stored by the owner of the sequence end: its append runs beside the
+            # scan and the exchange kernel attends the new token from the cache
+            kt = torch.randn(B, Hkv, 1, D, generator=g).half().to(dev)
+            vt = torch.randn(B, Hkv, 1, D, generator=g).half().to(dev)
+            app = None
+            if is_owner:
+                n_local += 1
+                app = lambda: local.append(0, kt, vt)
             xchg.advance()
             for slot in range(2):
                 xchg.decode(_lib.FMT_INT4, qs if slot == 0 else -qs, t, n_local, 0.088, slot=slot, out=out2[slot],
-                            inv_tau=tau.to(dev))
+                            inv_tau=tau.to(dev), append=app if slot == 0 else None)
             torch.cuda.synchronize()
             for slot in range(2):
                 want = P.sharded_decode(_lib.FMT_INT4, qs if slot == 0 else -qs, t, n_local, 0.088, send=send, recv=recv,
