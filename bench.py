@@ -41,6 +41,8 @@ WORKLOADS = {
                desc="C3: Qwen2.5-1.5B geometry, batch 32, ctx 16384, INT4 group-32 + 3 fp16 outlier channels (4 layers)"),
     "c4": dict(layers=2, B=64, Hq=28, Hkv=4, S=32768, kind="int8_dyn", n_out=0,
                desc="C4: Qwen2.5-7B geometry, batch 64, ctx 32768, INT8 group-32 (2 layers)"),
+    "c2_fp16": dict(layers=8, B=16, Hq=12, Hkv=2, S=8192, kind="fp16", n_out=0,
+                    desc="config-2 shape with an UNQUANTISED fp16 cache (comparison point, 8 layers): batch 16, ctx 8192"),
     "c5": dict(layers=4, B=1, Hq=40, Hkv=8, S=131072, kind="int4_outlier", n_out=1,
                desc="C5: Qwen2.5-14B geometry, batch 1, ctx 131072, INT4 group-32 + 1 fp16 outlier channel (4 layers)"),
 }
@@ -51,12 +53,14 @@ G = D // GS
 
 # DRAM traffic / algorithmic bytes of the split-K scan, from the ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same kernel, scaled by token-heads)
-NCU_TRAFFIC_RATIO = {"int4_asym": 1.003, "int8_dyn": 1.004, "int8_static": 1.004, "int4_outlier": 1.028}
+NCU_TRAFFIC_RATIO = {"fp16": 1.0, "int4_asym": 1.003, "int8_dyn": 1.004, "int8_static": 1.004, "int4_outlier": 1.028}
 
 
 def bytes_per_token_head(kind: str, n_out: int) -> int:
     """Algorithmic HBM bytes per cached token per KV head (K and V): payload + per-token
     fp16 scales (+ zero-points) (+ fp16 outlier side values), each counted once."""
+    if kind == "fp16":
+        return 2 * 2 * D
     if kind in ("int8_static", "int8_dyn"):
         return 2 * (D + 2 * G)
     if kind == "int4_asym":
@@ -127,7 +131,9 @@ def build_workload(wl: dict, dev, seed: int, extra_slots: int):
     cap = S + extra_slots
     kw = dict(device=dev, group_size=GS, max_seq_len=cap)
     outlier_idx = None
-    if kind == "int8_static":
+    if kind == "fp16":
+        cache = kvq.FP16KVCache(L, device=dev, max_seq_len=cap)
+    elif kind == "int8_static":
         tab = torch.full((L, Hkv, G), 4.5 / 127, dtype=torch.float16, device=dev)
         cache = kvq.INT8KVCache(L, static_k_scale=tab, static_v_scale=tab, **kw)
     elif kind == "int8_dyn":
@@ -172,7 +178,7 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
     L, B, Hkv, S, kind = wl["layers"], wl["B"], wl["Hkv"], wl["S"], wl["kind"]
     dev = q.device
     ctx = torch.full((B,), S + 1, dtype=torch.int32, device=dev)
-    fmt = _lib.FMT_INT8 if kind.startswith("int8") else _lib.FMT_INT4
+    fmt = _lib.FMT_FP16 if kind == "fp16" else _lib.FMT_INT8 if kind.startswith("int8") else _lib.FMT_INT4
     splits = int(os.environ.get("KVQ_BENCH_SPLITS", "0"))
     layers = []
     for l in range(L):
@@ -184,6 +190,8 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
         elif kind == "int8_dyn":
             policy = _lib.SCALE_DYNAMIC_PCT
             app.update(quantile=1.0)
+        elif kind == "fp16":
+            policy = _lib.SCALE_STATIC
         else:
             policy = _lib.SCALE_STATIC
             app.update(k_static=cache._static_table("k", l, Hkv, G, dev), v_static=cache._static_table("v", l, Hkv, G, dev))
@@ -193,6 +201,7 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
             app.update(outlier_idx=oidx, k_side=b["kside"], v_side=b["vside"])
             att.update(outlier_idx=oidx, k_side=view["kside"], v_side=view["vside"])
         layers.append((b, view, policy, app, att))
+    gsz = D if kind == "fp16" else GS
 
     # The append of a layer runs on a second stream, concurrently with the split-K scan of the old tokens
     # (tail_tokens = 1); the combine stage waits for both and attends the new token from the cache.
@@ -200,7 +209,7 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
     side = torch.cuda.Stream(device=dev) if overlap else None
 
     def attend(l, view, att, **kw):
-        ops.decode_attn(fmt, q[l], view["k"], view["v"], view["ks"], view["vs"], ctx, 1.0 / D ** 0.5,
+        ops.decode_attn(fmt, q[l], view["k"], view["v"], view.get("ks"), view.get("vs"), ctx, 1.0 / D ** 0.5,
                         head_dim=D, inv_tau=inv_tau[l], splits=splits, out=out[l], max_ctx=S + 1, **att, **kw)
 
     def step():
@@ -209,15 +218,62 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
                 main = torch.cuda.current_stream(dev)
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
-                    ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], S, GS, **app)
+                    ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b.get("ks"), b.get("vs"), S, gsz, **app)
                 attend(l, view, att, stages=1, tail_tokens=1)
                 main.wait_stream(side)
                 attend(l, view, att, stages=2, tail_tokens=1)
                 continue
             if with_append:
-                ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b["ks"], b["vs"], S, GS, **app)
+                ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b.get("ks"), b.get("vs"), S, gsz, **app)
             attend(l, view, att, stages=stages)
     return step, (lambda: ops.last_splits())
+
+
+def time_aux(wl, cache, dev, iters=10):
+    """The kernels either side of the decode path, at this workload's shape, one layer per call, CUDA events:
+    `get_kv` (kvq_dequantize of a whole layer) and a bulk prefill append of S tokens (quantize, pack, store)."""
+    import torch
+    B, Hkv, S, kind, n_out = wl["B"], wl["Hkv"], wl["S"], wl["kind"], wl["n_out"]
+    L = wl["layers"]
+    res = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    read_b = B * Hkv * S * bytes_per_token_head(kind, n_out)
+    for _ in range(2):
+        for l in range(min(L, 2)):
+            cache.get_kv(l)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(iters):
+        kv = cache.get_kv(i % L)
+    e1.record(); torch.cuda.synchronize()
+    del kv
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    res["get_kv"] = {"us_per_layer": us, "GBps": (read_b + 2 * B * Hkv * S * D * 2) / us / 1e3,
+                     "bytes": "payload + scales read, 2 x fp16 [B,Hkv,S,D] written"}
+    gen = torch.Generator(device=dev).manual_seed(7)
+    chunk = max(1, min(S, (1 << 25) // (B * Hkv * D)))
+    k = torch.randn(B, Hkv, chunk, D, device=dev, generator=gen).half()
+    v = torch.randn(B, Hkv, chunk, D, device=dev, generator=gen).half()
+    old = list(cache._layer_seq_lens)
+
+    def refill(l):
+        cache._layer_seq_lens[l] = 0
+        for s0 in range(0, S - chunk + 1, chunk):
+            cache.append(l, k, v)
+    refill(0)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(iters):
+        refill(i % L)
+    e1.record(); torch.cuda.synchronize()
+    n_tok = (S // chunk) * chunk
+    for l in range(L):                       # restore the nominal lengths (contents are synthetic either way)
+        cache._layer_seq_lens[l] = old[l]
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    res["prefill_append"] = {"us_per_layer": us, "tokens": n_tok,
+                             "GBps": (2 * B * Hkv * n_tok * D * 2 + B * Hkv * n_tok * bytes_per_token_head(kind, n_out)) / us / 1e3,
+                             "bytes": "fp16 K and V read, payload + scales written"}
+    return res
 
 
 def capture(step):
@@ -511,6 +567,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
+    ap.add_argument("--aux", action="store_true",
+                    help="also time the neighbouring kernels at this workload's shape: bulk prefill quantize-append "
+                         "(T = context) and the dequantising get_kv, one layer each")
     ap.add_argument("--collective", default="fused", choices=("fused", "nccl"),
                     help="sequence-sharded mode: the library's fused combine/peer-store/merge kernel, or "
                          "combine + NCCL all-gather + merge")
@@ -631,8 +690,12 @@ def main():
                "api": "GraphedKVStackStep.step(host_q, host_k, host_v) -> host_out: pinned H2D of q/k/v, one CUDA "
                       "graph (append + attention for every layer), pinned D2H of the outputs, stream sync"}
 
+    aux = None
+    if args.aux and wl["kind"] != "fp16":
+        aux = time_aux(wl, cache, dev)
+
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and wl["kind"] != "fp16":
         per_pass, rows, threads = cpu_sample(wl, target_s=12.0)
         step_s = per_pass * L * (B / rows)
         cpu = {"value": B / step_s, "unit": "tokens/s", "cores": threads, "kind": "port",
@@ -651,6 +714,8 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": args.steps * L * 3, "clocks": clocks,
         }
+        if aux is not None:
+            line["aux"] = aux
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -959,22 +959,34 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < nh * D; i += kMmaWarps * 32) {
-        const int h = i / D, d = i % D;
+    // per (warp, head) merge weight, per head total: computed once, not once per channel
+    __shared__ float mrg_w[kMmaWarps][kHeadsPerCta];
+    __shared__ float mrg_ml[kHeadsPerCta][2];
+    if (threadIdx.x < kHeadsPerCta) {
+        const int h = threadIdx.x;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kMmaWarps; ++w) M = fmaxf(M, red_ml[w][h][0]);
-        float ov = 0.f, L = 0.f;
+        float L = 0.f;
 #pragma unroll
         for (int w = 0; w < kMmaWarps; ++w) {
             const float mw = red_ml[w][h][0];
             const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-            ov += red_acc[((size_t)w * kHeadsPerCta + h) * D + d] * wgt;
+            mrg_w[w][h] = wgt;
             L += red_ml[w][h][1] * wgt;
         }
+        mrg_ml[h][0] = M;
+        mrg_ml[h][1] = L;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nh * D; i += kMmaWarps * 32) {
+        const int h = i / D, d = i % D;
+        float ov = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) ov += red_acc[((size_t)w * kHeadsPerCta + h) * D + d] * mrg_w[w][h];
         const long long row = ((long long)b * a.Hq + (h0 + h)) * p.splits + split;
         p.ws_o[row * D + d] = ov;
-        if (d == 0) { p.ws_ml[row * 2] = M; p.ws_ml[row * 2 + 1] = L; }
+        if (d == 0) { p.ws_ml[row * 2] = mrg_ml[h][0]; p.ws_ml[row * 2 + 1] = mrg_ml[h][1]; }
     }
 }
 

@@ -322,8 +322,13 @@ static int launch(const QuantParams& p, cudaStream_t st) {
     const KvqAppendArgs& a = p.a;
     const bool rope_vec_ok = !a.rope_cos || ((a.rotary_dim % 64) == 0 && ((((uintptr_t)a.rope_cos | (uintptr_t)a.rope_sin) & 15) == 0) &&
                                              (a.rope_stride_b & 7) == 0 && (a.rope_stride_t & 7) == 0);
-    if (p.a.group_size == 32 && !dyn_sort && side_vec_ok(p.a.k) && side_vec_ok(p.a.v) && rope_vec_ok)
-        return launch_gs<FMT, POLICY, 32>(p, st);
+    if (!dyn_sort && side_vec_ok(p.a.k) && side_vec_ok(p.a.v) && rope_vec_ok) {
+        // register-resident groups; rotary partners must be whole groups (rotary_dim a multiple of 2 * GS)
+        const bool rope = a.rope_cos != nullptr;
+        if (p.a.group_size == 32) return launch_gs<FMT, POLICY, 32>(p, st);
+        if (p.a.group_size == 16) return launch_gs<FMT, POLICY, 16>(p, st);
+        if (p.a.group_size == 64 && (!rope || a.rotary_dim % 128 == 0)) return launch_gs<FMT, POLICY, 64>(p, st);
+    }
     return launch_gs<FMT, POLICY, 0>(p, st);
 }
 
