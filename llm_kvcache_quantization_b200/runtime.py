@@ -59,6 +59,7 @@ class GraphedKVStackStep:
         self.host_v = torch.empty(self.v_new.shape, dtype=torch.float16).pin_memory()
         self.host_out = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
         self.graph = None
+        self.graph_host = None
         self.launches_per_step = 0
         self.overlap_append = bool(overlap_append)
         self._side = torch.cuda.Stream(device=dev) if self.overlap_append else None
@@ -151,6 +152,17 @@ class GraphedKVStackStep:
         self.ctx.fill_(self._len + 1)
         self.graph = g
         self.launches_per_step = self.L * 3
+        # the host-buffer form: uploads, the step and the download as ONE graph launch
+        gh = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gh):
+            self.q.copy_(self.host_q, non_blocking=True)
+            self.k_new.copy_(self.host_k, non_blocking=True)
+            self.v_new.copy_(self.host_v, non_blocking=True)
+            self._body()
+            self.host_out.copy_(self.out, non_blocking=True)
+        self.pos.fill_(self._len)
+        self.ctx.fill_(self._len + 1)
+        self.graph_host = gh
 
     def step_device(self) -> torch.Tensor:
         """Advance by one token with inputs already in `self.q / self.k_new / self.v_new`."""
@@ -169,15 +181,19 @@ class GraphedKVStackStep:
         """Host-to-host step: upload this token's q / k / v for all layers (pinned memory, one copy
         each), replay the graph, download the attention outputs.  Returns the pinned output buffer
         (valid until the next call) after synchronising the stream."""
+        if self.graph is None:
+            self.capture()
+        if self._len + 1 > self.capacity:
+            raise ValueError(f"cache capacity {self.capacity} exhausted")
         if host_q is not self.host_q:
             self.host_q.copy_(host_q)
             self.host_k.copy_(host_k)
             self.host_v.copy_(host_v)
-        self.q.copy_(self.host_q, non_blocking=True)
-        self.k_new.copy_(self.host_k, non_blocking=True)
-        self.v_new.copy_(self.host_v, non_blocking=True)
-        self.step_device()
-        self.host_out.copy_(self.out, non_blocking=True)
+        self.graph_host.replay()                       # pinned H2D x3, every layer, pinned D2H
+        self._len += 1
+        for i in range(self.L):
+            self.cache._layer_seq_lens[i] = self._len
+        self.cache._seq_len = self._len
         torch.cuda.current_stream(self.device).synchronize()
         return self.host_out
 
