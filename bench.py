@@ -229,6 +229,83 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
     return step, (lambda: ops.last_splits())
 
 
+MODEL_GEOMETRY = {   # (Hq, Hkv) -> hidden, intermediate size, vocabulary of the Qwen2.5 member with that attention shape
+    (12, 2): (1536, 8960, 151936), (28, 4): (3584, 18944, 152064), (40, 8): (5120, 13824, 152064),
+}
+
+
+def time_model_step(wl, cache, dev, steps=5):
+    """One decode step of a random-init Qwen2 model with the workload's geometry (model-card sizes, weights drawn
+    on the GPU) through the patched attention forward: HF embedding / norms / projections / MLP / lm_head in eager
+    PyTorch, RoPE + quantize-append + fused decode attention per layer from this library, over the synthetic cache
+    already built.  The model has as many layers as the cache.  Times `steps` steps with CUDA events."""
+    import torch
+    import transformers
+    from llm_kvcache_quantization_b200 import engine as E
+    L, B, Hq, Hkv, S = wl["layers"], wl["B"], wl["Hq"], wl["Hkv"], wl["S"]
+    hidden, inter, vocab = MODEL_GEOMETRY[(Hq, Hkv)]
+    cfg = transformers.Qwen2Config(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=L,
+                                   num_attention_heads=Hq, num_key_value_heads=Hkv, head_dim=D,
+                                   max_position_embeddings=S + 4096, rope_theta=1e6, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.float16)
+    try:
+        with torch.device(dev):
+            model = transformers.Qwen2ForCausalLM(cfg)
+    finally:
+        torch.set_default_dtype(prev)
+    model = model.eval()
+    n_params = sum(p.numel() for p in model.parameters())
+    start = cache.get_seq_len()
+    tok = torch.randint(0, vocab, (B, 1), device=dev)
+    E.apply_int8_fused_patch(model)
+    try:
+        wrapper = E.INT8CacheWrapperContainer(cache, L)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        times = []
+        with torch.no_grad():
+            for i in range(steps + 2):
+                pos = torch.full((B, 1), cache.get_seq_len(), dtype=torch.long, device=dev)
+                torch.cuda.synchronize()
+                e0.record()
+                out = model(input_ids=tok, position_ids=pos, past_key_values=wrapper, use_cache=True)
+                tok = out.logits[:, -1].argmax(-1, keepdim=True)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    times.append(e0.elapsed_time(e1))
+        assert bool(torch.isfinite(out.logits.float()).all())
+    finally:
+        E.remove_int8_fused_patch(model)
+    ms = statistics.median(times)
+    # the same step as ONE CUDA graph (device-side positions, greedy token fed back on the device)
+    from llm_kvcache_quantization_b200.runtime import GraphedModelStep
+    graphed = None
+    st = GraphedModelStep(model, cache, B)
+    try:
+        with torch.no_grad():
+            st.capture(tok)
+            for _ in range(2):
+                st.step()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(steps):
+                st.step()
+            e1.record()
+            torch.cuda.synchronize()
+        gms = e0.elapsed_time(e1) / steps
+        graphed = {"ms_per_step": gms, "tokens_per_s": B / (gms * 1e-3),
+                   "what": "runtime.GraphedModelStep: the whole model step (embedding .. argmax, token feedback) "
+                           "captured once and replayed"}
+    finally:
+        st.close()
+    return {"ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "graphed": graphed, "layers": L, "parameters": n_params,
+            "context_start": start, "steps": steps,
+            "what": "eager HF Qwen2 forward (random-init weights of the model-card sizes) with the library's patched "
+                    "attention: fused RoPE + quantize-append, fused decode attention; argmax of the logits read back"}
+
+
 def time_aux(wl, cache, dev, iters=10):
     """The kernels either side of the decode path, at this workload's shape, one layer per call, CUDA events:
     `get_kv` (kvq_dequantize of a whole layer) and a bulk prefill append of S tokens (quantize, pack, store)."""
@@ -570,6 +647,10 @@ def main():
     ap.add_argument("--aux", action="store_true",
                     help="also time the neighbouring kernels at this workload's shape: bulk prefill quantize-append "
                          "(T = context) and the dequantising get_kv, one layer each")
+    ap.add_argument("--model-step", action="store_true",
+                    help="also time one decode step of a random-init Qwen2 model of the workload's geometry through "
+                         "the patched attention forward over the same synthetic cache (weights, MLP, eager Python "
+                         "included); reported under model_step")
     ap.add_argument("--collective", default="fused", choices=("fused", "nccl"),
                     help="sequence-sharded mode: the library's fused combine/peer-store/merge kernel, or "
                          "combine + NCCL all-gather + merge")
@@ -606,7 +687,7 @@ def main():
         return
 
     L, B, Hq, Hkv, S = wl["layers"], wl["B"], wl["Hq"], wl["Hkv"], wl["S"]
-    e2e_slots = args.steps + args.warmup + 8
+    e2e_slots = args.steps + args.warmup + 8 + (64 if args.model_step else 0)
     cache, q, k_new, v_new, inv_tau = build_workload(wl, dev, seed=1234 + rank, extra_slots=e2e_slots)
     out = torch.empty(L, B, Hq, D, dtype=torch.float16, device=dev)
     small = L * B * Hkv * S * bytes_per_token_head(wl["kind"], wl["n_out"]) <= 126e6
@@ -695,6 +776,10 @@ def main():
     if args.aux and wl["kind"] != "fp16":
         aux = time_aux(wl, cache, dev)
 
+    model_step = None
+    if args.model_step and world == 1:
+        model_step = time_model_step(wl, cache, dev, steps=max(3, min(args.steps, 10)))
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and wl["kind"] != "fp16":
         per_pass, rows, threads = cpu_sample(wl, target_s=12.0)
@@ -717,6 +802,8 @@ def main():
         }
         if aux is not None:
             line["aux"] = aux
+        if model_step is not None:
+            line["model_step"] = model_step
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

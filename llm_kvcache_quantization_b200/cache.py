@@ -63,6 +63,7 @@ class _CacheBase:
         self._min_capacity = 256
         self._bufs: List[Optional[Dict[str, Tensor]]] = [None] * num_layers
         self._layer_seq_lens: List[int] = [0] * num_layers
+        self._dev_positions = None
         self._layer_capacity: List[int] = [0] * num_layers
         self._seq_len = 0
         self.decode_stats: Dict[str, object] = _new_stats()
@@ -165,13 +166,45 @@ class _CacheBase:
         bufs = self._bufs[layer_id]
         if bufs is None:
             raise ValueError(f"Cache for layer {layer_id} is empty")
-        n = self._layer_seq_lens[layer_id]
+        n = self._layer_seq_lens[layer_id] if self._dev_positions is None else self._dev_positions[2]
         return tuple(bufs[name][:, :, :n] for name in names)
 
     def _finish_append(self, layer_id: int, target_len: int) -> None:
+        if self._dev_positions is not None:
+            return                                   # lengths live on the device; advance_host_lengths() follows
         self._layer_seq_lens[layer_id] = target_len
         if layer_id == 0:
             self._seq_len = target_len
+
+    # ---- device-side positions: what a captured (CUDA-graph) decode step needs.  While this mode is on,
+    # single-token appends write at `*pos` (int32 device scalar), fused_decode attends over `ctx` (int32 [B]
+    # device tensor) inside views of the first `capacity` slots, and nothing here touches host-side lengths.
+    def use_device_positions(self, pos: Tensor, ctx: Tensor, capacity: int) -> None:
+        if pos.dtype != torch.int32 or ctx.dtype != torch.int32 or not pos.is_cuda or not ctx.is_cuda:
+            raise ValueError("pos / ctx must be int32 CUDA tensors")
+        for l in range(self.num_layers):
+            if self._bufs[l] is None or self._bufs[l]["k"].shape[2] < capacity:
+                raise ValueError(f"reserve at least {capacity} slots in layer {l} before switching to device positions")
+        self._dev_positions = (pos, ctx, int(capacity))
+
+    def use_host_positions(self) -> None:
+        self._dev_positions = None
+
+    def advance_host_lengths(self, tokens: int = 1) -> None:
+        """Bring the host-side lengths in line after `tokens` replays of a captured step."""
+        for l in range(self.num_layers):
+            self._layer_seq_lens[l] += tokens
+        self._seq_len = self._layer_seq_lens[0]
+
+    def _write_slot(self, layer_id: int, batch: int, heads: int, head_dim: int, tokens: int):
+        """(first slot to write - an int, or the device scalar -, host length before the append)."""
+        old = self._layer_seq_lens[layer_id]
+        if self._dev_positions is None:
+            self._ensure_capacity(layer_id, batch, heads, head_dim, old + tokens)
+            return old, old
+        if tokens != 1:
+            raise ValueError("device-side positions serve single-token appends")
+        return self._dev_positions[0], old
 
     @staticmethod
     def _rope_tables(cos: Tensor, sin: Tensor, batch: int, tokens: int, device):
@@ -247,22 +280,20 @@ class FP16KVCache(_CacheBase):
     def append(self, layer_id: int, k: Tensor, v: Tensor) -> None:
         self._check_append(layer_id, k, v)
         B, H, T, D = k.shape
-        old = self._layer_seq_lens[layer_id]
-        self._ensure_capacity(layer_id, B, H, D, old + T)
+        slot, old = self._write_slot(layer_id, B, H, D, T)
         bufs = self._bufs[layer_id]
         ops.quantize_append(FMT_FP16, SCALE_STATIC, k.to(torch.float16), v.to(torch.float16),
-                            bufs["k"], bufs["v"], None, None, old, D)
+                            bufs["k"], bufs["v"], None, None, slot, D)
         self._finish_append(layer_id, old + T)
 
     def append_rotary(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
         self._check_append(layer_id, k, v)
         B, H, T, D = k.shape
-        old = self._layer_seq_lens[layer_id]
-        self._ensure_capacity(layer_id, B, H, D, old + T)
+        slot, old = self._write_slot(layer_id, B, H, D, T)
         bufs = self._bufs[layer_id]
         c16, s16 = self._rope_tables(cos, sin, B, T, k.device)
         q_rot = ops.quantize_append(FMT_FP16, SCALE_STATIC, k.to(torch.float16), v.to(torch.float16),
-                                    bufs["k"], bufs["v"], None, None, old, D, rope_cos=c16, rope_sin=s16,
+                                    bufs["k"], bufs["v"], None, None, slot, D, rope_cos=c16, rope_sin=s16,
                                     q=q.to(torch.float16))
         self._finish_append(layer_id, old + T)
         return q_rot
@@ -281,7 +312,8 @@ class FP16KVCache(_CacheBase):
         original = q.dtype
         if original != torch.float16:
             q = q.to(torch.float16)
-        res = ops.decode_attn(FMT_FP16, q, k, v, None, None, None, float(sm_scale), head_dim=q.shape[-1],
+        ctx = None if self._dev_positions is None else self._dev_positions[1]
+        res = ops.decode_attn(FMT_FP16, q, k, v, None, None, ctx, float(sm_scale), head_dim=q.shape[-1],
                               inv_tau=None if inv_tau is None else inv_tau.float(), out=out)
         return res if original == torch.float16 else res.to(original)
 
@@ -410,8 +442,7 @@ class _QuantCache(_CacheBase):
             c16, s16 = self._rope_tables(rope[1], rope[2], B, T, k.device)
         G = self._num_groups(D)
         gs = D // G
-        old = self._layer_seq_lens[layer_id]
-        self._ensure_capacity(layer_id, B, H, D, old + T)
+        slot, old = self._write_slot(layer_id, B, H, D, T)
         bufs = self._bufs[layer_id]
         kw = dict(k_scale_f32=bufs.get("ks32"), v_scale_f32=bufs.get("vs32"))
         oidx = None
@@ -440,10 +471,10 @@ class _QuantCache(_CacheBase):
             kw.update(quantile=(max(min(p / 100.0, 1.0), 0.0) if p < 100.0 else 1.0))
         if rope is not None:
             kw.update(rope_cos=c16, rope_sin=s16, q=rope[0].to(torch.float16))
-        q_rot = ops.quantize_append(self._fmt, policy, k, v, bufs["k"], bufs["v"], bufs["ks"], bufs["vs"], old, gs,
+        q_rot = ops.quantize_append(self._fmt, policy, k, v, bufs["k"], bufs["v"], bufs["ks"], bufs["vs"], slot, gs,
                                     flags=flags, adaptive_margin=float(self.adaptive_static_margin), **kw)
         self._finish_append(layer_id, old + T)
-        if self.validate_inputs and policy == SCALE_STATIC and rope is None:
+        if self.validate_inputs and policy == SCALE_STATIC and rope is None and self._dev_positions is None:
             self._warn_if_clipped(layer_id, k, v, old, T)
         return q_rot
 
@@ -492,7 +523,8 @@ class _QuantCache(_CacheBase):
             extra.update(outlier_idx=t["outlier_idx"].to(q.device).contiguous(), k_side=t["kside"], v_side=t["vside"])
         if inv_tau is not None and inv_tau.dtype != torch.float32:
             inv_tau = inv_tau.float()
-        res = ops.decode_attn(self._fmt, q, t["k"], t["v"], t["ks"], t["vs"], None, float(sm_scale),
+        ctx = None if self._dev_positions is None else self._dev_positions[1]
+        res = ops.decode_attn(self._fmt, q, t["k"], t["v"], t["ks"], t["vs"], ctx, float(sm_scale),
                               head_dim=q.shape[-1], inv_tau=inv_tau, out=out, **extra)
         return res if original == torch.float16 else res.to(original)
 

@@ -26,6 +26,8 @@ struct DequantParams {
     KvqDequantArgs a;
     int chunks;                  // D / 8
     unsigned per_row_block;      // S * chunks: work items of one (side, b, h)
+    int chunk_shift;             // log2(chunks)              } when chunks and group_size are powers of two
+    int group_shift;             // log2(group_size / 8)      } (POW2 instantiation: no division per chunk)
 };
 
 __device__ __forceinline__ uint32_t dq_prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -54,7 +56,7 @@ __device__ __forceinline__ __half2 dq_nib_hi(uint32_t w) {       // bits 4-7 of 
 // (memory-level parallelism: the kernel has no reuse and little arithmetic).
 constexpr int kDqUnroll = 4;
 
-template <int FMT, bool ASYM>
+template <int FMT, bool ASYM, bool POW2>
 __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) {
     const KvqDequantArgs& a = p.a;
     const int bh = blockIdx.y % (a.B * a.Hkv), side = blockIdx.y / (a.B * a.Hkv);
@@ -74,15 +76,20 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const DequantParams p) 
     for (int u = 0; u < kDqUnroll; ++u) {
         const unsigned i = base + 256u * u;
         ok[u] = i < p.per_row_block;
-        s[u] = (int)(i / (unsigned)p.chunks);
-        c[u] = (int)(i - (unsigned)s[u] * (unsigned)p.chunks);
+        if (POW2) {
+            s[u] = (int)(i >> p.chunk_shift);
+            c[u] = (int)(i & (unsigned)(p.chunks - 1));
+        } else {
+            s[u] = (int)(i / (unsigned)p.chunks);
+            c[u] = (int)(i - (unsigned)s[u] * (unsigned)p.chunks);
+        }
         w[u] = make_uint2(0u, 0u);
         sc[u] = zp[u] = __half();
         if (ok[u]) {
             const char* row = pay0 + s[u] * cs.pay_stride_s;
             if (FMT == KVQ_FMT_INT8) w[u] = *(const uint2*)(row + 8 * c[u]);
             else w[u].x = *(const uint32_t*)(row + 4 * c[u]);
-            const long long so = s[u] * cs.sc_stride_s + (8 * c[u]) / a.group_size;
+            const long long so = s[u] * cs.sc_stride_s + (POW2 ? (c[u] >> p.group_shift) : (8 * c[u]) / a.group_size);
             sc[u] = sc0[so];
             if (ASYM) zp[u] = zp0[so];
         }
@@ -173,12 +180,19 @@ extern "C" int kvq_dequantize(const KvqDequantArgs* args, kvq_stream_t stream) {
     p.per_row_block = (unsigned)a.S * (unsigned)p.chunks;
     dim3 grid((p.per_row_block + 256u * kDqUnroll - 1u) / (256u * kDqUnroll), (unsigned)(a.B * a.Hkv * (two ? 2 : 1)));
     cudaStream_t st = (cudaStream_t)stream;
+    auto is_pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
+    auto log2i = [](int v) { int l = 0; while ((1 << l) < v) ++l; return l; };
+    const bool pow2 = is_pow2(p.chunks) && is_pow2(gs / 8);
+    p.chunk_shift = pow2 ? log2i(p.chunks) : 0;
+    p.group_shift = pow2 ? log2i(gs / 8) : 0;
+#define KVQ_DQ(F, A)                                                                  \
+    if (pow2) dequantize_kernel<F, A, true><<<grid, 256, 0, st>>>(p);                 \
+    else dequantize_kernel<F, A, false><<<grid, 256, 0, st>>>(p);
     if (a.format == KVQ_FMT_INT8) {
-        if (asym) dequantize_kernel<KVQ_FMT_INT8, true><<<grid, 256, 0, st>>>(p);
-        else dequantize_kernel<KVQ_FMT_INT8, false><<<grid, 256, 0, st>>>(p);
+        if (asym) { KVQ_DQ(KVQ_FMT_INT8, true) } else { KVQ_DQ(KVQ_FMT_INT8, false) }
     } else {
-        if (asym) dequantize_kernel<KVQ_FMT_INT4, true><<<grid, 256, 0, st>>>(p);
-        else dequantize_kernel<KVQ_FMT_INT4, false><<<grid, 256, 0, st>>>(p);
+        if (asym) { KVQ_DQ(KVQ_FMT_INT4, true) } else { KVQ_DQ(KVQ_FMT_INT4, false) }
     }
+#undef KVQ_DQ
     return check_launch();
 }

@@ -204,3 +204,92 @@ class GraphedKVStackStep:
     @property
     def d2h_bytes_per_step(self) -> int:
         return self.out.numel() * 2
+
+
+class GraphedModelStep:
+    """One greedy decode step of a HuggingFace causal LM as ONE CUDA graph: embedding, every layer (norms,
+    projections, the patched attention with fused RoPE + quantize-append + fused decode attention, MLP),
+    final norm, lm_head, argmax - and the feedback of the chosen token into the next step's input.  The
+    per-step host work of the reference's decode loop (src/engine/generate_loop.py:1320-1498: Python
+    dispatch of every op, position tensors, cache bookkeeping) shrinks to one graph launch.
+
+    The cache must hold the prompt already and have `capacity` slots reserved in every layer; positions
+    live on the device and advance inside the graph.  The attention-forward patch of `engine` is applied
+    for the lifetime of this object (`close()` removes it).
+    """
+
+    def __init__(self, model, cache, batch: int, capacity: Optional[int] = None):
+        from . import engine as E
+        self.model, self.cache = model, cache
+        self.L = cache.num_layers
+        lens = set(cache._layer_seq_lens)
+        if len(lens) != 1:
+            raise ValueError("all layers must hold the same number of tokens")
+        self._len = lens.pop()
+        b0 = cache._bufs[0]
+        if b0 is None:
+            raise ValueError("prefill the cache (and reserve room for the new tokens) first")
+        self.capacity = min(b0["k"].shape[2], capacity or cache._layer_capacity[0])
+        dev = b0["k"].device
+        self.device, self.B = dev, batch
+        self.pos = torch.full((1,), self._len, dtype=torch.int32, device=dev)
+        self.ctx = torch.full((batch,), self._len + 1, dtype=torch.int32, device=dev)
+        self.pos_ids = torch.full((batch, 1), self._len, dtype=torch.long, device=dev)
+        self.tok = torch.zeros((batch, 1), dtype=torch.long, device=dev)
+        self.next_tok = torch.zeros((batch, 1), dtype=torch.long, device=dev)
+        self.logits = None
+        self.graph = None
+        self._E = E
+        E.apply_int8_fused_patch(model)
+        self.wrapper = E.INT8CacheWrapperContainer(cache, self.L)
+
+    def _body(self) -> None:
+        out = self.model(input_ids=self.tok, position_ids=self.pos_ids, past_key_values=self.wrapper, use_cache=True)
+        self.logits = out.logits
+        self.next_tok.copy_(out.logits[:, -1].argmax(-1, keepdim=True))
+        self.tok.copy_(self.next_tok)                 # greedy feedback: the next replay consumes it
+        self.pos.add_(1)
+        self.ctx.add_(1)
+        self.pos_ids.add_(1)
+
+    def _rewind(self) -> None:
+        self.pos.fill_(self._len)
+        self.ctx.fill_(self._len + 1)
+        self.pos_ids.fill_(self._len)
+
+    def capture(self, first_token: torch.Tensor) -> None:
+        """`first_token` [B,1]: the token the prompt's last logits chose."""
+        self.cache.use_device_positions(self.pos, self.ctx, self.capacity)
+        keep = first_token.to(self.device).clone()
+        with torch.no_grad():
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(s):
+                self.tok.copy_(keep)
+                self._body()                          # warm-up: lazy initialisation, workspaces, autotuned GEMMs
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            torch.cuda.synchronize(self.device)
+            self._rewind()
+            self.tok.copy_(keep)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._body()
+            self._rewind()
+            self.tok.copy_(keep)
+        self.graph = g
+
+    def step(self) -> torch.Tensor:
+        """Advance by one token; returns the device tensor [B,1] of the tokens just chosen (valid until the
+        next call; no host synchronisation)."""
+        if self.graph is None:
+            raise RuntimeError("capture(first_token) first")
+        if self._len + 1 > self.capacity:
+            raise ValueError(f"cache capacity {self.capacity} exhausted")
+        self.graph.replay()
+        self._len += 1
+        self.cache.advance_host_lengths(1)
+        return self.next_tok
+
+    def close(self) -> None:
+        self.cache.use_host_positions()
+        self._E.remove_int8_fused_patch(self.model)

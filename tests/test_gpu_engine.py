@@ -139,3 +139,50 @@ def test_graphed_stack_step_equals_eager_layer_calls(overlap):
             ta, tb = ca.get_decode_tensors(l), cb.get_decode_tensors(l)
             for n in ("k", "v", "ks", "vs"):
                 assert torch.equal(ta[n], tb[n])
+
+
+def test_graphed_model_step_matches_the_eager_patched_loop(tiny_model):
+    """Whole-model greedy decode as one CUDA graph per token (device-side positions, token fed back on
+    the device) against the eager patched forward on a second cache with the same prompt."""
+    import llm_kvcache_quantization_b200 as kvq
+    from llm_kvcache_quantization_b200.runtime import GraphedModelStep
+    g = torch.Generator().manual_seed(11)
+    B, P, N = 2, 48, 6
+    ids = torch.randint(0, 512, (B, P), generator=g).to(DEV)
+    model = tiny_model
+
+    def fresh():
+        c = E.build_cache("int8_baseline", 3, DEV, group_size=32, clip_percentile=100.0, max_seq_len=P + N + 8)
+        with torch.no_grad():
+            first = E._prefill_into_cache(model, c, ids, torch.ones_like(ids))
+        for l in range(3):
+            c.reserve(l, B, 2, 128, P + N + 8)
+        return c, first.argmax(-1, keepdim=True)
+
+    ca, tok0 = fresh()
+    cb, _ = fresh()
+    # eager reference: patched forward, host-side positions
+    E.apply_int8_fused_patch(model)
+    try:
+        ref, tok = [], tok0
+        with torch.no_grad():
+            for i in range(N):
+                pos = torch.full((B, 1), P + i, dtype=torch.long, device=DEV)
+                out = model(input_ids=tok, position_ids=pos, past_key_values=E.INT8CacheWrapperContainer(cb, 3),
+                            use_cache=True)
+                tok = out.logits[:, -1].argmax(-1, keepdim=True)
+                ref.append(tok)
+    finally:
+        E.remove_int8_fused_patch(model)
+    st = GraphedModelStep(model, ca, B)
+    try:
+        st.capture(tok0)
+        got = [st.step().clone() for _ in range(N)]
+    finally:
+        st.close()
+    assert ca.get_seq_len() == cb.get_seq_len() == P + N
+    assert torch.equal(torch.cat(got, 1), torch.cat(ref, 1))
+    for l in range(3):
+        for a, b in zip(ca.get_int8_tensors(l), cb.get_int8_tensors(l)):
+            assert torch.equal(a, b)
+    assert not hasattr(type(model.model.layers[0].self_attn), "_original_forward")
