@@ -37,14 +37,17 @@ WORKLOADS = {
     "c2": dict(layers=28, B=16, Hq=12, Hkv=2, S=8192, kind="int4_asym", n_out=0,
                desc="C2: 28-layer KV stack, Qwen2.5-1.5B geometry (12q/2kv heads, d128), batch 16, ctx 8192, "
                     "INT4 asymmetric group-32 (fp16 scale+zero-point), decode step incl. quantize-on-append"),
-    "c3": dict(layers=4, B=32, Hq=12, Hkv=2, S=16384, kind="int4_outlier", n_out=3,
-               desc="C3: Qwen2.5-1.5B geometry, batch 32, ctx 16384, INT4 group-32 + 3 fp16 outlier channels (4 layers)"),
-    "c4": dict(layers=2, B=64, Hq=28, Hkv=4, S=32768, kind="int8_dyn", n_out=0,
-               desc="C4: Qwen2.5-7B geometry, batch 64, ctx 32768, INT8 group-32 (2 layers)"),
-    "c2_fp16": dict(layers=8, B=16, Hq=12, Hkv=2, S=8192, kind="fp16", n_out=0,
-                    desc="config-2 shape with an UNQUANTISED fp16 cache (comparison point, 8 layers): batch 16, ctx 8192"),
-    "c5": dict(layers=4, B=1, Hq=40, Hkv=8, S=131072, kind="int4_outlier", n_out=1,
-               desc="C5: Qwen2.5-14B geometry, batch 1, ctx 131072, INT4 group-32 + 1 fp16 outlier channel (4 layers)"),
+    "c3": dict(layers=28, B=32, Hq=12, Hkv=2, S=16384, kind="int4_outlier", n_out=3,
+               desc="C3: 28-layer KV stack, Qwen2.5-1.5B geometry, batch 32, ctx 16384, INT4 group-32 + 3 fp16 outlier "
+                    "channels"),
+    "c4": dict(layers=28, B=64, Hq=28, Hkv=4, S=32768, kind="int8_dyn", n_out=0,
+               desc="C4: 28-layer KV stack (64 GB), Qwen2.5-7B geometry, batch 64, ctx 32768, INT8 group-32"),
+    "c2_fp16": dict(layers=28, B=16, Hq=12, Hkv=2, S=8192, kind="fp16", n_out=0,
+                    desc="config-2 shape with an UNQUANTISED fp16 cache (comparison point): 28-layer KV stack, batch 16, "
+                         "ctx 8192"),
+    "c5": dict(layers=48, B=1, Hq=40, Hkv=8, S=131072, kind="int4_outlier", n_out=1,
+               desc="C5: 48-layer KV stack, Qwen2.5-14B geometry, batch 1, ctx 131072, INT4 group-32 + 1 fp16 outlier "
+                    "channel"),
 }
 D = 128
 GS = 32
