@@ -671,6 +671,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # the fused exchange uses plain peer stores; symmetric-memory buffers are not bound to an NVLink multicast object
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch
     import llm_kvcache_quantization_b200 as kvq
     from llm_kvcache_quantization_b200 import ops

@@ -532,9 +532,7 @@ static int launch_mma(MmaTag<FMT, ASYM, OUTL, FAST, GS> tag, const AttnParams& p
     MmaParams mp;
     mp.p = p;
     mp.nstage = cfg.nstage;
-    mp.stage_bytes = cfg.stage_bytes;
     mp.warp_smem_bytes = cfg.nstage * cfg.stage_bytes;
-    mp.row_bytes = RB;
     CUtensorMap kmap, vmap;
     int rc = make_payload_map(&kmap, p.a.k, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;

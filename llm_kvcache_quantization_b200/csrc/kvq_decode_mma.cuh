@@ -53,9 +53,7 @@ __device__ int g_kvq_error_flag = 0;  // 1: an mbarrier wait expired
 struct MmaParams {
     AttnParams p;
     int nstage;
-    int warp_smem_bytes;
-    int stage_bytes;
-    int row_bytes;
+    int warp_smem_bytes;     // nstage * bytes of one stage: the private ring of one warp
 };
 
 // Bytes of one pipeline stage: K tile, V tile (each TS rows), then 2 (4 with zero-points)
@@ -514,7 +512,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int c = 2 * gp + e;                // 32-channel chunk; its group:
-                        constexpr int kDummy = 0; (void)kDummy;
                         const int G = (32 * c) / GS;
                         const uint32_t w0 = r[2 * e], w1 = r[2 * e + 1];
                         mma16816(sg[G], nib_lo_to_h2(w0), nib_lo_to_h2(w1), nib_hi_to_h2(w0), nib_hi_to_h2(w1),
@@ -575,7 +572,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             // 2t, 2t+1 (GS == 16): s2[row][half], half = which 16-channel half of the slice
             uint32_t s2[2][2], z2[2][2] = {{0u, 0u}, {0u, 0u}};
             {
-                constexpr int kFirst = 0; (void)kFirst;
                 const int gidx = (32 * t) / GS;                  // first group of the slice
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
