@@ -252,7 +252,7 @@ __device__ __forceinline__ uint32_t apply_scale(uint32_t c, uint32_t s2, uint32_
 // FAST is opt-in (KvqAttnArgs.fast_dequant).
 // GS = quantisation group size (16 / 32 / 64 / 128 channels), NG = 128 / GS scales per token.
 template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
-__global__ void __launch_bounds__(kMmaWarps * 32, (FMT == KVQ_FMT_INT4 && !OUTL) ? 4 : 1)
+__global__ void __launch_bounds__(kMmaWarps * 32, (FMT == KVQ_FMT_INT4) ? 4 : 1)
 decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
     constexpr bool F16 = FMT == KVQ_FMT_FP16;                 // unquantised cache: no scales, no dequantisation
