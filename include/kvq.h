@@ -59,6 +59,9 @@ extern "C" {
 #define KVQ_F_ADAPTIVE     1  /* s = max(static*margin, absmax/qmax)  (int8_cache.py:392-402, int4_cache.py:451-455) */
 #define KVQ_F_MIXED_RESCUE 2  /* s = max(s, absmax/7)                 (int4_cache.py:456-459)                        */
 #define KVQ_F_RESCUE_THR   4  /* s = dyn >= *thr ? max(s,dyn) : s     (int4_cache.py:360-390)                        */
+#define KVQ_F_UNPACKED     8  /* KVQ_FMT_INT4 only: store one code per byte ([.., D] int8 in [-8, 7]) instead of
+                                 two nibbles per byte: INT4KVCache(bit_packed=False), int4_cache.py:520-560; the
+                                 attention kernels read such a payload as KVQ_FMT_INT8                          */
 
 typedef void* kvq_stream_t;
 

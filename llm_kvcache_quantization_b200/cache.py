@@ -32,7 +32,7 @@ import torch
 from torch import Tensor
 
 from . import ops, quant
-from ._lib import (FMT_FP16, FMT_INT4, FMT_INT8, F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR,
+from ._lib import (FMT_FP16, FMT_INT4, FMT_INT8, F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR, F_UNPACKED,
                    SCALE_ASYM_MINMAX, SCALE_DYNAMIC_PCT, SCALE_STATIC)
 
 logger = logging.getLogger(__name__)
@@ -449,7 +449,7 @@ class _QuantCache(_CacheBase):
         if self.outlier_idx is not None:
             oidx = self.outlier_idx[layer_id].to(device=k.device, dtype=torch.int16).contiguous()
             kw.update(outlier_idx=oidx, k_side=bufs["kside"], v_side=bufs["vside"])
-        flags = 0
+        flags = extra_flags & F_UNPACKED
         if self.asymmetric:
             policy = SCALE_ASYM_MINMAX
             kw.update(k_zp=bufs["kz"], v_zp=bufs["vz"])
@@ -524,7 +524,7 @@ class _QuantCache(_CacheBase):
         if inv_tau is not None and inv_tau.dtype != torch.float32:
             inv_tau = inv_tau.float()
         ctx = None if self._dev_positions is None else self._dev_positions[1]
-        res = ops.decode_attn(self._fmt, q, t["k"], t["v"], t["ks"], t["vs"], ctx, float(sm_scale),
+        res = ops.decode_attn(getattr(self, "_decode_fmt", self._fmt), q, t["k"], t["v"], t["ks"], t["vs"], ctx, float(sm_scale),
                               head_dim=q.shape[-1], inv_tau=inv_tau, out=out, **extra)
         return res if original == torch.float16 else res.to(original)
 
@@ -609,10 +609,9 @@ class INT4KVCache(_QuantCache):
                          validate_inputs)
         if outlier_rescue_ratio < 0:
             raise ValueError(f"outlier_rescue_ratio must be >= 0, got {outlier_rescue_ratio}")
-        if not bit_packed:
-            raise ValueError("this cache stores INT4 nibble-packed only (bit_packed=True); "
-                             "decode_attn_int4(bit_packed=False) still accepts unpacked tensors")
-        self.bit_packed = True
+        # bit_packed=False keeps one INT4 code per byte (src/cache/int4_cache.py:520-560): same quantizer,
+        # payload [B,H,S,D]; the attention kernels read it as INT8 codes with the same scales
+        self.bit_packed = bool(bit_packed)
         self.outlier_rescue_ratio = float(outlier_rescue_ratio)
         self.mixed_rescue = bool(mixed_rescue)
         self.asymmetric = bool(asymmetric)
@@ -626,9 +625,15 @@ class INT4KVCache(_QuantCache):
         self.outlier_idx = outlier_idx
 
     def _payload_dim(self, head_dim: int) -> int:
+        if not self.bit_packed:
+            return head_dim
         if head_dim % 2 != 0:
             raise ValueError(f"INT4 bit packing requires even head_dim, got {head_dim}")
         return head_dim // 2
+
+    @property
+    def _decode_fmt(self) -> int:
+        return FMT_INT4 if self.bit_packed else FMT_INT8
 
     def _rescue_threshold(self, x: Tensor, G: int) -> Tensor:
         """Global quantile of the per-group absmax/7 over the whole appended tensor
@@ -653,7 +658,7 @@ class INT4KVCache(_QuantCache):
         self._append_impl(layer_id, k, v, extra_flags=self._rescue_flags())
 
     def _rescue_flags(self) -> int:
-        flags = 0
+        flags = 0 if self.bit_packed else F_UNPACKED
         if self.mixed_rescue:
             flags |= F_MIXED_RESCUE
         if self.outlier_rescue_ratio >= 1.0:
@@ -679,7 +684,7 @@ class INT4KVCache(_QuantCache):
         oidx = t.get("outlier_idx")
         if oidx is not None:
             oidx = oidx.to(device=t["k"].device, dtype=torch.int16).contiguous()
-        kd, vd = ops.dequantize(FMT_INT4, t["k"], t["v"], t["ks"], t["vs"], k_zp=t.get("kz"), v_zp=t.get("vz"),
+        kd, vd = ops.dequantize(self._decode_fmt, t["k"], t["v"], t["ks"], t["vs"], k_zp=t.get("kz"), v_zp=t.get("vz"),
                                 outlier_idx=oidx, k_side=t.get("kside"), v_side=t.get("vside"))
         return kd.to(self.dtype), vd.to(self.dtype)
 

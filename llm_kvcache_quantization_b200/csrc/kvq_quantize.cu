@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
         return (int)fminf(fmaxf(qv, -7.f), 7.f);
     };
 
-    if (FMT == KVQ_FMT_INT8) {
+    if (FMT == KVQ_FMT_INT8 || (a.flags & KVQ_F_UNPACKED)) {
         int8_t* dst = (int8_t*)pay + cb;
 #pragma unroll
         for (int i = 0; i < cw; i += 4) {

@@ -35,7 +35,8 @@ class GraphedKVStackStep:
         if b0 is None:
             raise ValueError("preallocate the cache (append a prompt or call reserve) before building the step")
         B, Hkv, cap_phys = b0["k"].shape[0], b0["k"].shape[1], b0["k"].shape[2]
-        D = b0["k"].shape[3] * (2 if cache._fmt == _lib.FMT_INT4 else 1)
+        packed = cache._fmt == _lib.FMT_INT4 and getattr(cache, "bit_packed", True)
+        D = b0["k"].shape[3] * (2 if packed else 1)
         self.L, self.B, self.Hq, self.Hkv, self.D = L, B, num_q_heads, Hkv, D
         self.capacity = min(cap_phys, capacity or cache._layer_capacity[0])
         dev = b0["k"].device
@@ -97,6 +98,10 @@ class GraphedKVStackStep:
         gs = self.D // G
         app, att = {}, {}
         flags = 0
+        dfmt = fmt                                     # unpacked INT4 codes are read by the kernels as INT8
+        if fmt == _lib.FMT_INT4 and not getattr(c, "bit_packed", True):
+            flags |= _lib.F_UNPACKED
+            dfmt = _lib.FMT_INT8
         if getattr(c, "asymmetric", False):
             policy = _lib.SCALE_ASYM_MINMAX
             app.update(k_zp=b["kz"], v_zp=b["vz"])
@@ -123,7 +128,7 @@ class GraphedKVStackStep:
             lambda: ops.quantize_append(fmt, policy, self.k_new[l], self.v_new[l], b["k"], b["v"], b["ks"], b["vs"],
                                         self.pos, gs, flags=flags, adaptive_margin=float(c.adaptive_static_margin),
                                         k_scale_f32=b.get("ks32"), v_scale_f32=b.get("vs32"), **app),
-            lambda **kw: ops.decode_attn(fmt, self.q[l], view["k"], view["v"], view["ks"], view["vs"], self.ctx,
+            lambda **kw: ops.decode_attn(dfmt, self.q[l], view["k"], view["v"], view["ks"], view["vs"], self.ctx,
                                          self.sm_scale, head_dim=self.D,
                                          inv_tau=None if self.inv_tau is None else self.inv_tau[l], out=self.out[l],
                                          max_ctx=cap, **att, **kw))
