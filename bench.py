@@ -773,9 +773,10 @@ def main():
         e2e = {"value": world * B / (ems / args.steps * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": stepper.h2d_bytes_per_step, "d2h_bytes_per_step": stepper.d2h_bytes_per_step,
                "ms_per_step": ems / args.steps,
-               "api": "GraphedKVStackStep.step(host_q, host_k, host_v) -> host_out: one CUDA graph launch holding "
-                      "the pinned H2D copies of q/k/v, append + attention for every layer and the pinned D2H of "
-                      "the outputs; stream sync"}
+               "api": "GraphedKVStackStep.step(host_q, host_k, host_v) -> host_out: one CUDA graph launch holding the "
+                      "pinned H2D copies of q/k/v (first layers, then the rest beside their kernels), append + attention "
+                      "for every layer, and the pinned D2H of the outputs (all but the last layers beside the last "
+                      "layers' kernels, then the tail); stream sync"}
 
     aux = None
     if args.aux and wl["kind"] != "fp16":

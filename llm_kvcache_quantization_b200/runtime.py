@@ -50,14 +50,18 @@ class GraphedKVStackStep:
         # device state advanced inside the graph
         self.pos = torch.full((1,), self._len, dtype=torch.int32, device=dev)
         self.ctx = torch.full((B,), self._len + 1, dtype=torch.int32, device=dev)
-        # device staging + pinned host mirrors
-        self.q = torch.empty(L, B, num_q_heads, D, dtype=torch.float16, device=dev)
-        self.k_new = torch.empty(L, B, Hkv, 1, D, dtype=torch.float16, device=dev)
-        self.v_new = torch.empty_like(self.k_new)
+        # device staging + pinned host mirrors.  q | k | v of one layer are contiguous (one upload per layer);
+        # the public tensors are views into the staging rows
+        nq, nk = B * num_q_heads * D, B * Hkv * D
+        self._stage = torch.empty(L, nq + 2 * nk, dtype=torch.float16, device=dev)
+        self._host_stage = torch.empty(L, nq + 2 * nk, dtype=torch.float16).pin_memory()
+
+        def views(t):
+            return (t[:, :nq].view(L, B, num_q_heads, D), t[:, nq:nq + nk].view(L, B, Hkv, 1, D),
+                    t[:, nq + nk:].view(L, B, Hkv, 1, D))
+        self.q, self.k_new, self.v_new = views(self._stage)
+        self.host_q, self.host_k, self.host_v = views(self._host_stage)
         self.out = torch.empty(L, B, num_q_heads, D, dtype=torch.float16, device=dev)
-        self.host_q = torch.empty(self.q.shape, dtype=torch.float16).pin_memory()
-        self.host_k = torch.empty(self.k_new.shape, dtype=torch.float16).pin_memory()
-        self.host_v = torch.empty(self.v_new.shape, dtype=torch.float16).pin_memory()
         self.host_out = torch.empty(self.out.shape, dtype=torch.float16).pin_memory()
         self.graph = None
         self.graph_host = None
@@ -157,14 +161,41 @@ class GraphedKVStackStep:
         self.ctx.fill_(self._len + 1)
         self.graph = g
         self.launches_per_step = self.L * 3
-        # the host-buffer form: uploads, the step and the download as ONE graph launch
+        # The host-buffer form: uploads, the step and the downloads as ONE graph launch.  The copies run on
+        # their own streams in two pieces each: the first layers' inputs (small, exposed), then the rest while
+        # those layers compute; all outputs but the last layers' while the last layers compute, then the tail
+        # (small, exposed).  Two extra cross-stream edges in all, so the kernels of the other layers keep their
+        # programmatic launch overlap.
+        L = self.L
+        head = min(2, L)
+        tail = min(2, L - head) if L > head else 0
+        up, down = torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device)
         gh = torch.cuda.CUDAGraph()
         with torch.cuda.graph(gh):
-            self.q.copy_(self.host_q, non_blocking=True)
-            self.k_new.copy_(self.host_k, non_blocking=True)
-            self.v_new.copy_(self.host_v, non_blocking=True)
-            self._body()
-            self.host_out.copy_(self.out, non_blocking=True)
+            main = torch.cuda.current_stream(self.device)
+            up.wait_stream(main)
+            down.wait_stream(main)
+            with torch.cuda.stream(up):
+                self._stage[:head].copy_(self._host_stage[:head], non_blocking=True)
+                first = torch.cuda.Event()
+                first.record(up)
+                if L > head:
+                    self._stage[head:].copy_(self._host_stage[head:], non_blocking=True)
+            main.wait_event(first)
+            for l in range(L):
+                if l == head:
+                    main.wait_stream(up)
+                self._layer(l)
+                if tail and l == L - tail - 1:
+                    down.wait_stream(main)
+                    with torch.cuda.stream(down):
+                        self.host_out[:L - tail].copy_(self.out[:L - tail], non_blocking=True)
+            self.pos.add_(1)
+            self.ctx.add_(1)
+            main.wait_stream(up)
+            main.wait_stream(down)
+            done = L - tail if tail else 0             # layers whose output went out with the early download
+            self.host_out[done:].copy_(self.out[done:], non_blocking=True)
         self.pos.fill_(self._len)
         self.ctx.fill_(self._len + 1)
         self.graph_host = gh
@@ -194,7 +225,7 @@ class GraphedKVStackStep:
             self.host_q.copy_(host_q)
             self.host_k.copy_(host_k)
             self.host_v.copy_(host_v)
-        self.graph_host.replay()                       # pinned H2D x3, every layer, pinned D2H
+        self.graph_host.replay()                       # pinned uploads, every layer, pinned downloads
         self._len += 1
         for i in range(self.L):
             self.cache._layer_seq_lens[i] = self._len

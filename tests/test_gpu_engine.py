@@ -95,8 +95,8 @@ def test_torch_ref_impl_agrees_with_fused(tiny_model):
     assert torch.allclose(outs["triton_fused"], outs["torch_ref"], atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("overlap", (False, True))
-def test_graphed_stack_step_equals_eager_layer_calls(overlap):
+@pytest.mark.parametrize("overlap,L", ((False, 3), (True, 3), (True, 1), (True, 7)))
+def test_graphed_stack_step_equals_eager_layer_calls(overlap, L):
     """The captured whole-stack step (device-side position, cache growing inside the graph) against eager
     per-layer append + fused decode, over several steps: bit-identical caches always; outputs bit-identical
     in the serial form, and within the attention tolerance when the append runs beside the scan and the new
@@ -104,7 +104,7 @@ def test_graphed_stack_step_equals_eager_layer_calls(overlap):
     import llm_kvcache_quantization_b200 as kvq
     from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
     g = torch.Generator().manual_seed(5)
-    L, B, Hq, Hkv, S, D, steps = 3, 2, 12, 2, 200, 128, 4
+    B, Hq, Hkv, S, D, steps = 2, 12, 2, 200, 128, 4         # L = 1 / 3 / 7: every shape of the two-piece copy pipeline
     for make in (lambda: kvq.INT4KVCache(L, device=DEV, group_size=32, asymmetric=True, max_seq_len=S + 8),
                  lambda: kvq.INT8KVCache(L, device=DEV, group_size=32, clip_percentile=100.0, max_seq_len=S + 8),
                  lambda: kvq.FP16KVCache(L, device=DEV, max_seq_len=S + 8)):
