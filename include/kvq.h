@@ -245,6 +245,22 @@ typedef struct KvqCombineArgs {
 KVQ_API int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream);
 
 /*
+ * Calibration statistic: out[h, g] = max(out[h, g], max over batch rows, tokens and the channels of group g
+ * of |x[b, h, s, d]|).  Stands in for compute_absmax_per_group (scripts/calibrate_behavior.py:228-260), the
+ * collection half of static-scale calibration; `out` (fp32 [H, G]) is zero-filled by the caller once and
+ * accumulates over calls.  Bit-identical to the reference's abs().amax() (a maximum has no rounding).
+ */
+typedef struct KvqAbsmaxArgs {
+    int32_t B, H, S, D;
+    int32_t group_size;          /* channels per group; -1 = D                               */
+    const void* x;               /* fp16 [B, H, S, D], D contiguous, 16-byte aligned rows    */
+    int64_t stride_b, stride_h, stride_s;               /* elements, multiples of 8      */
+    float*  out;                 /* fp32 [H, D / group_size]                                 */
+} KvqAbsmaxArgs;
+
+KVQ_API int kvq_group_absmax(const KvqAbsmaxArgs* args, kvq_stream_t stream);
+
+/*
  * Sequence-sharded decode, fused exchange: merge this rank's KV splits (the partials that
  * kvq_decode_attn with stages = 1 left in `workspace`), store the normalised partial of every
  * (batch, head) row into every rank's receive buffer with plain 8-byte peer stores over NVLink

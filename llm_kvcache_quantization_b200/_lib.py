@@ -95,6 +95,14 @@ class KvqDequantArgs(C.Structure):
     ]
 
 
+class KvqAbsmaxArgs(C.Structure):
+    _fields_ = [
+        ("B", _i32), ("H", _i32), ("S", _i32), ("D", _i32), ("group_size", _i32),
+        ("x", _vp), ("stride_b", _i64), ("stride_h", _i64), ("stride_s", _i64),
+        ("out", _vp),
+    ]
+
+
 MAX_PEERS = 16
 
 
@@ -121,6 +129,7 @@ EXPORTS = (
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
     ("kvq_exchange_bytes", C.c_size_t, (_i32, _i32, _i32, _i32, _i32)),
     ("kvq_combine_exchange", C.c_int, (C.POINTER(KvqExchangeArgs), _vp)),
+    ("kvq_group_absmax", C.c_int, (C.POINTER(KvqAbsmaxArgs), _vp)),
     ("kvq_dequantize", C.c_int, (C.POINTER(KvqDequantArgs), _vp)),
     ("kvq_debug_error_flag", C.c_int, (C.c_int,)),
     ("kvq_decode_kernel_kind", C.c_int, (C.POINTER(KvqAttnArgs),)),

@@ -315,6 +315,35 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     return out
 
 
+def group_absmax(x: torch.Tensor, group_size: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 [H, G] table of max |x| per (head, channel group) over batch rows and tokens of `x`
+    ([B,H,S,D] or [H,S,D] fp16); max-accumulates into `out` when given (zero-filled by the caller)."""
+    dev = _require_cuda(x)
+    if x.dtype != torch.float16:
+        raise ValueError("group_absmax expects an fp16 tensor")
+    if x.ndim == 3:
+        x = x[None]
+    if x.ndim != 4 or x.stride(-1) != 1:
+        raise ValueError("expected [B,H,S,D] (or [H,S,D]) with a contiguous last dimension")
+    B, H, S, D = x.shape
+    gs = D if group_size == -1 else int(group_size)
+    if gs <= 0 or D % gs != 0:
+        raise ValueError(f"head_dim ({D}) must be divisible by group_size ({group_size})")
+    if out is None:
+        out = torch.zeros((H, D // gs), dtype=torch.float32, device=dev)
+    elif out.dtype != torch.float32 or tuple(out.shape) != (H, D // gs) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous fp32 [H, G] tensor")
+    a = _lib.KvqAbsmaxArgs()
+    a.B, a.H, a.S, a.D, a.group_size = B, H, S, D, gs
+    a.x = x.data_ptr()
+    a.stride_b, a.stride_h, a.stride_s = x.stride(0), x.stride(1), x.stride(2)
+    a.out = out.data_ptr()
+    with torch.cuda.device(dev):
+        rc = _lib.load().kvq_group_absmax(C.byref(a), _stream_ptr(dev))
+    _lib.check("kvq_group_absmax", rc)
+    return out
+
+
 def neutral_partial(B: int, Hq: int, D: int, dev) -> None:
     """Fill the split-K workspace with ONE empty split per (batch, head) row (o = 0, m = -inf, l = 0):
     what a rank without cached tokens hands to `combine_exchange`."""

@@ -153,3 +153,21 @@ def test_build_cache_modes(tmp_path):
     assert c.mixed_rescue and c.group_size == 32 and abs(c.outlier_rescue_ratio - 0.01) < 1e-9 and c.inv_tau is not None
     cal8 = E.load_calibration(str(f), "int8_ours", "cpu")
     assert cal8["static_k_scale"].dtype == torch.float16
+
+
+def test_save_calibration_writes_the_schema_load_calibration_reads(tmp_path):
+    """calibration.save_calibration -> engine.load_calibration on CPU tensors (no kernel involved)."""
+    import json
+    import torch
+    from llm_kvcache_quantization_b200 import calibration as C, engine as E
+    ks = [torch.full((2, 4), 0.01 * (l + 1)) for l in range(3)]
+    path = str(tmp_path / "c.json")
+    doc = C.save_calibration(path, ks, ks, group_size=32, clip_percentile=99.5, inv_tau=torch.ones(3, 12),
+                             int4_outlier_ratio=0.02, int4_mixed_rescue=True)
+    assert json.load(open(path)) == doc and doc["version"] == 2
+    out = E.load_calibration(path, "int4_ours", "cpu")
+    assert out["group_size"] == 32 and out["clip_percentile"] == 99.5 and out["mixed_rescue"] is True
+    assert out["outlier_rescue_ratio"] == 0.02 and out["static_k_scale"].dtype == torch.float32
+    assert tuple(out["static_k_scale"].shape) == (3, 2, 4) and tuple(out["inv_tau"].shape) == (3, 12)
+    with __import__("pytest").raises(ValueError):
+        C.compute_absmax_per_group(torch.zeros(2, 5, 128), 48)
