@@ -245,6 +245,39 @@ typedef struct KvqCombineArgs {
 KVQ_API int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream);
 
 /*
+ * KIVI-format cache (src/cache/kivi_style_cache.py): K asymmetric per channel with parameters fixed by the
+ * first append of a layer, V asymmetric per token; fp32 scale and float zero-point; INT8 codes or
+ * nibble-packed INT4.  kvq_kivi_append stands in for KIVIStyleKVCache.append (:296-600) with
+ * quantize_asymmetric_per_channel / _per_token (src/quant/asymmetric_quant.py:199-289) at percentile 100;
+ * kvq_kivi_dequantize for get_kv (:602-650) with dequantize_asymmetric (:144-196).  Bit-exact codes,
+ * parameters and dequantised values.  In kvq_kivi_dequantize, T is the number of cached tokens to convert.
+ */
+typedef struct KvqKiviArgs {
+    int32_t bits;                /* 4 (packed, payload [.., D/2]) or 8 (payload [.., D])      */
+    int32_t B, H, T, D;          /* D in {64, 128, 256}                                       */
+    int32_t init_k_params;       /* append: 1 = compute k_scale / k_zp from these T tokens    */
+    const void* k_src;           /* fp16 [B, H, T, D] new tokens (append)                     */
+    const void* v_src;
+    int64_t src_stride_b, src_stride_h, src_stride_t;   /* elements, multiples of 8      */
+    void* k_payload;             /* int8 cache [B, H, cap, D or D/2]                          */
+    void* v_payload;
+    int64_t pay_stride_b, pay_stride_h, pay_stride_s;   /* BYTES                         */
+    float* k_scale;              /* fp32 [B, H, D] contiguous, 16-byte aligned                */
+    float* k_zp;
+    float* v_scale;              /* fp32 [B, H, cap], token-contiguous                        */
+    float* v_zp;
+    int64_t vs_stride_b, vs_stride_h;                   /* elements                      */
+    int64_t write_pos;           /* append: first slot written                                */
+    const int32_t* write_pos_dev;/* if not NULL the slot is read on the device                */
+    void* k_out;                 /* dequantize: fp16 [B, H, T, D]                             */
+    void* v_out;                 /* or NULL                                                   */
+    int64_t out_stride_b, out_stride_h, out_stride_s;   /* elements, multiples of 8      */
+} KvqKiviArgs;
+
+KVQ_API int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream);
+KVQ_API int kvq_kivi_dequantize(const KvqKiviArgs* args, kvq_stream_t stream);
+
+/*
  * Calibration statistic: out[h, g] = max(out[h, g], max over batch rows, tokens and the channels of group g
  * of |x[b, h, s, d]|).  Stands in for compute_absmax_per_group (scripts/calibrate_behavior.py:228-260), the
  * collection half of static-scale calibration; `out` (fp32 [H, G]) is zero-filled by the caller once and

@@ -11,6 +11,7 @@ All compute runs in libkvq.so (CUDA, sm_100a).  There is no CPU fallback: the
 entry points raise if the library is missing or a tensor is not on a CUDA device.
 """
 from .cache import FP16KVCache, INT4KVCache, INT8KVCache
+from .kivi import KIVIStyleKVCache
 from .kernels import (decode_attn_fp16, decode_attn_int4, decode_attn_int4_asym,
                       decode_attn_int4_outlier, decode_attn_int8)
 from .quant import (dequantize_asymmetric_groupwise, dequantize_symmetric_int4,
@@ -19,7 +20,7 @@ from .quant import (dequantize_asymmetric_groupwise, dequantize_symmetric_int4,
                     quantize_symmetric_int8, quantize_symmetric_int8_with_scale, unpack_int4)
 
 __all__ = [
-    "FP16KVCache", "INT4KVCache", "INT8KVCache",
+    "FP16KVCache", "INT4KVCache", "INT8KVCache", "KIVIStyleKVCache",
     "decode_attn_fp16", "decode_attn_int4", "decode_attn_int4_asym", "decode_attn_int4_outlier",
     "decode_attn_int8",
     "dequantize_asymmetric_groupwise", "dequantize_symmetric_int4", "dequantize_symmetric_int8",

@@ -103,6 +103,17 @@ class KvqAbsmaxArgs(C.Structure):
     ]
 
 
+class KvqKiviArgs(C.Structure):
+    _fields_ = [
+        ("bits", _i32), ("B", _i32), ("H", _i32), ("T", _i32), ("D", _i32), ("init_k_params", _i32),
+        ("k_src", _vp), ("v_src", _vp), ("src_stride_b", _i64), ("src_stride_h", _i64), ("src_stride_t", _i64),
+        ("k_payload", _vp), ("v_payload", _vp), ("pay_stride_b", _i64), ("pay_stride_h", _i64), ("pay_stride_s", _i64),
+        ("k_scale", _vp), ("k_zp", _vp), ("v_scale", _vp), ("v_zp", _vp), ("vs_stride_b", _i64), ("vs_stride_h", _i64),
+        ("write_pos", _i64), ("write_pos_dev", _vp),
+        ("k_out", _vp), ("v_out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64), ("out_stride_s", _i64),
+    ]
+
+
 MAX_PEERS = 16
 
 
@@ -129,6 +140,8 @@ EXPORTS = (
     ("kvq_lse_combine", C.c_int, (C.POINTER(KvqCombineArgs), _vp)),
     ("kvq_exchange_bytes", C.c_size_t, (_i32, _i32, _i32, _i32, _i32)),
     ("kvq_combine_exchange", C.c_int, (C.POINTER(KvqExchangeArgs), _vp)),
+    ("kvq_kivi_append", C.c_int, (C.POINTER(KvqKiviArgs), _vp)),
+    ("kvq_kivi_dequantize", C.c_int, (C.POINTER(KvqKiviArgs), _vp)),
     ("kvq_group_absmax", C.c_int, (C.POINTER(KvqAbsmaxArgs), _vp)),
     ("kvq_dequantize", C.c_int, (C.POINTER(KvqDequantArgs), _vp)),
     ("kvq_debug_error_flag", C.c_int, (C.c_int,)),

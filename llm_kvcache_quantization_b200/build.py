@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libkvq.so")
 
-SOURCES = ("kvq_api.cu", "kvq_quantize.cu", "kvq_decode.cu", "kvq_dequantize.cu", "kvq_calibrate.cu")
+SOURCES = ("kvq_api.cu", "kvq_quantize.cu", "kvq_decode.cu", "kvq_dequantize.cu", "kvq_calibrate.cu", "kvq_kivi.cu")
 
 # No --use_fast_math / -ftz / -prec-div=false: the quantizer needs IEEE fp32
 # division, RN fp16 conversions and fp16 subnormals to stay bit-exact.

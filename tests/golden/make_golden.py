@@ -7,7 +7,7 @@ Usage (only where the reference checkout is available):
 
 The reference's own classes and functions are imported unmodified
 (`INT8KVCache`, `INT4KVCache`, `quantize_asymmetric`, `pack_int4`,
-`_decode_attn_int8_torch_ref`, `_apply_rope`) and driven on seeded inputs on CPU; inputs and
+`_decode_attn_int8_torch_ref`, `_apply_rope`, `KIVIStyleKVCache`) and driven on seeded inputs on CPU; inputs and
 outputs are stored as small `.npz` files.  The fixtures travel with the
 repository, the reference does not.
 """
@@ -69,15 +69,45 @@ def make_rope():
     print("rope.npz", os.path.getsize(os.path.join(HERE, "rope.npz")) // 1024, "KiB")
 
 
+def make_kivi():
+    """KIVIStyleKVCache (src/cache/kivi_style_cache.py) on CPU: a prompt, then single-token appends; INT4 and
+    INT8; payloads, per-channel K and per-token V parameters, and get_kv."""
+    from src.cache.kivi_style_cache import KIVIStyleKVCache
+    gen = torch.Generator().manual_seed(20261127)
+    out = {}
+    B, H, P, N, D = 2, 2, 37, 3, 128
+    k = gen_kv(gen, B, H, P + N, D, outlier_ch=2)
+    v = gen_kv(gen, B, H, P + N, D, chan_std=True)
+    k[:, :, P + 1] *= 3.0                        # a decode token outside the prompt's range: clipped codes
+    out["k"], out["v"], out["prompt"] = _np(k), _np(v), np.array(P)
+    for bits in (4, 8):
+        c = KIVIStyleKVCache(num_layers=1, device="cpu", quant_bits=bits)
+        c.append(0, k[:, :, :P], v[:, :, :P])
+        for t in range(P, P + N):
+            c.append(0, k[:, :, t:t + 1], v[:, :, t:t + 1])
+        S = P + N
+        out[f"b{bits}_k_payload"] = _np(c._k_cache[0][:, :, :S])
+        out[f"b{bits}_v_payload"] = _np(c._v_cache[0][:, :, :S])
+        out[f"b{bits}_k_scale"], out[f"b{bits}_k_zp"] = _np(c._k_scale[0]), _np(c._k_zp[0])
+        out[f"b{bits}_v_scale"], out[f"b{bits}_v_zp"] = _np(c._v_scale[0][:, :, :S]), _np(c._v_zp[0][:, :, :S])
+        kd, vd = c.get_kv(0)
+        out[f"b{bits}_k_deq"], out[f"b{bits}_v_deq"] = _np(kd), _np(vd)
+    np.savez_compressed(os.path.join(HERE, "kivi.npz"), **out)
+    print("kivi.npz", os.path.getsize(os.path.join(HERE, "kivi.npz")) // 1024, "KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
-    ap.add_argument("--only", default="", help="'rope' regenerates rope.npz alone")
+    ap.add_argument("--only", default="", help="'rope' / 'kivi' regenerate rope.npz / kivi.npz alone")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     warnings.simplefilter("ignore")
     if args.only == "rope":
         make_rope()
+        return
+    if args.only == "kivi":
+        make_kivi()
         return
 
     from src.cache.int8_cache import INT8KVCache
@@ -214,6 +244,7 @@ def main():
     for f in ("quantizers.npz", "pack_int4.npz", "attention.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
     make_rope()
+    make_kivi()
 
 
 if __name__ == "__main__":

@@ -152,3 +152,21 @@ def test_rope_matches_reference(golden_dir, name):
         ref = z[f"{name}_{which}_out"]
         assert got.dtype == np.float16 and got.shape == ref.shape
         assert np.array_equal(got.view(np.uint16), ref.view(np.uint16)), f"{name} {which}"
+
+
+@pytest.mark.parametrize("bits", (4, 8))
+def test_kivi_format_matches_reference(golden_dir, bits):
+    """Per-channel K (parameters from the prompt, later tokens clipped) and per-token V asymmetric
+    quantization restated in numpy == the reference's KIVIStyleKVCache on CPU: payloads, fp32
+    parameters and dequantised values, bit for bit."""
+    z = np.load(os.path.join(golden_dir, "kivi.npz"))
+    k, v, P = z["k"], z["v"], int(z["prompt"])
+    ck, sk, zk = O.quantize_asym_axis(k[:, :, :P], 2, bits)
+    codes_k = np.concatenate([ck, O.quantize_asym_with_params(k[:, :, P:], sk, zk, 2, bits)], axis=2)
+    cv, sv, zv = O.quantize_asym_axis(v, 3, bits)
+    pk, pv = (O.pack_int4(codes_k), O.pack_int4(cv)) if bits == 4 else (codes_k, cv)
+    assert np.array_equal(pk, z[f"b{bits}_k_payload"]) and np.array_equal(pv, z[f"b{bits}_v_payload"])
+    for got, name in ((sk, "k_scale"), (zk, "k_zp"), (sv, "v_scale"), (zv, "v_zp")):
+        assert got.dtype == np.float32 and np.array_equal(got, z[f"b{bits}_{name}"]), name
+    assert np.array_equal(O.dequant_asym_f32(codes_k, sk, zk, 2).view(np.uint16), z[f"b{bits}_k_deq"].view(np.uint16))
+    assert np.array_equal(O.dequant_asym_f32(cv, sv, zv, 3).view(np.uint16), z[f"b{bits}_v_deq"].view(np.uint16))
