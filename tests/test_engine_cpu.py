@@ -141,8 +141,10 @@ def test_build_cache_modes(tmp_path):
     import json
     assert type(E.build_cache("fp16", 2, "cpu")).__name__ == "FP16KVCache"
     assert type(E.build_cache("int8_baseline", 2, "cpu", group_size=32)).__name__ == "INT8KVCache"
+    kivi = E.build_cache("kivi_style", 2, "cpu", quant_bits=4)
+    assert type(kivi).__name__ == "KIVIStyleKVCache" and kivi.bit_packed and kivi.decode_attn_impl == "torch_ref"
     with pytest.raises(ValueError, match="not supported"):
-        E.build_cache("kivi_style", 2, "cpu")
+        E.build_cache("int4_mixed_kv", 2, "cpu")
     f = tmp_path / "calib.json"
     f.write_text(json.dumps({"version": 2, "group_size_k": 32, "group_size_v": 32, "clip_percentile_k": 99.5,
                              "k_scale": [[[0.1] * 4]], "v_scale": [[[0.2] * 4]], "inv_tau": [[1.0, 1.1]],

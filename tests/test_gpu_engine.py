@@ -186,3 +186,18 @@ def test_graphed_model_step_matches_the_eager_patched_loop(tiny_model):
         for a, b in zip(ca.get_int8_tensors(l), cb.get_int8_tensors(l)):
             assert torch.equal(a, b)
     assert not hasattr(type(model.model.layers[0].self_attn), "_original_forward")
+
+
+@pytest.mark.parametrize("bits", (8, 4))
+def test_kivi_style_mode_generates(tiny_model, bits):
+    """kv_mode="kivi_style": prompt K/V quantized per channel / per token, decode through the patched forward
+    (dequantise + tensor-core fp16 attention); INT8 tracks plain HF greedy decoding on the first tokens."""
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 512, (2, 40), generator=g).to(DEV)
+    ref, _ = _hf_greedy(tiny_model, ids, 6)
+    out = E.generate_from_ids(tiny_model, _Tok(), ids, max_new_tokens=6, kv_mode="kivi_style", quant_bits=bits,
+                              stop_on_eos=False)
+    assert out.generated_ids.shape == (2, 6) and out.kv_cache_seq_len == 45
+    assert torch.equal(out.generated_ids[:, 0], ref[:, 0])          # the first token comes from the fp16 prefill
+    if bits == 8:
+        assert (out.generated_ids == ref).float().mean() >= 0.6
