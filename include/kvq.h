@@ -272,6 +272,8 @@ typedef struct KvqKiviArgs {
     void* k_out;                 /* dequantize: fp16 [B, H, T, D]                             */
     void* v_out;                 /* or NULL                                                   */
     int64_t out_stride_b, out_stride_h, out_stride_s;   /* elements, multiples of 8      */
+    void* v_scale_h;             /* append, optional: fp16 copies RN16(v_scale), RN16(v_zp), laid out like the fp32  */
+    void* v_zp_h;                /* buffers - the per-token tiles the fused decode kernel reads                      */
 } KvqKiviArgs;
 
 KVQ_API int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream);

@@ -111,6 +111,7 @@ class KvqKiviArgs(C.Structure):
         ("k_scale", _vp), ("k_zp", _vp), ("v_scale", _vp), ("v_zp", _vp), ("vs_stride_b", _i64), ("vs_stride_h", _i64),
         ("write_pos", _i64), ("write_pos_dev", _vp),
         ("k_out", _vp), ("v_out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64), ("out_stride_s", _i64),
+        ("v_scale_h", _vp), ("v_zp_h", _vp),
     ]
 
 

@@ -143,6 +143,10 @@ __global__ void __launch_bounds__(256) kivi_quantize_kernel(const KiviParams p) 
             const long long o = (long long)b * a.vs_stride_b + (long long)h * a.vs_stride_h + pos;
             a.v_scale[o] = s;
             a.v_zp[o] = zp;
+            if (a.v_scale_h) {
+                ((__half*)a.v_scale_h)[o] = __float2half_rn(s);
+                ((__half*)a.v_zp_h)[o] = __float2half_rn(zp);
+            }
         }
     }
     if (!live) return;
@@ -242,6 +246,7 @@ extern "C" int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream) {
     const KvqKiviArgs& a = *args;
     if (a.B == 0 || a.T == 0) return KVQ_OK;
     if (!a.k_src || !a.v_src || a.write_pos < 0) return KVQ_EINVAL;
+    if ((a.v_scale_h != nullptr) != (a.v_zp_h != nullptr)) return KVQ_EINVAL;
     if (((uintptr_t)a.k_src & 15) || ((uintptr_t)a.v_src & 15) || (a.src_stride_b & 7) || (a.src_stride_h & 7) ||
         (a.src_stride_t & 7))
         return KVQ_EINVAL;

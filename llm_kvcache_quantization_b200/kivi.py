@@ -51,6 +51,12 @@ class KIVIStyleKVCache:
         self._k_zp: List[Optional[Tensor]] = [None] * num_layers
         self._v_scale: List[Optional[Tensor]] = [None] * num_layers     # fp32 [B, H, capacity]
         self._v_zp: List[Optional[Tensor]] = [None] * num_layers
+        # fp16 per-token tiles for the fused decode kernel (INT4): copies of the V parameters, and the
+        # constant K tiles (scale 1, zero-point 0: the per-channel K scale travels inside the query)
+        self._v_scale16: List[Optional[Tensor]] = [None] * num_layers
+        self._v_zp16: List[Optional[Tensor]] = [None] * num_layers
+        self._k_ones: List[Optional[Tensor]] = [None] * num_layers
+        self._k_zeros: List[Optional[Tensor]] = [None] * num_layers
         self._k_scale_initialized: List[bool] = [False] * num_layers
         self._layer_seq_lens: List[int] = [0] * num_layers
         self._layer_capacity: List[int] = [0] * num_layers
@@ -89,6 +95,14 @@ class KIVIStyleKVCache:
                 dst[:, :, :old] = src[:, :, :old]
         self._k_cache[layer_id], self._v_cache[layer_id], self._v_scale[layer_id], self._v_zp[layer_id] = new
         self._layer_capacity[layer_id] = new_cap
+        if self.bit_packed:
+            h16 = [torch.empty((batch, heads, phys, 1), device=dev, dtype=torch.float16) for _ in range(2)]
+            if self._v_scale16[layer_id] is not None and old > 0:
+                h16[0][:, :, :old] = self._v_scale16[layer_id][:, :, :old]
+                h16[1][:, :, :old] = self._v_zp16[layer_id][:, :, :old]
+            self._v_scale16[layer_id], self._v_zp16[layer_id] = h16
+            self._k_ones[layer_id] = torch.ones((batch, heads, phys, 1), device=dev, dtype=torch.float16)
+            self._k_zeros[layer_id] = torch.zeros((batch, heads, phys, 1), device=dev, dtype=torch.float16)
         if self._k_scale[layer_id] is None:
             self._k_scale[layer_id] = torch.empty((batch, heads, head_dim), device=dev, dtype=torch.float32)
             self._k_zp[layer_id] = torch.empty((batch, heads, head_dim), device=dev, dtype=torch.float32)
@@ -104,6 +118,8 @@ class KIVIStyleKVCache:
         vs = self._v_scale[layer_id]
         a.v_scale, a.v_zp = vs.data_ptr(), self._v_zp[layer_id].data_ptr()
         a.vs_stride_b, a.vs_stride_h = vs.stride(0), vs.stride(1)
+        if self._v_scale16[layer_id] is not None:
+            a.v_scale_h, a.v_zp_h = self._v_scale16[layer_id].data_ptr(), self._v_zp16[layer_id].data_ptr()
         return a
 
     # ------------------------------------------------------------------ append / read back
@@ -180,11 +196,30 @@ class KIVIStyleKVCache:
 
     def fused_decode(self, layer_id: int, q: Tensor, sm_scale: float, inv_tau: Optional[Tensor] = None,
                      out: Optional[Tensor] = None) -> Tensor:
-        """q_len == 1 attention over this layer: dequantise, then the tensor-core fp16 attention kernel."""
-        k, v = self.get_kv(layer_id)
+        """q_len == 1 attention over this layer.
+
+        Packed INT4 with head_dim 128: ONE fused kernel over the packed cache.  The per-channel K scale is
+        multiplied into the query (logit = sum_d (q_d s_d) code_d; the K zero-points add the same constant to
+        every logit of a head and cancel in the softmax), the per-token V scale is folded into the
+        probabilities and the V zero-points enter as sum_t p_t z_t - the factored-scale path of the decode
+        kernel with one group per token.  The V parameters are read as fp16 (RN16 of the fp32 ones).
+        Otherwise: dequantise, then the tensor-core fp16 attention kernel."""
         original = q.dtype
         if original != torch.float16:
             q = q.to(torch.float16)
+        S = self._layer_seq_lens[layer_id]
+        kc = self._k_cache[layer_id]
+        if self.bit_packed and q.shape[-1] == 128 and kc is not None and S > 0:
+            B, Hq, D = q.shape
+            H = kc.shape[1]
+            qs = (q.float().view(B, H, Hq // H, D) * self._k_scale[layer_id][:, :, None, :]).to(torch.float16)
+            res = ops.decode_attn(_lib.FMT_INT4, qs.view(B, Hq, D), kc[:, :, :S], self._v_cache[layer_id][:, :, :S],
+                                  self._k_ones[layer_id][:, :, :S], self._v_scale16[layer_id][:, :, :S], None,
+                                  float(sm_scale), head_dim=D, k_zp=self._k_zeros[layer_id][:, :, :S],
+                                  v_zp=self._v_zp16[layer_id][:, :, :S],
+                                  inv_tau=None if inv_tau is None else inv_tau.float(), out=out, fast_dequant=True)
+            return res if original == torch.float16 else res.to(original)
+        k, v = self.get_kv(layer_id)
         res = ops.decode_attn(_lib.FMT_FP16, q, k.to(torch.float16), v.to(torch.float16), None, None, None,
                               float(sm_scale), head_dim=q.shape[-1],
                               inv_tau=None if inv_tau is None else inv_tau.float(), out=out)
@@ -203,6 +238,7 @@ class KIVIStyleKVCache:
         n = self.num_layers
         self._k_cache, self._v_cache = [None] * n, [None] * n
         self._k_scale, self._k_zp, self._v_scale, self._v_zp = [None] * n, [None] * n, [None] * n, [None] * n
+        self._v_scale16, self._v_zp16, self._k_ones, self._k_zeros = [None] * n, [None] * n, [None] * n, [None] * n
         self._layer_capacity = [0] * n
         self.clear()
 

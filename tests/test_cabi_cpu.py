@@ -56,7 +56,7 @@ def test_struct_sizes_match_header(lib):
     assert ctypes.sizeof(_lib.KvqCacheSide) == 13 * 8
     assert ctypes.sizeof(_lib.KvqCombineArgs) == 4 * 4 + 10 * 8
     assert ctypes.sizeof(_lib.KvqDequantArgs) == 8 * 4 + 8 + 2 * 13 * 8 + 5 * 8
-    assert ctypes.sizeof(_lib.KvqKiviArgs) == 6 * 4 + 23 * 8
+    assert ctypes.sizeof(_lib.KvqKiviArgs) == 6 * 4 + 25 * 8
     assert ctypes.sizeof(_lib.KvqAbsmaxArgs) == 5 * 4 + 4 + 8 + 3 * 8 + 8
     assert ctypes.sizeof(_lib.KvqExchangeArgs) == 4 * 4 + 2 * 8 + 2 * 4 + 8 + 2 * 4 + 7 * 8
 
