@@ -98,7 +98,7 @@ def make_kivi():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--only", default="", help="'rope' / 'kivi' regenerate rope.npz / kivi.npz alone")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
