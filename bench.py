@@ -6,7 +6,7 @@
 One "step" = one decode step over the whole KV stack of the workload: for every
 layer, quantize-on-append of the new token (one launch for K and V) followed by
 the fused decode attention (split-K kernel + combine) over the cached context.
-Default workload is configuration 2 of BASELINE.json (Qwen2.5-1.5B geometry, 28
+Default workload is configuration 2 of the benchmark definition (Qwen2.5-1.5B geometry, 28
 layers, batch 16, context 8192, INT4 asymmetric group-32 with fp16 scale and
 zero-point).  With N > 1 the batch is sharded by sequence: every rank owns its own
 batch of sequences and its own cache, no collective on the data path (weak scaling).
