@@ -429,7 +429,7 @@ static bool mma_eligible(const AttnParams& p, bool asym) {
     if (a.n_out > 0 && gs != 32) return false;
     const bool f16 = a.format == KVQ_FMT_FP16;
     if (!f16 && a.format != KVQ_FMT_INT8 && a.format != KVQ_FMT_INT4) return false;
-    if (a.format != KVQ_FMT_INT4 && asym) return false;
+    if (asym && (f16 || (a.format == KVQ_FMT_INT8 && gs != 128))) return false;   // INT8 zero-points: one group per token
     if (a.n_out < 0 || a.n_out > kMaxOut || (a.n_out > 0 && (asym || f16))) return false;
     if (a.max_ctx < 1) return false;
     if (!a.k.payload || !a.v.payload || (!f16 && (!a.k.scale || !a.v.scale))) return false;
@@ -505,6 +505,7 @@ static int mma_dispatch(const AttnParams& p, bool asym, F&& f) {
     KVQ_MMA_GS(KVQ_FMT_INT8, false, false)
     KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, false, 16)
     KVQ_MMA_CASE(KVQ_FMT_INT8, false, true, false, 32)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, true, false, false, 128)
     KVQ_MMA_GS(KVQ_FMT_INT4, false, true)
     KVQ_MMA_GS(KVQ_FMT_INT4, true, true)
     KVQ_MMA_CASE(KVQ_FMT_INT4, false, true, true, 32)

@@ -95,7 +95,7 @@ class KIVIStyleKVCache:
                 dst[:, :, :old] = src[:, :, :old]
         self._k_cache[layer_id], self._v_cache[layer_id], self._v_scale[layer_id], self._v_zp[layer_id] = new
         self._layer_capacity[layer_id] = new_cap
-        if self.bit_packed:
+        if head_dim == 128:
             h16 = [torch.empty((batch, heads, phys, 1), device=dev, dtype=torch.float16) for _ in range(2)]
             if self._v_scale16[layer_id] is not None and old > 0:
                 h16[0][:, :, :old] = self._v_scale16[layer_id][:, :, :old]
@@ -198,7 +198,8 @@ class KIVIStyleKVCache:
                      out: Optional[Tensor] = None) -> Tensor:
         """q_len == 1 attention over this layer.
 
-        Packed INT4 with head_dim 128: ONE fused kernel over the packed cache.  The per-channel K scale is
+        head_dim 128: ONE fused kernel over the quantized cache (INT4: the factored-scale path; INT8: per-element
+        fp16 scale and zero-point with one group per token).  The per-channel K scale is
         multiplied into the query (logit = sum_d (q_d s_d) code_d; the K zero-points add the same constant to
         every logit of a head and cancel in the softmax), the per-token V scale is folded into the
         probabilities and the V zero-points enter as sum_t p_t z_t - the factored-scale path of the decode
@@ -209,15 +210,17 @@ class KIVIStyleKVCache:
             q = q.to(torch.float16)
         S = self._layer_seq_lens[layer_id]
         kc = self._k_cache[layer_id]
-        if self.bit_packed and q.shape[-1] == 128 and kc is not None and S > 0:
+        if q.shape[-1] == 128 and kc is not None and S > 0 and self._v_scale16[layer_id] is not None:
             B, Hq, D = q.shape
             H = kc.shape[1]
             qs = (q.float().view(B, H, Hq // H, D) * self._k_scale[layer_id][:, :, None, :]).to(torch.float16)
-            res = ops.decode_attn(_lib.FMT_INT4, qs.view(B, Hq, D), kc[:, :, :S], self._v_cache[layer_id][:, :, :S],
+            fmt = _lib.FMT_INT4 if self.bit_packed else _lib.FMT_INT8
+            res = ops.decode_attn(fmt, qs.view(B, Hq, D), kc[:, :, :S], self._v_cache[layer_id][:, :, :S],
                                   self._k_ones[layer_id][:, :, :S], self._v_scale16[layer_id][:, :, :S], None,
                                   float(sm_scale), head_dim=D, k_zp=self._k_zeros[layer_id][:, :, :S],
                                   v_zp=self._v_zp16[layer_id][:, :, :S],
-                                  inv_tau=None if inv_tau is None else inv_tau.float(), out=out, fast_dequant=True)
+                                  inv_tau=None if inv_tau is None else inv_tau.float(), out=out,
+                                  fast_dequant=self.bit_packed)
             return res if original == torch.float16 else res.to(original)
         k, v = self.get_kv(layer_id)
         res = ops.decode_attn(_lib.FMT_FP16, q, k.to(torch.float16), v.to(torch.float16), None, None, None,
