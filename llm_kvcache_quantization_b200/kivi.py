@@ -4,9 +4,11 @@ asymmetric with fp32 scale and float zero-point, INT8 codes or nibble-packed INT
 Mirror of the reference's `KIVIStyleKVCache` (src/cache/kivi_style_cache.py:34-895) on the CUDA kernels of
 csrc/kvq_kivi.cu: `append` (one launch for K and V; three small launches more on the first append of a
 layer, which derives the per-channel K parameters), `get_kv` (bit-exact dequantisation) and a decode call
-that dequantises and runs the tensor-core fp16 attention kernel - the reference, too, decodes this cache
-through dequantise-then-attend (`decode_attn_impl = "torch_ref"`).  Clipping percentiles below 100 and the
-fp16 residual window (`residual_length > 0`) are not offered.
+over the quantized cache (one fused kernel at head_dim 128; dequantise-then-attend otherwise, which is how
+the reference decodes this cache, `decode_attn_impl = "torch_ref"`).  With `residual_length > 0` the newest
+decode tokens stay in an fp16 window and are quantized as they leave it (:363-405); attention then merges the
+partial over the quantized tokens with the partial over the window.  Clipping percentiles below 100 are not
+offered.
 """
 from __future__ import annotations
 
@@ -31,8 +33,6 @@ class KIVIStyleKVCache:
             raise ValueError(f"quant_bits must be 4 or 8, got {quant_bits}")
         if float(k_percentile) != 100.0 or float(v_percentile) != 100.0:
             raise NotImplementedError("clipping percentiles below 100 are not offered by this cache")
-        if int(residual_length) > 0:
-            raise NotImplementedError("the fp16 residual window (residual_length > 0) is not offered by this cache")
         self.num_layers = num_layers
         self.device = device
         self.dtype = dtype
@@ -43,7 +43,10 @@ class KIVIStyleKVCache:
         self.decode_attn_impl = "torch_ref"
         self.inv_tau = inv_tau
         self.use_attn_temperature = use_attn_temperature
-        self.residual_length = 0
+        self.residual_length = max(0, int(residual_length))
+        self._fp16_k_recent: List[Optional[Tensor]] = [None] * num_layers    # [B, H, residual_length, D]
+        self._fp16_v_recent: List[Optional[Tensor]] = [None] * num_layers
+        self._residual_lens: List[int] = [0] * num_layers
         self._min_capacity = 256
         self._k_cache: List[Optional[Tensor]] = [None] * num_layers
         self._v_cache: List[Optional[Tensor]] = [None] * num_layers
@@ -143,6 +146,26 @@ class KIVIStyleKVCache:
             raise ValueError(f"Invalid k/v shape values: heads={H}, new_seq_len={T}, head_dim={D}")
         if self.bit_packed and D % 2 != 0:
             raise ValueError(f"KIVI INT4 bit packing requires even head_dim, got {D}")
+        if self.residual_length > 0 and T == 1 and self._k_scale_initialized[layer_id]:
+            # the token enters the fp16 window; the oldest one leaves it for the quantized cache once it is full
+            if self._fp16_k_recent[layer_id] is None:
+                self._fp16_k_recent[layer_id] = torch.zeros(B, H, self.residual_length, D, device=k.device, dtype=self.dtype)
+                self._fp16_v_recent[layer_id] = torch.zeros(B, H, self.residual_length, D, device=k.device, dtype=self.dtype)
+            kr, vr = self._fp16_k_recent[layer_id], self._fp16_v_recent[layer_id]
+            rlen = self._residual_lens[layer_id]
+            if rlen < self.residual_length:
+                kr[:, :, rlen:rlen + 1] = k.to(self.dtype)
+                vr[:, :, rlen:rlen + 1] = v.to(self.dtype)
+                self._residual_lens[layer_id] = rlen + 1
+                if layer_id == 0:
+                    self._seq_len = self._layer_seq_lens[0] + self._residual_lens[0]
+                return
+            evict_k, evict_v = kr[:, :, 0:1].clone(), vr[:, :, 0:1].clone()
+            kr[:, :, :-1] = kr[:, :, 1:].clone()
+            vr[:, :, :-1] = vr[:, :, 1:].clone()
+            kr[:, :, -1:] = k.to(self.dtype)
+            vr[:, :, -1:] = v.to(self.dtype)
+            k, v = evict_k, evict_v
         k16 = k if k.dtype == torch.float16 else k.to(torch.float16)
         v16 = v if v.dtype == torch.float16 else v.to(torch.float16)
         if k16.stride(-1) != 1:
@@ -162,7 +185,7 @@ class KIVIStyleKVCache:
         _lib.check("kvq_kivi_append", rc)
         self._k_scale_initialized[layer_id] = True
         self._layer_seq_lens[layer_id] = old + T
-        self._seq_len = max(self._layer_seq_lens)
+        self._seq_len = max(self._layer_seq_lens) + (max(self._residual_lens) if self.residual_length > 0 else 0)
 
     def get_kv(self, layer_id: int) -> Tuple[Tensor, Tensor]:
         """Dequantised (k, v) in `self.dtype` (src/cache/kivi_style_cache.py:602-650)."""
@@ -184,7 +207,12 @@ class KIVIStyleKVCache:
         with torch.cuda.device(kc.device):
             rc = _lib.load().kvq_kivi_dequantize(C.byref(a), ops._stream_ptr(kc.device))
         _lib.check("kvq_kivi_dequantize", rc)
-        return k_out.to(self.dtype), v_out.to(self.dtype)
+        k_out, v_out = k_out.to(self.dtype), v_out.to(self.dtype)
+        rlen = self._residual_lens[layer_id]
+        if self.residual_length > 0 and rlen > 0 and self._fp16_k_recent[layer_id] is not None:
+            k_out = torch.cat([k_out, self._fp16_k_recent[layer_id][:, :, :rlen]], dim=2)
+            v_out = torch.cat([v_out, self._fp16_v_recent[layer_id][:, :, :rlen]], dim=2)
+        return k_out, v_out
 
     def get_int4_asym_tensors(self, layer_id: int):
         """(k_packed, v_packed, k_scale, k_zp, v_scale, v_zp) views (src/cache/kivi_style_cache.py:668-700)."""
@@ -210,6 +238,8 @@ class KIVIStyleKVCache:
             q = q.to(torch.float16)
         S = self._layer_seq_lens[layer_id]
         kc = self._k_cache[layer_id]
+        rlen = self._residual_lens[layer_id] if self.residual_length > 0 else 0
+        tau = None if inv_tau is None else inv_tau.float()
         if q.shape[-1] == 128 and kc is not None and S > 0 and self._v_scale16[layer_id] is not None:
             B, Hq, D = q.shape
             H = kc.shape[1]
@@ -218,14 +248,23 @@ class KIVIStyleKVCache:
             res = ops.decode_attn(fmt, qs.view(B, Hq, D), kc[:, :, :S], self._v_cache[layer_id][:, :, :S],
                                   self._k_ones[layer_id][:, :, :S], self._v_scale16[layer_id][:, :, :S], None,
                                   float(sm_scale), head_dim=D, k_zp=self._k_zeros[layer_id][:, :, :S],
-                                  v_zp=self._v_zp16[layer_id][:, :, :S],
-                                  inv_tau=None if inv_tau is None else inv_tau.float(), out=out,
-                                  fast_dequant=self.bit_packed)
+                                  v_zp=self._v_zp16[layer_id][:, :, :S], inv_tau=tau, out=out,
+                                  fast_dequant=self.bit_packed, return_partial=rlen > 0)
+            if rlen > 0:
+                # merge with the fp16 window.  The fused kernel's logits lack the constant sum_d q_d zp_d of
+                # the K zero-points (it cancels inside one softmax, not across two): add it to that partial's max
+                _, (po, pm, pl) = res
+                qt = q if tau is None else (q * tau.to(torch.float16).view(1, -1, 1))
+                const = (qt.float().view(B, H, Hq // H, D) * self._k_zp[layer_id][:, :, None, :]).sum(-1).view(B, Hq)
+                pm = pm + float(sm_scale) * const
+                _, (wo, wm, wl) = ops.decode_attn(_lib.FMT_FP16, q, self._fp16_k_recent[layer_id][:, :, :rlen].to(torch.float16),
+                                                  self._fp16_v_recent[layer_id][:, :, :rlen].to(torch.float16), None, None,
+                                                  None, float(sm_scale), head_dim=D, inv_tau=tau, return_partial=True)
+                res = ops.lse_combine(torch.stack([po, wo]), torch.stack([pm, wm]), torch.stack([pl, wl]), out=out)
             return res if original == torch.float16 else res.to(original)
         k, v = self.get_kv(layer_id)
         res = ops.decode_attn(_lib.FMT_FP16, q, k.to(torch.float16), v.to(torch.float16), None, None, None,
-                              float(sm_scale), head_dim=q.shape[-1],
-                              inv_tau=None if inv_tau is None else inv_tau.float(), out=out)
+                              float(sm_scale), head_dim=q.shape[-1], inv_tau=tau, out=out)
         return res if original == torch.float16 else res.to(original)
 
     # ------------------------------------------------------------------ bookkeeping (reference surface)
@@ -235,6 +274,7 @@ class KIVIStyleKVCache:
     def clear(self) -> None:
         self._layer_seq_lens = [0] * self.num_layers
         self._k_scale_initialized = [False] * self.num_layers
+        self._residual_lens = [0] * self.num_layers
         self._seq_len = 0
 
     def release(self) -> None:
@@ -243,6 +283,7 @@ class KIVIStyleKVCache:
         self._k_scale, self._k_zp, self._v_scale, self._v_zp = [None] * n, [None] * n, [None] * n, [None] * n
         self._v_scale16, self._v_zp16, self._k_ones, self._k_zeros = [None] * n, [None] * n, [None] * n, [None] * n
         self._layer_capacity = [0] * n
+        self._fp16_k_recent, self._fp16_v_recent = [None] * n, [None] * n
         self.clear()
 
     def get_memory_mb(self) -> float:

@@ -92,6 +92,21 @@ def make_kivi():
         out[f"b{bits}_v_scale"], out[f"b{bits}_v_zp"] = _np(c._v_scale[0][:, :, :S]), _np(c._v_zp[0][:, :, :S])
         kd, vd = c.get_kv(0)
         out[f"b{bits}_k_deq"], out[f"b{bits}_v_deq"] = _np(kd), _np(vd)
+    # fp16 residual window: the newest `residual_length` decode tokens stay unquantized, older ones are
+    # quantized as they leave the window
+    R, N2 = 4, 7
+    k2 = gen_kv(gen, B, H, P + N2, D, outlier_ch=2)
+    v2 = gen_kv(gen, B, H, P + N2, D)
+    out["res_k"], out["res_v"], out["res_len"] = _np(k2), _np(v2), np.array(R)
+    c = KIVIStyleKVCache(num_layers=1, device="cpu", quant_bits=4, residual_length=R)
+    c.append(0, k2[:, :, :P], v2[:, :, :P])
+    for t in range(P, P + N2):
+        c.append(0, k2[:, :, t:t + 1], v2[:, :, t:t + 1])
+    nq = c._layer_seq_lens[0]
+    out["res_quantized_len"], out["res_seq_len"] = np.array(nq), np.array(c.get_seq_len())
+    out["res_k_payload"], out["res_v_payload"] = _np(c._k_cache[0][:, :, :nq]), _np(c._v_cache[0][:, :, :nq])
+    kd, vd = c.get_kv(0)
+    out["res_k_deq"], out["res_v_deq"] = _np(kd), _np(vd)
     np.savez_compressed(os.path.join(HERE, "kivi.npz"), **out)
     print("kivi.npz", os.path.getsize(os.path.join(HERE, "kivi.npz")) // 1024, "KiB")
 
