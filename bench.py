@@ -45,6 +45,9 @@ WORKLOADS = {
     "c2_fp16": dict(layers=28, B=16, Hq=12, Hkv=2, S=8192, kind="fp16", n_out=0,
                     desc="config-2 shape with an UNQUANTISED fp16 cache (comparison point): 28-layer KV stack, batch 16, "
                          "ctx 8192"),
+    "c2_kivi4": dict(layers=28, B=16, Hq=12, Hkv=2, S=8192, kind="kivi4", n_out=0,
+                     desc="config-2 shape with the KIVI-format cache: per-channel K / per-token V asymmetric INT4, "
+                          "28-layer KV stack, batch 16, ctx 8192"),
     "c5": dict(layers=48, B=1, Hq=40, Hkv=8, S=131072, kind="int4_outlier", n_out=1,
                desc="C5: 48-layer KV stack, Qwen2.5-14B geometry, batch 1, ctx 131072, INT4 group-32 + 1 fp16 outlier "
                     "channel"),
@@ -56,7 +59,7 @@ G = D // GS
 
 # DRAM traffic / algorithmic bytes of the split-K scan, from the ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same kernel, scaled by token-heads)
-NCU_TRAFFIC_RATIO = {"fp16": 1.0, "int4_asym": 1.003, "int8_dyn": 1.004, "int8_static": 1.004, "int4_outlier": 1.028}
+NCU_TRAFFIC_RATIO = {"kivi4": 1.0, "fp16": 1.0, "int4_asym": 1.003, "int8_dyn": 1.004, "int8_static": 1.004, "int4_outlier": 1.028}
 
 
 def bytes_per_token_head(kind: str, n_out: int) -> int:
@@ -64,6 +67,8 @@ def bytes_per_token_head(kind: str, n_out: int) -> int:
     fp16 scales (+ zero-points) (+ fp16 outlier side values), each counted once."""
     if kind == "fp16":
         return 2 * 2 * D
+    if kind == "kivi4":               # packed K and V rows + the four fp16 per-token tiles the fused kernel reads
+        return 2 * (D // 2) + 4 * 2
     if kind in ("int8_static", "int8_dyn"):
         return 2 * (D + 2 * G)
     if kind == "int4_asym":
@@ -136,6 +141,8 @@ def build_workload(wl: dict, dev, seed: int, extra_slots: int):
     outlier_idx = None
     if kind == "fp16":
         cache = kvq.FP16KVCache(L, device=dev, max_seq_len=cap)
+    elif kind == "kivi4":
+        cache = kvq.KIVIStyleKVCache(L, device=dev, quant_bits=4, max_seq_len=cap)
     elif kind == "int8_static":
         tab = torch.full((L, Hkv, G), 4.5 / 127, dtype=torch.float16, device=dev)
         cache = kvq.INT8KVCache(L, static_k_scale=tab, static_v_scale=tab, **kw)
@@ -151,7 +158,10 @@ def build_workload(wl: dict, dev, seed: int, extra_slots: int):
         cache = kvq.INT4KVCache(L, static_k_scale=tab, static_v_scale=tab, outlier_idx=outlier_idx.to(dev), **kw)
     chunk = max(1, min(S, (1 << 26) // (B * Hkv * D)))       # <= 128 MB fp16 per generated chunk
     for l in range(L):
-        cache.reserve(l, B, Hkv, D, cap)
+        if kind == "kivi4":
+            cache._ensure_capacity(l, B, Hkv, D, cap)
+        else:
+            cache.reserve(l, B, Hkv, D, cap)
         if kind == "int4_asym":
             std = torch.exp(torch.empty(1, Hkv, 1, D, device=dev).uniform_(np.log(0.3), np.log(3.0), generator=gen))
         else:
@@ -172,12 +182,35 @@ def build_workload(wl: dict, dev, seed: int, extra_slots: int):
     return cache, q, k_new, v_new, inv_tau
 
 
+def make_kivi_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=True):
+    """Decode step over the KIVI-format cache: per layer the single-token append (slot S every step) and the
+    fused decode (per-channel K scale applied to the query inside the kernel, factored-scale path over the
+    packed cache)."""
+    import torch
+    from llm_kvcache_quantization_b200 import ops, _lib
+    L, B, Hq, Hkv, S = wl["layers"], wl["B"], wl["Hq"], wl["Hkv"], wl["S"]
+    n = S + 1
+
+    def step():
+        for l in range(L):
+            if with_append:
+                cache._layer_seq_lens[l] = S
+                cache.append(l, k_new[l], v_new[l])
+            ops.decode_attn(_lib.FMT_INT4, q[l], cache._k_cache[l][:, :, :n], cache._v_cache[l][:, :, :n],
+                            cache._k_ones[l][:, :, :n], cache._v_scale16[l][:, :, :n], None, 1.0 / D ** 0.5, head_dim=D,
+                            k_zp=cache._k_zeros[l][:, :, :n], v_zp=cache._v_zp16[l][:, :, :n], inv_tau=inv_tau[l],
+                            out=out[l], fast_dequant=True, stages=stages, q_chan_scale=cache._k_scale[l])
+    return step, (lambda: ops.last_splits())
+
+
 def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=True):
     """Returns a callable running one decode step with device-resident inputs.  The new
     token is written at slot S every step (steady state at the nominal context)."""
     import torch
     from llm_kvcache_quantization_b200 import ops, _lib
 
+    if wl["kind"] == "kivi4":
+        return make_kivi_step(wl, cache, q, k_new, v_new, inv_tau, out, stages, with_append)
     L, B, Hkv, S, kind = wl["layers"], wl["B"], wl["Hkv"], wl["S"], wl["kind"]
     dev = q.device
     ctx = torch.full((B,), S + 1, dtype=torch.int32, device=dev)
@@ -748,7 +781,7 @@ def main():
     # for all layers from pinned memory, replays the captured whole-stack step (append + attention per
     # layer, device-side position counter, the cache grows by one token) and downloads the outputs
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and wl["kind"] != "kivi4":      # the host-buffer stepper serves the group-wise caches
         from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
         stepper = GraphedKVStackStep(cache, Hq, 1.0 / D ** 0.5, inv_tau=inv_tau)
         stepper.capture()
@@ -779,7 +812,7 @@ def main():
                       "layers' kernels, then the tail); stream sync"}
 
     aux = None
-    if args.aux and wl["kind"] != "fp16":
+    if args.aux and wl["kind"] not in ("fp16", "kivi4"):
         aux = time_aux(wl, cache, dev)
 
     model_step = None
@@ -787,7 +820,7 @@ def main():
         model_step = time_model_step(wl, cache, dev, steps=max(3, min(args.steps, 10)))
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and wl["kind"] != "fp16":
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and wl["kind"] not in ("fp16", "kivi4"):
         per_pass, rows, threads = cpu_sample(wl, target_s=12.0)
         step_s = per_pass * L * (B / rows)
         cpu = {"value": B / step_s, "unit": "tokens/s", "cores": threads, "kind": "port",

@@ -166,6 +166,10 @@ typedef struct KvqAttnArgs {
     void*   out;              /* fp16 [B, Hq, D] or NULL                                  */
     int64_t out_stride_b, out_stride_h;                 /* elements                      */
     /* optional normalised partial for a cross-GPU merge (all three or none):            */
+    const float* q_chan_scale; /* fp32 [B, Hkv, D] or NULL: q[b, h, d] <- RN16(q[b, h, d] * q_chan_scale[b, h / n_rep, d])
+                                  after inv_tau - a per-channel K scale carried by the query (KIVI-format caches,
+                                  whose K tiles then hold scale 1)                                                  */
+    int64_t qcs_stride_b, qcs_stride_h;                 /* elements                      */
     float*  part_o;           /* fp32 [B, Hq, D]  o = sum p v / l                         */
     float*  part_m;           /* fp32 [B, Hq]     running max of scaled logits (-inf if empty) */
     float*  part_l;           /* fp32 [B, Hq]     sum exp(logit - m)  (0 if empty)        */

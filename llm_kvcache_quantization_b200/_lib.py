@@ -71,6 +71,7 @@ class KvqAttnArgs(C.Structure):
         ("splits", _i32), ("stages", _i32), ("fast_dequant", _i32), ("tail_tokens", _i32),
         ("workspace", _vp), ("workspace_bytes", C.c_size_t),
         ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
+        ("q_chan_scale", _vp), ("qcs_stride_b", _i64), ("qcs_stride_h", _i64),
         ("part_o", _vp), ("part_m", _vp), ("part_l", _vp),
         ("part_o_stride", _i64), ("part_ml_stride", _i64),
     ]

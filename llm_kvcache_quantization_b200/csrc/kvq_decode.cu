@@ -121,6 +121,8 @@ __device__ __forceinline__ void fold_tail(const AttnParams& p, int b, int h, flo
     if (d < D) {
         __half qv = ((const __half*)a.q)[b * a.q_stride_b + h * a.q_stride_h + d];
         if (a.inv_tau) qv = __hmul(qv, __float2half_rn(a.inv_tau[h]));
+        if (a.q_chan_scale)
+            qv = __float2half_rn(__half2float(qv) * a.q_chan_scale[b * a.qcs_stride_b + kvh * a.qcs_stride_h + d]);
         prod = __half2float(qv) * cached_value(a, a.k, b, kvh, t, d);
         vd = cached_value(a, a.v, b, kvh, t, d);
     }
@@ -659,6 +661,7 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     if ((a.q_stride_b & 1) || (a.q_stride_h & 1) || (((uintptr_t)a.q) & 3)) return KVQ_EINVAL;
     if (a.stages < 0 || a.stages > 2) return KVQ_EINVAL;
     if (a.tail_tokens < 0 || a.tail_tokens > 1) return KVQ_EINVAL;
+    if (a.q_chan_scale && (a.format == KVQ_FMT_FP16 || a.n_out > 0)) return KVQ_EUNSUPPORTED;
 
     const bool mma = mma_eligible(p, asym);
     p.splits = a.splits > 0 ? a.splits : pick_splits_internal(p, asym, mma);

@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(128) decode_split_generic_kernel(const AttnPar
         if (h < nh) {
             __half qv = ((const __half*)a.q)[b * a.q_stride_b + (h0 + h) * a.q_stride_h + d];
             if (a.inv_tau) qv = __hmul(qv, __float2half_rn(a.inv_tau[h0 + h]));
+            if (a.q_chan_scale)
+                qv = __float2half_rn(__half2float(qv) * a.q_chan_scale[b * a.qcs_stride_b + kvh * a.qcs_stride_h + d]);
             v = __half2float(qv) * qk_scale;
         }
         q_s[h][d] = v;

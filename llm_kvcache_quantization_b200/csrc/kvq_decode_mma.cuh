@@ -341,6 +341,16 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             qv[i] = hv ? qv[i] : __float2half(0.f);
             if (a.inv_tau) qv[i] = __hmul(qv[i], tau);
         }
+        if (a.q_chan_scale) {
+            // per-channel factor of this kv head; element i of the slice is channel 32 (i / 8) + 8 t + i % 8 in the
+            // factored layout, 32 t + i otherwise
+            const float* cs = a.q_chan_scale + (long long)b * a.qcs_stride_b + (long long)kvh * a.qcs_stride_h;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int ch = FAST ? 32 * (i >> 3) + 8 * t + (i & 7) : 32 * t + i;
+                qv[i] = __float2half_rn(__half2float(qv[i]) * cs[ch]);
+            }
+        }
         if (FAST && ASYM) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {                       // 32-channel chunk c lies in group (32 c) / GS

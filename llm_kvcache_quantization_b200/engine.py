@@ -522,7 +522,7 @@ def load_calibration(calib_file: str, kv_mode: str, device, *, use_static_scales
 
 def build_cache(kv_mode: str, num_layers: int, device, *, group_size=128, clip_percentile=99.9, max_seq_len=None,
                 calib: Optional[dict] = None, decode_attn_impl="triton_fused", use_attn_temperature=True,
-                quant_bits: int = 8):
+                quant_bits: int = 8, residual_length: int = 0):
     """Cache engine for a kv_mode (src/engine/generate_loop.py:891-938)."""
     if kv_mode not in FUSED_KV_MODES:
         raise ValueError(f"kv_mode={kv_mode!r} is not supported here; choose one of {sorted(FUSED_KV_MODES)}")
@@ -530,7 +530,8 @@ def build_cache(kv_mode: str, num_layers: int, device, *, group_size=128, clip_p
         return FP16KVCache(num_layers, device=device, max_seq_len=max_seq_len)
     if kv_mode == "kivi_style":        # per-channel K / per-token V asymmetric (src/engine/generate_loop.py:905-921)
         from .kivi import KIVIStyleKVCache
-        return KIVIStyleKVCache(num_layers, device=device, max_seq_len=max_seq_len, quant_bits=quant_bits)
+        return KIVIStyleKVCache(num_layers, device=device, max_seq_len=max_seq_len, quant_bits=quant_bits,
+                                residual_length=residual_length)
     calib = calib or {}
     gs = calib.get("group_size") or group_size
     cp = calib.get("clip_percentile") or clip_percentile
@@ -569,7 +570,7 @@ def _prefill_into_cache(model, cache, input_ids, attention_mask):
 def generate_from_ids(model, tokenizer, input_ids, attention_mask=None, max_new_tokens=128, kv_mode="fp16",
                       group_size=128, clip_percentile=99.9, seed=1234, calib_file=None, use_attn_temperature=True,
                       use_static_scales=True, decode_attn_impl="triton_fused", allow_missing_calib=False,
-                      stop_on_eos=True, quant_bits=8, **_ignored) -> GenerationBatchOutput:
+                      stop_on_eos=True, quant_bits=8, residual_length=0, **_ignored) -> GenerationBatchOutput:
     """Greedy generation with a quantized KV cache and the fused decode path
     (src/engine/generate_loop.py:393-1581, the fused modes and fp16).  Requires CUDA."""
     if kv_mode not in FUSED_KV_MODES:
@@ -599,7 +600,8 @@ def generate_from_ids(model, tokenizer, input_ids, attention_mask=None, max_new_
     max_seq = prompt_len + max_new_tokens if max_pos is None else min(max_pos, prompt_len + max_new_tokens)
     cache = build_cache(kv_mode, num_layers, device, group_size=group_size, clip_percentile=clip_percentile,
                         max_seq_len=max_seq, calib=calib, decode_attn_impl=decode_attn_impl,
-                        use_attn_temperature=use_attn_temperature, quant_bits=quant_bits)
+                        use_attn_temperature=use_attn_temperature, quant_bits=quant_bits,
+                        residual_length=residual_length)
     eos = getattr(tokenizer, "eos_token_id", None)
     if isinstance(eos, (list, tuple)):
         eos = eos[0] if eos else None

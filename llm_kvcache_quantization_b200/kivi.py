@@ -228,7 +228,7 @@ class KIVIStyleKVCache:
 
         head_dim 128: ONE fused kernel over the quantized cache (INT4: the factored-scale path; INT8: per-element
         fp16 scale and zero-point with one group per token).  The per-channel K scale is
-        multiplied into the query (logit = sum_d (q_d s_d) code_d; the K zero-points add the same constant to
+        multiplied into the query inside the kernel (`q_chan_scale`; logit = sum_d (q_d s_d) code_d; the K zero-points add the same constant to
         every logit of a head and cancel in the softmax), the per-token V scale is folded into the
         probabilities and the V zero-points enter as sum_t p_t z_t - the factored-scale path of the decode
         kernel with one group per token.  The V parameters are read as fp16 (RN16 of the fp32 ones).
@@ -243,13 +243,13 @@ class KIVIStyleKVCache:
         if q.shape[-1] == 128 and kc is not None and S > 0 and self._v_scale16[layer_id] is not None:
             B, Hq, D = q.shape
             H = kc.shape[1]
-            qs = (q.float().view(B, H, Hq // H, D) * self._k_scale[layer_id][:, :, None, :]).to(torch.float16)
             fmt = _lib.FMT_INT4 if self.bit_packed else _lib.FMT_INT8
-            res = ops.decode_attn(fmt, qs.view(B, Hq, D), kc[:, :, :S], self._v_cache[layer_id][:, :, :S],
+            res = ops.decode_attn(fmt, q, kc[:, :, :S], self._v_cache[layer_id][:, :, :S],
                                   self._k_ones[layer_id][:, :, :S], self._v_scale16[layer_id][:, :, :S], None,
                                   float(sm_scale), head_dim=D, k_zp=self._k_zeros[layer_id][:, :, :S],
                                   v_zp=self._v_zp16[layer_id][:, :, :S], inv_tau=tau, out=out,
-                                  fast_dequant=self.bit_packed, return_partial=rlen > 0)
+                                  fast_dequant=self.bit_packed, return_partial=rlen > 0,
+                                  q_chan_scale=self._k_scale[layer_id])
             if rlen > 0:
                 # merge with the fp16 window.  The fused kernel's logits lack the constant sum_d q_d zp_d of
                 # the K zero-points (it cancels inside one softmax, not across two): add it to that partial's max

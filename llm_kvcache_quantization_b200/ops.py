@@ -214,7 +214,8 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
                 splits: int = 0, out: Optional[torch.Tensor] = None,
                 return_partial: bool = False, max_ctx: Optional[int] = None, stages: int = 0,
                 packed_partial: Optional[torch.Tensor] = None, fast_dequant: Optional[bool] = None,
-                tail_tokens: int = 0, exchange: Optional[dict] = None):
+                tail_tokens: int = 0, exchange: Optional[dict] = None,
+                q_chan_scale: Optional[torch.Tensor] = None):
     """Fused q_len==1 attention over a (quantized) cache.  q fp16 [B,Hq,D].
 
     Returns `out` fp16 [B,Hq,D]; with `return_partial` also the normalised
@@ -253,6 +254,11 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
     if fast_dequant is None:       # KVQ_INT4_FAST=1: factored-scale INT4 path instead of bit-faithful dequantisation
         fast_dequant = os.environ.get("KVQ_INT4_FAST", "0") == "1"
     a.fast_dequant = 1 if fast_dequant else 0
+    if q_chan_scale is not None:       # fp32 [B, Hkv, D]: per-channel factor applied to the query inside the kernel
+        if q_chan_scale.dtype != torch.float32 or tuple(q_chan_scale.shape) != (B, Hkv, D) or q_chan_scale.stride(-1) != 1:
+            raise ValueError("q_chan_scale must be an fp32 [B, Hkv, D] tensor, contiguous in head_dim")
+        a.q_chan_scale = q_chan_scale.data_ptr()
+        a.qcs_stride_b, a.qcs_stride_h = q_chan_scale.stride(0), q_chan_scale.stride(1)
     a.tail_tokens = int(tail_tokens)   # 1: the last token of each row is attended by the combine stage (see kvq.h)
     a.k = _cache_side(k_payload, k_scale, k_zp, k_side)
     a.v = _cache_side(v_payload, v_scale, v_zp, v_side)

@@ -196,7 +196,7 @@ def test_kivi_style_mode_generates(tiny_model, bits):
     ids = torch.randint(0, 512, (2, 40), generator=g).to(DEV)
     ref, _ = _hf_greedy(tiny_model, ids, 6)
     out = E.generate_from_ids(tiny_model, _Tok(), ids, max_new_tokens=6, kv_mode="kivi_style", quant_bits=bits,
-                              stop_on_eos=False)
+                              residual_length=4 if bits == 4 else 0, stop_on_eos=False)
     assert out.generated_ids.shape == (2, 6) and out.kv_cache_seq_len == 45
     assert torch.equal(out.generated_ids[:, 0], ref[:, 0])          # the first token comes from the fp16 prefill
     if bits == 8:
