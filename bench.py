@@ -479,6 +479,10 @@ def run_reference_arm(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # the multi-process launcher pins every rank to one OpenMP thread; this arm runs on rank 0 alone and
+        # uses the host's cores (the setting is read when the OpenMP runtime of the C oracle starts)
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     per_pass, rows, threads = cpu_sample(wl, target_s=2.0)          # warm-up + calibration
     times = []
     for _ in range(max(args.warmup, 0)):
