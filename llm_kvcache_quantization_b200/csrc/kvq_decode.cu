@@ -107,17 +107,20 @@ __device__ __forceinline__ float cached_value(const KvqAttnArgs& a, const KvqCac
 }
 
 // The last token of the row's context, attended here instead of in the split kernel (tail_tokens = 1).
-// Thread d owns channel d.  In: the merged splits as (M log2-domain max, o_d weighted sum, Lt denominator);
-// out: the same triple with the token folded in.  Called by every thread of the CTA (it synchronises).
+// Thread d owns channel d.  tail_load issues the loads (query, the token's K and V rows, their parameters) and
+// returns this thread's q.k product and V value; it is called BEFORE the partials are merged so that both sets of
+// loads are in flight together.  tail_fold then folds the token into the merged splits, given as (M log2-domain
+// max, o_d weighted sum, Lt denominator).  Both are called by every thread of the CTA.
 template <int EPL>
-__device__ __forceinline__ void fold_tail(const AttnParams& p, int b, int h, float* scratch, float& M, float& o_d, float& Lt) {
+__device__ __forceinline__ bool tail_load(const AttnParams& p, int b, int h, float& prod, float& vd) {
     const KvqAttnArgs& a = p.a;
     constexpr int D = EPL * 32;
+    prod = 0.f;
+    vd = 0.f;
     int ctx = a.context_lens ? a.context_lens[b] : a.max_ctx;
     ctx = max(0, min(ctx, a.max_ctx));
-    if (ctx < 1) return;                                  // uniform over the CTA
+    if (ctx < 1) return false;                            // uniform over the CTA
     const int t = ctx - 1, kvh = h / p.n_rep, d = threadIdx.x;
-    float prod = 0.f, vd = 0.f;
     if (d < D) {
         __half qv = ((const __half*)a.q)[b * a.q_stride_b + h * a.q_stride_h + d];
         if (a.inv_tau) qv = __hmul(qv, __float2half_rn(a.inv_tau[h]));
@@ -126,6 +129,11 @@ __device__ __forceinline__ void fold_tail(const AttnParams& p, int b, int h, flo
         prod = __half2float(qv) * cached_value(a, a.k, b, kvh, t, d);
         vd = cached_value(a, a.v, b, kvh, t, d);
     }
+    return true;
+}
+
+__device__ __forceinline__ void tail_fold(const KvqAttnArgs& a, float* scratch, float prod, float vd, float& M,
+                                          float& o_d, float& Lt) {
     prod = warp_sum(prod);
     __syncthreads();                                      // scratch may still be read as `red`
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = prod;
@@ -151,10 +159,12 @@ __global__ void __launch_bounds__(kCombineThreads) combine_splits_kernel(const A
     constexpr int D = EPL * 32;
     __shared__ float red[kCombineWarps][D + 1];
     __shared__ float tail_scratch[kCombineWarps];
+    float tprod, tvd;
+    const bool has_tail = a.tail_tokens && tail_load<EPL>(p, b, h, tprod, tvd);
     float M = combine_partials<EPL>(p, b, h, red);
     float o = threadIdx.x < D ? red_sum(red, threadIdx.x) : 0.f;      // kCombineThreads >= D: one channel per thread
     float Lt = red_sum(red, D);
-    if (a.tail_tokens) fold_tail<EPL>(p, b, h, tail_scratch, M, o, Lt);
+    if (has_tail) tail_fold(a, tail_scratch, tprod, tvd, M, o, Lt);
     for (int d = threadIdx.x; d < D; d += kCombineThreads) {
         const float r = (Lt > 0.f) ? o / Lt : 0.f;
         if (a.out) ((__half*)a.out)[b * a.out_stride_b + h * a.out_stride_h + d] = __float2half_rn(r);
@@ -224,10 +234,12 @@ __global__ void __launch_bounds__(kCombineThreads) combine_exchange_kernel(const
     __shared__ float red[kCombineWarps][D + 1];
     __shared__ float pm[KVQ_MAX_PEERS], pl[KVQ_MAX_PEERS];
     __shared__ float tail_scratch[kCombineWarps];
+    float tprod, tvd;
+    const bool has_tail = a.tail_tokens && tail_load<EPL>(p, b, h, tprod, tvd);
     float M = combine_partials<EPL>(p, b, h, red);
     float o = threadIdx.x < D ? red_sum(red, threadIdx.x) : 0.f;      // one channel per thread
     float Lt = red_sum(red, D);
-    if (a.tail_tokens) fold_tail<EPL>(p, b, h, tail_scratch, M, o, Lt);
+    if (has_tail) tail_fold(a, tail_scratch, tprod, tvd, M, o, Lt);
 
     const int epoch = *x.epoch;
     const long long rows = (long long)a.B * a.Hq;
