@@ -392,6 +392,10 @@ static int launch(const QuantParams& p, cudaStream_t st) {
     if (!dyn_sort && side_vec_ok(a.k) && side_vec_ok(a.v) && rope_vec_ok) {
         // register-resident chunks of 32 (or 16) channels; rotary partners are whole chunks
         if (FMT == KVQ_FMT_FP16 && a.D % 32 == 0) return launch_gs<FMT, POLICY, 32, 1>(p, st);   // a plain copy: any chunking
+        // a handful of rows (one decode token): spread each group of 32 over two lanes - the per-element division
+        // chain of a thread halves, and the launch is a latency chain, not a throughput kernel
+        const long long groups = (long long)a.B * a.Hkv * a.T * (a.D / (gs > 0 ? gs : 1)) * p.nsides;
+        if (gs == 32 && FMT != KVQ_FMT_FP16 && groups <= 4096) return launch_gs<FMT, POLICY, 16, 2>(p, st);
         if (gs == 32) return launch_gs<FMT, POLICY, 32, 1>(p, st);
         if (gs == 64) return launch_gs<FMT, POLICY, 32, 2>(p, st);
         if (gs == 128) return launch_gs<FMT, POLICY, 32, 4>(p, st);
