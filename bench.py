@@ -261,7 +261,8 @@ def make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=0, with_append=Tr
                 continue
             if with_append:
                 ops.quantize_append(fmt, policy, k_new[l], v_new[l], b["k"], b["v"], b.get("ks"), b.get("vs"), S, gsz, **app)
-            attend(l, view, att, stages=stages)
+            # scan-only timing: the same scan as the overlapped step (the newest token belongs to the combine stage)
+            attend(l, view, att, stages=stages, tail_tokens=1 if (stages == 1 and not with_append) else 0)
     return step, (lambda: ops.last_splits())
 
 

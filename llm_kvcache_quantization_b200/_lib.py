@@ -165,7 +165,8 @@ class KvqError(RuntimeError):
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    """The library this process loads: `KVQ_LIBRARY` (a variant built with `build.py --out`), else the in-tree build."""
+    return os.environ.get("KVQ_LIBRARY") or _build.LIB_PATH
 
 
 def load():

@@ -1,9 +1,11 @@
 """Builds libkvq.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python -m llm_kvcache_quantization_b200.build [--force] [--verbose]
+    python -m llm_kvcache_quantization_b200.build [--force] [--verbose] [-DNAME=VALUE ...] [--out PATH]
 
 The library is written next to this file so that it travels with a source
 snapshot; nothing is installed into site-packages and no JIT cache is used.
+`-D` and `--out` build a second, differently configured copy (the profiling variants: phase
+ablations of the decode kernel, occupancy settings); `KVQ_LIBRARY=PATH` makes the package load it.
 """
 from __future__ import annotations
 
@@ -44,11 +46,16 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library if it is missing or older than its sources."""
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, defines=(), out: str | None = None) -> str:
+    """Compile the library if it is missing or older than its sources.  `defines` ("NAME=VALUE") and `out`
+    produce a variant next to (never instead of) the default library."""
+    if out is None and defines:
+        raise ValueError("a build with extra defines needs its own output path")
+    target = out or LIB_PATH
+    if out is None and not force and not _stale():
         return LIB_PATH
-    cmd = [_nvcc(), "-shared", "-o", LIB_PATH, "-I", INCLUDE, "-I", CSRC, *NVCC_FLAGS]
+    cmd = [_nvcc(), "-shared", "-o", target, "-I", INCLUDE, "-I", CSRC, *NVCC_FLAGS]
+    cmd += [f"-D{d}" for d in defines]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
@@ -58,8 +65,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write(proc.stdout + proc.stderr)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed building libkvq.so")
-    return LIB_PATH
+    return target
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    argv = sys.argv[1:]
+    out_path = argv[argv.index("--out") + 1] if "--out" in argv else None
+    print(build(force="--force" in argv, verbose="--verbose" in argv,
+                defines=[a[2:] for a in argv if a.startswith("-D")], out=out_path))

@@ -404,13 +404,18 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // Payload [B, Hkv, S, row_bytes] as a 4-D byte tensor; box = (min(row_bytes, 128), TS, 1, 1), swizzle = box
 // width.  Rows at or beyond `s_extent` are zero-filled by the copy engine.
-static int make_payload_map(CUtensorMap* map, const KvqCacheSide& sd, int row_bytes, int s_extent, int hkv, int b) {
+// `pair_rows`: two consecutive 64-byte token rows are mapped as ONE 128-byte row (`s_extent` counts such pairs; the
+// caller guarantees tokens are contiguous, pay_stride_s == row_bytes / 2): the copy engine then moves 128-byte
+// segments instead of 64-byte ones, which is what the memory system is built for.
+static int make_payload_map(CUtensorMap* map, const KvqCacheSide& sd, int row_bytes, int s_extent, int hkv, int b,
+                            bool pair_rows = false) {
     const int box_bytes = row_bytes > 128 ? 128 : row_bytes;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return KVQ_EUNSUPPORTED;
     cuuint64_t dims[4] = {(cuuint64_t)row_bytes, (cuuint64_t)s_extent, (cuuint64_t)hkv, (cuuint64_t)b};
-    cuuint64_t strides[3] = {(cuuint64_t)sd.pay_stride_s, (cuuint64_t)sd.pay_stride_h, (cuuint64_t)sd.pay_stride_b};
-    cuuint32_t box[4] = {(cuuint32_t)box_bytes, (cuuint32_t)kTS, 1, 1};
+    cuuint64_t strides[3] = {(cuuint64_t)(pair_rows ? 2 * sd.pay_stride_s : sd.pay_stride_s), (cuuint64_t)sd.pay_stride_h,
+                             (cuuint64_t)sd.pay_stride_b};
+    cuuint32_t box[4] = {(cuuint32_t)box_bytes, (cuuint32_t)(pair_rows ? kTS / 2 : kTS), 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(sd.payload), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -539,6 +544,14 @@ static const MmaConfig* mma_config_for(const AttnParams& p, bool asym) {
     return out;
 }
 
+static bool wide_rows_possible(const KvqAttnArgs& a) {
+    return a.format == KVQ_FMT_INT4 && a.k.pay_stride_s == 64 && a.v.pay_stride_s == 64 && a.max_ctx >= 2 &&
+           !getenv("KVQ_INT4_NARROW_ROWS");
+}
+static bool wide_rows_ok(const KvqAttnArgs& a) {
+    return wide_rows_possible(a) && ((a.max_ctx & 1) == 0 || a.tail_tokens == 1);
+}
+
 template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
 static int launch_mma(MmaTag<FMT, ASYM, OUTL, FAST, GS> tag, const AttnParams& p, cudaStream_t st) {
     constexpr int RB = FMT == KVQ_FMT_FP16 ? 256 : FMT == KVQ_FMT_INT8 ? 128 : 64;
@@ -548,10 +561,17 @@ static int launch_mma(MmaTag<FMT, ASYM, OUTL, FAST, GS> tag, const AttnParams& p
     mp.p = p;
     mp.nstage = cfg.nstage;
     mp.warp_smem_bytes = cfg.nstage * cfg.stage_bytes;
+    // Packed INT4 rows are 64 bytes.  When the tokens of a (b, h) row are contiguous, pairs of tokens are fetched as
+    // 128-byte rows.  The pair view covers floor(max_ctx / 2) pairs, so that nothing beyond token max_ctx - 1 is ever
+    // read: with an odd max_ctx the last token must belong to the combine stage (tail_tokens), which kvq_decode_attn
+    // arranges for whole calls; a split-only call without it keeps the 64-byte rows.
+    mp.wide_rows = FMT == KVQ_FMT_INT4 && wide_rows_ok(p.a);
     CUtensorMap kmap, vmap;
-    int rc = make_payload_map(&kmap, p.a.k, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
+    int rc, ext = p.a.max_ctx;
+    if (mp.wide_rows) ext = p.a.max_ctx / 2;
+    rc = make_payload_map(&kmap, p.a.k, mp.wide_rows ? 2 * RB : RB, ext, p.a.Hkv, p.a.B, mp.wide_rows != 0);
     if (rc) return rc;
-    rc = make_payload_map(&vmap, p.a.v, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
+    rc = make_payload_map(&vmap, p.a.v, mp.wide_rows ? 2 * RB : RB, ext, p.a.Hkv, p.a.B, mp.wide_rows != 0);
     if (rc) return rc;
     dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
     return launch_pdl(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST, GS>, grid, dim3(kMmaWarps * 32), cfg.dyn_smem, st, mp,
@@ -676,6 +696,9 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     if (a.q_chan_scale && (a.format == KVQ_FMT_FP16 || a.n_out > 0)) return KVQ_EUNSUPPORTED;
 
     const bool mma = mma_eligible(p, asym);
+    // whole call over a packed-INT4 cache with an odd token count: hand the last token to the combine stage so that
+    // the scan can fetch pairs of tokens as 128-byte rows (see launch_mma)
+    if (mma && a.stages == 0 && a.tail_tokens == 0 && (a.max_ctx & 1) && wide_rows_possible(a)) p.a.tail_tokens = 1;
     p.splits = a.splits > 0 ? a.splits : pick_splits_internal(p, asym, mma);
     size_t need = kvq_decode_workspace_bytes(a.B, a.Hq, a.D, p.splits);
     if (!a.workspace || a.workspace_bytes < need || (((uintptr_t)a.workspace) & 15)) return KVQ_EWORKSPACE;

@@ -42,6 +42,17 @@
 #include "kvq_decode_generic.cuh"
 #include "kvq_internal.h"
 
+// Profiling builds only (build.py -DKVQ_ABLATE=bits --out ...): leave one phase of the loop out so that its share of
+// the kernel time can be read from CUDA-event timings.  1: no scale / zero-point arithmetic, 2: no softmax
+// (probabilities = logits), 4: no P.V product, 8: no q.K product, 16: scales and zero-points are not fetched.  The results of such a build are meaningless.
+#ifndef KVQ_ABLATE
+#define KVQ_ABLATE 0
+#endif
+// resident CTAs per SM the packed-INT4 instantiations are compiled for (register cap = 65536 / (128 * this))
+#ifndef KVQ_INT4_MIN_CTAS
+#define KVQ_INT4_MIN_CTAS 4
+#endif
+
 namespace kvq {
 
 constexpr int kMmaWarps = 4;
@@ -54,6 +65,7 @@ struct MmaParams {
     AttnParams p;
     int nstage;
     int warp_smem_bytes;     // nstage * bytes of one stage: the private ring of one warp
+    int wide_rows;           // packed INT4 only: the payload maps are built over 128-byte rows of TWO tokens
 };
 
 // Bytes of one pipeline stage: K tile, V tile (each TS rows), then 2 (4 with zero-points)
@@ -68,7 +80,7 @@ __host__ __device__ constexpr int mma_stage_bytes(int fmt, bool asym, bool outl,
     const int payload = 2 * kTS * (fmt == KVQ_FMT_INT8 ? 128 : 64);
     const int scb = kTS * (128 / gs) * 2;
     const int raw = payload + (asym ? 4 : 2) * scb + (outl ? 512 : 0);
-    const int al = fmt == KVQ_FMT_INT8 ? 1024 : 512;
+    const int al = 1024;      // the 128-byte swizzle repeats every 1024 bytes
     return (raw + al - 1) / al * al;
 }
 
@@ -209,6 +221,15 @@ __device__ __forceinline__ void load_row_floats(uint32_t addr, float (&f)[NG]) {
     }
 }
 
+// Byte offset of 16-byte chunk `c` (0..3) of token row `r` (0..31) inside a packed-INT4 payload tile.
+// Narrow tile: 32 rows of 64 bytes, 64-byte swizzle.  Wide tile: the same 2 KB fetched as 16 rows of 128 bytes
+// (tokens 2i, 2i+1 side by side), 128-byte swizzle - twice the bytes per copy-engine request.  In both layouts the
+// eight rows of an 8x8 ldmatrix tile and the lanes of a row-wise 16-byte load fall into distinct banks.
+__device__ __forceinline__ uint32_t int4_tile_off(bool wide, int r, int c) {
+    return wide ? (uint32_t)((r >> 1) * 128 + (((((r & 1) << 2) | c) ^ ((r >> 1) & 7)) << 4))
+                : (uint32_t)(r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+}
+
 constexpr uint32_t kMagic = 0x64006400u;     // half2(1024, 1024)
 constexpr uint32_t kH1152 = 0x64806480u;     // half2(1152, 1152)
 constexpr uint32_t kH1032 = 0x64086408u;     // half2(1032, 1032)
@@ -230,6 +251,7 @@ __device__ __forceinline__ uint32_t nib_hi_to_h2(uint32_t w) {
 }
 template <bool ASYM>
 __device__ __forceinline__ uint32_t apply_scale(uint32_t c, uint32_t s2, uint32_t z2) {
+    if (KVQ_ABLATE & 1) return c;
     uint32_t v = hmul2_u(c, s2);
     if (ASYM) v = hadd2_u(v, z2);
     return v;
@@ -252,7 +274,7 @@ __device__ __forceinline__ uint32_t apply_scale(uint32_t c, uint32_t s2, uint32_
 // FAST is opt-in (KvqAttnArgs.fast_dequant).
 // GS = quantisation group size (16 / 32 / 64 / 128 channels), NG = 128 / GS scales per token.
 template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
-__global__ void __launch_bounds__(kMmaWarps * 32, (FMT == KVQ_FMT_INT4) ? 4 : 1)
+__global__ void __launch_bounds__(kMmaWarps * 32, (FMT == KVQ_FMT_INT4) ? KVQ_INT4_MIN_CTAS : 1)
 decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
     constexpr bool F16 = FMT == KVQ_FMT_FP16;                 // unquantised cache: no scales, no dequantisation
@@ -275,6 +297,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     const int h0 = kvh * p.n_rep + rc * kHeadsPerCta;
     const int nh = min(kHeadsPerCta, p.n_rep - rc * kHeadsPerCta);
     const int nstage = mp.nstage;
+    const bool wide = FMT == KVQ_FMT_INT4 && mp.wide_rows != 0;
 
     extern __shared__ unsigned char smem_dyn[];
     // stage buffers, 1024-byte aligned by hand: the TMA swizzle pattern is a function of the
@@ -436,13 +459,14 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
                 tma_load_4d(sb + kTS * RB + kTS * 128, &vmap, bar, 128, tok0, kvh, b);
             } else {
-                tma_load_4d(sb, &kmap, bar, 0, tok0, kvh, b);
-                tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
+                const int row0 = wide ? (tok0 >> 1) : tok0;
+                tma_load_4d(sb, &kmap, bar, 0, row0, kvh, b);
+                tma_load_4d(sb + kTS * RB, &vmap, bar, 0, row0, kvh, b);
             }
         }
         // scale-like tiles: TS tokens x NG fp16 = 4*NG chunks of 16 bytes per tile; 2 (or 4) tiles.
         // Only bytes of tokens inside the cache view are read; the rest is zero-filled.
-        if (!F16 && lane < 4 * NG) {
+        if (!F16 && lane < 4 * NG && !(KVQ_ABLATE & 16)) {
             const int tok = tok0 + lane * 8 / NG;                  // first token of this 16-byte chunk
             const int nbytes = max(0, min(16, (a.max_ctx - tok) * 2 * NG));
             const long long off = nbytes ? (long long)tok * NG : 0;
@@ -472,12 +496,15 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     // byte offsets (inside a 64-byte-row tile) of this lane's ldmatrix row for sub-tile `sub`, group pair `gp`:
     // matrix (lane>>3): bit 0 = token half, bit 1 = second 16-byte chunk (= group) of the pair
     uint32_t ldsm_off[2][2];
+    // row-wise 16-byte loads of the bit-faithful q.K product: chunk t of rows 16 sub + g and 16 sub + g + 8
+    uint32_t krow_off[2][2];
 #pragma unroll
     for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
         for (int gp = 0; gp < 2; ++gp) {
             const int lrow = 16 * sub + ((lane >> 3) & 1) * 8 + (lane & 7);
-            ldsm_off[sub][gp] = lrow * 64 + (((2 * gp + (lane >> 4)) ^ ((lrow >> 1) & 3)) << 4);
+            ldsm_off[sub][gp] = int4_tile_off(wide, lrow, 2 * gp + (lane >> 4));
+            krow_off[sub][gp] = int4_tile_off(wide, 16 * sub + g + 8 * gp, t);
         }
 
     bool failed = false;
@@ -507,7 +534,14 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 
         // ================= q.K : logits for 2 sub-tiles of 16 tokens =================
         float sacc[2][4];
-        if (FAST) {
+        constexpr bool NO_QK = (KVQ_ABLATE & 8) != 0, NO_PV = (KVQ_ABLATE & 4) != 0, NO_SOFTMAX = (KVQ_ABLATE & 2) != 0;
+        if (NO_QK) {
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
+        }
+        if (FAST && !NO_QK) {
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 float sg[NG][4];                                 // per-group integer dot products
@@ -556,7 +590,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 }
             }
         }
-        if (F16) {
+        if (F16 && !NO_QK) {
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
 #pragma unroll
@@ -573,7 +607,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             }
         }
 #pragma unroll
-        for (int sub = 0; sub < ((FAST || F16) ? 0 : 2); ++sub) {
+        for (int sub = 0; sub < ((FAST || F16 || NO_QK) ? 0 : 2); ++sub) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
             const int r0 = 16 * sub + g, r1 = r0 + 8;
@@ -632,8 +666,8 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 }
             } else {
                 uint32_t w[2][4];
-                lds128(kb + r0 * 64 + ((t ^ ((r0 >> 1) & 3)) << 4), w[0]);
-                lds128(kb + r1 * 64 + ((t ^ ((r1 >> 1) & 3)) << 4), w[1]);
+                lds128(kb + krow_off[sub][0], w[0]);
+                lds128(kb + krow_off[sub][1], w[1]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int hh = i >> 1;                           // channels 8i.. lie in half i / 2 of the slice
@@ -685,14 +719,15 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         mx[0] = fmaxf(fmaxf(sacc[0][0], sacc[0][2]), fmaxf(sacc[1][0], sacc[1][2]));
         mx[1] = fmaxf(fmaxf(sacc[0][1], sacc[0][3]), fmaxf(sacc[1][1], sacc[1][3]));
 #pragma unroll
-        for (int off = 4; off <= 16; off <<= 1) {
+        for (int off = 4; off <= (NO_SOFTMAX ? 0 : 16); off <<= 1) {
             mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], off));
             mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], off));
         }
         float corr[2], mneg[2];
         bool changed = false;
+        if (NO_SOFTMAX) { corr[0] = corr[1] = 1.f; mneg[0] = mneg[1] = 0.f; m_run[0] = m_run[1] = 0.f; }
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
+        for (int e = 0; e < (NO_SOFTMAX ? 0 : 2); ++e) {
             const float m_new = fmaxf(m_run[e], mx[e] * qk_scale);   // finite: the stage has a valid token
             changed |= (m_new != m_run[e]);
             corr[e] = fast_exp2(m_run[e] - m_new);                       // exp2(-inf) = 0 on the first stage
@@ -704,10 +739,15 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         uint32_t pb[2][2];                                           // P^T B fragments per sub-tile
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
-            float p0 = fast_exp2(fmaf(sacc[sub][0], qk_scale, mneg[0]));
-            float p1 = fast_exp2(fmaf(sacc[sub][1], qk_scale, mneg[1]));
-            float p2 = fast_exp2(fmaf(sacc[sub][2], qk_scale, mneg[0]));
-            float p3 = fast_exp2(fmaf(sacc[sub][3], qk_scale, mneg[1]));
+            float p0, p1, p2, p3;
+            if (NO_SOFTMAX) {
+                p0 = sacc[sub][0] * 1e-4f; p1 = sacc[sub][1] * 1e-4f; p2 = sacc[sub][2] * 1e-4f; p3 = sacc[sub][3] * 1e-4f;
+            } else {
+                p0 = fast_exp2(fmaf(sacc[sub][0], qk_scale, mneg[0]));
+                p1 = fast_exp2(fmaf(sacc[sub][1], qk_scale, mneg[1]));
+                p2 = fast_exp2(fmaf(sacc[sub][2], qk_scale, mneg[0]));
+                p3 = fast_exp2(fmaf(sacc[sub][3], qk_scale, mneg[1]));
+            }
             psum[0] += p0 + p2;
             psum[1] += p1 + p3;
             pf[sub][0] = p0; pf[sub][1] = p1; pf[sub][2] = p2; pf[sub][3] = p3;
@@ -745,7 +785,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         }
 
         // ================= P.V =================
-        if (FAST) {
+        if (FAST && !NO_PV) {
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 // fold the V scale of (token, group) into P: B fragments per group
@@ -796,7 +836,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 }
             }
         }
-        if (F16) {
+        if (F16 && !NO_PV) {
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t mxm = 0xffffffffu, mym = 0xffffffffu;
@@ -817,7 +857,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             }
         }
 #pragma unroll
-        for (int sub = 0; sub < ((FAST || F16) ? 0 : 2); ++sub) {
+        for (int sub = 0; sub < ((FAST || F16 || NO_PV) ? 0 : 2); ++sub) {
             // scales of tokens (2t, 2t+1) and (2t+8, 2t+9), paired per group
             uint32_t sx[NG], sy[NG], zx[NG], zy[NG];
             {
@@ -862,7 +902,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
                 for (int i = 0; i < 4; i += 2) {
                     uint32_t r[4];
-                    ldmatrix_x4_trans(vb + lrow * 64 + (((i + lchunk) ^ ((lrow >> 1) & 3)) << 4), r);
+                    ldmatrix_x4_trans(vb + ldsm_off[sub][i >> 1], r);
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const uint32_t X = r[2 * e], Y = r[2 * e + 1];
