@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define KVQ_ABI_VERSION 3
+#define KVQ_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define KVQ_API __attribute__((visibility("default")))
@@ -94,6 +94,10 @@ typedef struct KvqAppendArgs {
     const int16_t* outlier_idx;   /* [Hkv, n_out] sorted channel indices                  */
     int64_t write_pos;        /* first cache slot to write                                */
     const int32_t* write_pos_dev; /* if not NULL the slot is read on the device instead   */
+    int64_t max_slots;        /* token slots of the destination buffers (their capacity).  > 0: a host
+                                 write_pos with write_pos + T > max_slots is refused (KVQ_ELIMIT); with a
+                                 device-side position the kernel stores nothing for a token whose slot is
+                                 >= max_slots and raises bit 1 of kvq_debug_error_flag.  0: unchecked    */
     KvqAppendSide k, v;
     /* Optional rotary embedding fused in front of the quantizer (rope_cos == NULL: off).  K is rotated
      * before it is quantized, V is not; with q_src the query rows are rotated by the same launch and
@@ -151,11 +155,18 @@ typedef struct KvqAttnArgs {
     int32_t splits;           /* KV splits per (batch, kv head); 0 = library heuristic    */
     int32_t stages;           /* 0 = split kernel + combine; 1 = split kernel only; 2 = combine only
                                  (for profiling one stage; the workspace carries the partials) */
-    int32_t fast_dequant;     /* 0 (default): every kernel dequantises bit-faithfully, RN16(code*scale) per element.
-                                 1: packed INT4 with group size >= 32 on the tensor-core kernel applies the scales
-                                 outside the integer products (about 10 % faster; differs from the reference's
-                                 fp16-rounded code*scale by <= 2^-11 relative per element, which can exceed the
-                                 2e-3 / 1e-2 tolerance on data with unquantised x20 outlier channels).             */
+    int32_t fast_dequant;     /* packed INT4 with groups of >= 32 channels on the tensor-core kernel; ignored elsewhere.
+                                 0: library default = 1 (KVQ_INT4_EXACT=1 in the environment makes it 2).
+                                 1: factored scales - integer code products per group, scales applied outside, fp32
+                                    accumulation: the arithmetic of the reference's fused kernel, which multiplies fp32
+                                    codes by fp32 scales (src/kernels/triton_decode_attn_int8.py:239, 277).
+                                 2: bit-faithful - every element is RN16(RN16(code * scale) + zero_point) before the
+                                    product, the fp16 values of the reference's torch path
+                                    (src/engine/patch_model.py:355-362); about 1.6x the instructions.
+                                 Both meet |a-b| <= 2e-3 + 1e-2 |b| against the torch path on the benchmark
+                                 configurations; they differ from each other by the fp16 granularity of code * scale
+                                 (2^-11 of its magnitude per unit of probability), which shows only on data whose
+                                 dequantised magnitudes reach the tens (unquantised outlier channels).             */
     int32_t tail_tokens;      /* 0 or 1.  1: the LAST token of every row's context is not read by the split
                                  kernel (stage 1) but by the combine (stage 2), straight from the cache.  The
                                  split kernel then does not depend on the kernel that appends that token: a
@@ -273,6 +284,8 @@ typedef struct KvqKiviArgs {
     int64_t vs_stride_b, vs_stride_h;                   /* elements                      */
     int64_t write_pos;           /* append: first slot written                                */
     const int32_t* write_pos_dev;/* if not NULL the slot is read on the device                */
+    int64_t max_slots;           /* append: capacity of the destination buffers in tokens; same rule as
+                                    KvqAppendArgs.max_slots (bit 2 of kvq_debug_error_flag); 0: unchecked */
     void* k_out;                 /* dequantize: fp16 [B, H, T, D]                             */
     void* v_out;                 /* or NULL                                                   */
     int64_t out_stride_b, out_stride_h, out_stride_s;   /* elements, multiples of 8      */
@@ -361,15 +374,21 @@ typedef struct KvqDequantArgs {
 KVQ_API int kvq_dequantize(const KvqDequantArgs* args, kvq_stream_t stream);
 
 /*
- * Device-side error flag (synchronises the device): 0 = clean, 1 = a bounded wait on a
- * copy-completion barrier expired inside the tensor-core decode kernel (results of that
- * launch are invalid).  `reset` != 0 clears it.  Negative = KVQ_E*.  No reference counterpart.
+ * Device-side error flags (synchronises the device): 0 = clean.  Bit 0 (1): a bounded wait on a
+ * copy-completion barrier expired inside the tensor-core decode kernel (results of that launch
+ * are invalid).  Bit 1 (2): kvq_quantize_append met a device-side position at or beyond
+ * max_slots and skipped the stores of that token.  Bit 2 (4): the same for kvq_kivi_append.
+ * `reset` != 0 clears them.  Negative = KVQ_E*.  No reference counterpart.
  */
 KVQ_API int kvq_debug_error_flag(int reset);
 
 KVQ_API const char* kvq_strerror(int code);
 KVQ_API int  kvq_last_cuda_error(void);     /* cudaError_t of the last KVQ_ECUDA on this thread */
 KVQ_API int  kvq_abi_version(void);
+/* sizeof of an argument struct as this library was compiled, for binders that mirror the structs by hand
+ * (ctypes, cgo): 0 KvqAppendSide, 1 KvqAppendArgs, 2 KvqCacheSide, 3 KvqAttnArgs, 4 KvqCombineArgs,
+ * 5 KvqDequantArgs, 6 KvqKiviArgs, 7 KvqAbsmaxArgs, 8 KvqExchangeArgs; 0 for any other id.  No reference counterpart. */
+KVQ_API size_t kvq_struct_size(int which);
 
 #ifdef __cplusplus
 }

@@ -41,7 +41,7 @@ class KvqAppendArgs(C.Structure):
         ("B", _i32), ("Hkv", _i32), ("T", _i32), ("D", _i32), ("group_size", _i32),
         ("adaptive_margin", _f32), ("quantile", _f32),
         ("n_out", _i32), ("outlier_idx", _vp),
-        ("write_pos", _i64), ("write_pos_dev", _vp),
+        ("write_pos", _i64), ("write_pos_dev", _vp), ("max_slots", _i64),
         ("k", KvqAppendSide), ("v", KvqAppendSide),
         ("rope_cos", _vp), ("rope_sin", _vp), ("rope_stride_b", _i64), ("rope_stride_t", _i64),
         ("rotary_dim", _i32), ("Hq", _i32),
@@ -110,7 +110,7 @@ class KvqKiviArgs(C.Structure):
         ("k_src", _vp), ("v_src", _vp), ("src_stride_b", _i64), ("src_stride_h", _i64), ("src_stride_t", _i64),
         ("k_payload", _vp), ("v_payload", _vp), ("pay_stride_b", _i64), ("pay_stride_h", _i64), ("pay_stride_s", _i64),
         ("k_scale", _vp), ("k_zp", _vp), ("v_scale", _vp), ("v_zp", _vp), ("vs_stride_b", _i64), ("vs_stride_h", _i64),
-        ("write_pos", _i64), ("write_pos_dev", _vp),
+        ("write_pos", _i64), ("write_pos_dev", _vp), ("max_slots", _i64),
         ("k_out", _vp), ("v_out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64), ("out_stride_s", _i64),
         ("v_scale_h", _vp), ("v_zp_h", _vp),
     ]
@@ -151,7 +151,13 @@ EXPORTS = (
     ("kvq_strerror", C.c_char_p, (C.c_int,)),
     ("kvq_last_cuda_error", C.c_int, ()),
     ("kvq_abi_version", C.c_int, ()),
+    ("kvq_struct_size", C.c_size_t, (C.c_int,)),
 )
+
+ABI_VERSION = 4
+# ids of kvq_struct_size, in the order of include/kvq.h
+STRUCTS = (KvqAppendSide, KvqAppendArgs, KvqCacheSide, KvqAttnArgs, KvqCombineArgs, KvqDequantArgs, KvqKiviArgs,
+           KvqAbsmaxArgs, KvqExchangeArgs)
 
 _LIB = None
 
@@ -184,6 +190,13 @@ def load():
         fn = getattr(lib, name)
         fn.restype = restype
         fn.argtypes = list(argtypes)
+    if lib.kvq_abi_version() != ABI_VERSION:
+        raise ImportError(f"{path} has ABI version {lib.kvq_abi_version()}, this package binds version {ABI_VERSION}: "
+                          "rebuild it with `python -m llm_kvcache_quantization_b200.build --force`")
+    for i, st in enumerate(STRUCTS):
+        if lib.kvq_struct_size(i) != C.sizeof(st):
+            raise ImportError(f"{path}: struct {st.__name__} is {lib.kvq_struct_size(i)} bytes in the library, "
+                              f"{C.sizeof(st)} in the binding")
     _LIB = lib
     return lib
 

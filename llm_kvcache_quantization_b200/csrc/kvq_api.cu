@@ -48,3 +48,18 @@ extern "C" const char* kvq_strerror(int code) {
 
 extern "C" int kvq_last_cuda_error(void) { return kvq::last_cuda_error_ref(); }
 extern "C" int kvq_abi_version(void) { return KVQ_ABI_VERSION; }
+
+extern "C" size_t kvq_struct_size(int which) {
+    switch (which) {
+        case 0: return sizeof(KvqAppendSide);
+        case 1: return sizeof(KvqAppendArgs);
+        case 2: return sizeof(KvqCacheSide);
+        case 3: return sizeof(KvqAttnArgs);
+        case 4: return sizeof(KvqCombineArgs);
+        case 5: return sizeof(KvqDequantArgs);
+        case 6: return sizeof(KvqKiviArgs);
+        case 7: return sizeof(KvqAbsmaxArgs);
+        case 8: return sizeof(KvqExchangeArgs);
+        default: return 0;
+    }
+}

@@ -7,6 +7,7 @@
 #include <stdlib.h>
 
 #include "kvq_decode_generic.cuh"
+#include "kvq_decode_int4.cuh"
 #include "kvq_decode_mma.cuh"
 #include "kvq_internal.h"
 
@@ -408,19 +409,43 @@ static EncodeTiledFn encode_tiled_fn() {
 // caller guarantees tokens are contiguous, pay_stride_s == row_bytes / 2): the copy engine then moves 128-byte
 // segments instead of 64-byte ones, which is what the memory system is built for.
 static int make_payload_map(CUtensorMap* map, const KvqCacheSide& sd, int row_bytes, int s_extent, int hkv, int b,
-                            bool pair_rows = false) {
+                            bool pair_rows = false, int box_tokens = kTS) {
     const int box_bytes = row_bytes > 128 ? 128 : row_bytes;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return KVQ_EUNSUPPORTED;
     cuuint64_t dims[4] = {(cuuint64_t)row_bytes, (cuuint64_t)s_extent, (cuuint64_t)hkv, (cuuint64_t)b};
     cuuint64_t strides[3] = {(cuuint64_t)(pair_rows ? 2 * sd.pay_stride_s : sd.pay_stride_s), (cuuint64_t)sd.pay_stride_h,
                              (cuuint64_t)sd.pay_stride_b};
-    cuuint32_t box[4] = {(cuuint32_t)box_bytes, (cuuint32_t)(pair_rows ? kTS / 2 : kTS), 1, 1};
+    cuuint32_t box[4] = {(cuuint32_t)box_bytes, (cuuint32_t)(pair_rows ? box_tokens / 2 : box_tokens), 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(sd.payload), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE,
                      box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? KVQ_OK : KVQ_EUNSUPPORTED;
+}
+
+
+// fp16 scales / zero-points [B, Hkv, S, NG] (tokens contiguous) as a 3-D tensor of 2- / 4- / 8-byte elements, one
+// (two for NG = 8) per token; box = `box_tokens` tokens.  Tokens at or beyond `s_extent` are zero-filled.
+static int make_scale_map(CUtensorMap* map, const void* base, long long stride_h, long long stride_b, int ng, int s_extent,
+                          int hkv, int b, int box_tokens) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return KVQ_EUNSUPPORTED;
+    const int tok_bytes = ng * 2;
+    const int elem = tok_bytes > 8 ? 8 : tok_bytes;
+    const int ept = tok_bytes / elem;
+    const CUtensorMapDataType ty = elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                 : elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT64;
+    const cuuint64_t row_bytes = (((cuuint64_t)s_extent * tok_bytes) + 15) & ~(cuuint64_t)15;
+    cuuint64_t dims[3] = {(cuuint64_t)s_extent * ept, (cuuint64_t)hkv, (cuuint64_t)b};
+    // a dimension of extent 1 never advances; give it any legal stride
+    cuuint64_t strides[2] = {hkv > 1 ? (cuuint64_t)stride_h * 2 : row_bytes,
+                             b > 1 ? (cuuint64_t)stride_b * 2 : row_bytes * (cuuint64_t)hkv};
+    cuuint32_t box[3] = {(cuuint32_t)(box_tokens * ept), 1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, ty, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? KVQ_OK : KVQ_EUNSUPPORTED;
 }
 
@@ -502,11 +527,8 @@ static const MmaConfig& mma_config(MmaTag<FMT, ASYM, OUTL, FAST, GS>) {
     return cfg;
 }
 
-// Bit-faithful dequantisation is the default everywhere.  Packed INT4 with groups of >= 32 channels
-// takes the factored-scale kernel only when the caller opts in (`fast_dequant`).
-static bool use_fast(const AttnParams& p) {
-    return p.a.format == KVQ_FMT_INT4 && p.a.fast_dequant && p.a.group_size >= 32;
-}
+static bool i4_use_fast(const KvqAttnArgs& a);
+static bool use_fast(const AttnParams& p) { return p.a.format == KVQ_FMT_INT4 && i4_use_fast(p.a); }
 
 // Calls f(MmaTag<...>{}) for the instantiation that serves these arguments.
 template <class F>
@@ -544,12 +566,132 @@ static const MmaConfig* mma_config_for(const AttnParams& p, bool asym) {
     return out;
 }
 
+
 static bool wide_rows_possible(const KvqAttnArgs& a) {
     return a.format == KVQ_FMT_INT4 && a.k.pay_stride_s == 64 && a.v.pay_stride_s == 64 && a.max_ctx >= 2 &&
            !getenv("KVQ_INT4_NARROW_ROWS");
 }
 static bool wide_rows_ok(const KvqAttnArgs& a) {
     return wide_rows_possible(a) && ((a.max_ctx & 1) == 0 || a.tail_tokens == 1);
+}
+
+// ---------------------------------------------------------------------------
+// Packed-INT4 kernel (kvq_decode_int4.cuh): configuration, dispatch, launch
+// ---------------------------------------------------------------------------
+template <bool ASYM, int NOUT, bool FAST, int GS>
+struct I4Tag {};
+
+static int i4_stages_from_env(int dflt) {
+    const char* e = getenv("KVQ_I4_STAGES");
+    if (!e) return dflt;
+    int v = atoi(e);
+    return (v >= 2 && v <= kI4MaxStages) ? v : dflt;
+}
+
+template <bool ASYM, int NOUT, bool FAST, int GS>
+static const MmaConfig& i4_config(I4Tag<ASYM, NOUT, FAST, GS>) {
+    static MmaConfig cfg = [] {
+        MmaConfig c;
+        c.nstage = i4_stages_from_env(2);
+        c.stage_bytes = int4_stage_bytes(ASYM, NOUT > 0, GS);
+        c.dyn_smem = (size_t)c.nstage * c.stage_bytes + 1024;
+        c.ctas_per_sm = 1;
+        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_int4_kernel<ASYM, NOUT, FAST, GS>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.dyn_smem));
+        if (c.rc == KVQ_OK) {
+            int n = 0;
+            c.rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &n, decode_split_int4_kernel<ASYM, NOUT, FAST, GS>, kMmaWarps * 32, c.dyn_smem));
+            if (n > 0) c.ctas_per_sm = n;
+        }
+        return c;
+    }();
+    return cfg;
+}
+
+// The factored-scale arithmetic (see kvq_decode_int4.cuh) serves groups of >= 32 channels unless the caller asks for
+// the bit-faithful one (fast_dequant = 0 in the C ABI means "library default"; 2 = bit-faithful).
+static bool i4_use_fast(const KvqAttnArgs& a) {
+    if (a.group_size < 32) return false;
+    if (a.fast_dequant == 2) return false;
+    if (a.fast_dequant == 1) return true;
+    const char* e = getenv("KVQ_INT4_EXACT");
+    return !(e && e[0] == '1');
+}
+
+template <class F>
+static int i4_dispatch(const AttnParams& p, bool asym, F&& f) {
+    const bool fast = i4_use_fast(p.a);
+    const int gs = p.a.group_size, nout = p.a.n_out;
+#define KVQ_I4_CASE(ASYM_, NOUT_, FAST_, GS_)                                              \
+    if (asym == ASYM_ && nout == NOUT_ && fast == FAST_ && gs == GS_) return f(I4Tag<ASYM_, NOUT_, FAST_, GS_>{});
+#define KVQ_I4_GS(ASYM_, FAST_) KVQ_I4_CASE(ASYM_, 0, FAST_, 32) KVQ_I4_CASE(ASYM_, 0, FAST_, 64) KVQ_I4_CASE(ASYM_, 0, FAST_, 128)
+#define KVQ_I4_OUT(FAST_) KVQ_I4_CASE(false, 1, FAST_, 32) KVQ_I4_CASE(false, 2, FAST_, 32) KVQ_I4_CASE(false, 3, FAST_, 32) KVQ_I4_CASE(false, 4, FAST_, 32)
+    KVQ_I4_GS(false, true)
+    KVQ_I4_GS(true, true)
+    KVQ_I4_OUT(true)
+    KVQ_I4_GS(false, false)
+    KVQ_I4_GS(true, false)
+    KVQ_I4_CASE(false, 0, false, 16)
+    KVQ_I4_CASE(true, 0, false, 16)
+    KVQ_I4_OUT(false)
+#undef KVQ_I4_OUT
+#undef KVQ_I4_GS
+#undef KVQ_I4_CASE
+    return KVQ_EUNSUPPORTED;
+}
+
+static const MmaConfig* i4_config_for(const AttnParams& p, bool asym) {
+    const MmaConfig* out = nullptr;
+    i4_dispatch(p, asym, [&](auto tag) { out = &i4_config(tag); return KVQ_OK; });
+    return out;
+}
+
+template <bool ASYM, int NOUT, bool FAST, int GS>
+static int launch_i4(I4Tag<ASYM, NOUT, FAST, GS> tag, const AttnParams& p, cudaStream_t st) {
+    const MmaConfig& cfg = i4_config(tag);
+    if (cfg.rc) return cfg.rc;
+    Int4Params ip;
+    ip.p = p;
+    ip.nstage = cfg.nstage;
+    // Pairs of tokens travel as 128-byte rows when the tokens of a (b, h) row are contiguous.  The pair view covers
+    // floor(max_ctx / 2) pairs, so that nothing beyond token max_ctx - 1 is ever read: with an odd max_ctx the last
+    // token must belong to the combine stage (tail_tokens), which kvq_decode_attn arranges for whole calls; a
+    // split-only call without it keeps the 64-byte rows.
+    ip.wide_rows = wide_rows_ok(p.a);
+    {
+        static const int pf = [] { const char* e = getenv("KVQ_I4_PREFETCH"); int v = e ? atoi(e) : 4; return v < 0 ? 0 : (v > 64 ? 64 : v); }();
+        static const int ahead = [] { const char* e = getenv("KVQ_I4_L2_AHEAD"); int v = e ? atoi(e) : 0; return v < 0 ? 0 : (v > 16 ? 16 : v); }();
+        ip.prefetch_stages = pf;
+        ip.l2_ahead = ahead;
+    }
+    const KvqAttnArgs& a = p.a;
+    const int ext = ip.wide_rows ? a.max_ctx / 2 : a.max_ctx;
+    const int ng = 128 / GS;
+    CUtensorMap kmap, vmap, ksmap, vsmap, kzmap, vzmap;
+    int rc;
+    if ((rc = make_payload_map(&kmap, a.k, ip.wide_rows ? 128 : 64, ext, a.Hkv, a.B, ip.wide_rows != 0, kI4Tok))) return rc;
+    if ((rc = make_payload_map(&vmap, a.v, ip.wide_rows ? 128 : 64, ext, a.Hkv, a.B, ip.wide_rows != 0, kI4Tok))) return rc;
+    if ((rc = make_scale_map(&ksmap, a.k.scale, a.k.sc_stride_h, a.k.sc_stride_b, ng, a.max_ctx, a.Hkv, a.B, kI4Tok))) return rc;
+    if ((rc = make_scale_map(&vsmap, a.v.scale, a.v.sc_stride_h, a.v.sc_stride_b, ng, a.max_ctx, a.Hkv, a.B, kI4Tok))) return rc;
+    if (ASYM) {
+        if ((rc = make_scale_map(&kzmap, a.k.zp, a.k.sc_stride_h, a.k.sc_stride_b, ng, a.max_ctx, a.Hkv, a.B, kI4Tok))) return rc;
+        if ((rc = make_scale_map(&vzmap, a.v.zp, a.v.sc_stride_h, a.v.sc_stride_b, ng, a.max_ctx, a.Hkv, a.B, kI4Tok))) return rc;
+    } else {
+        kzmap = ksmap;
+        vzmap = vsmap;
+    }
+    dim3 grid(p.splits, a.Hkv * p.rep_chunks, a.B);
+    return launch_pdl(decode_split_int4_kernel<ASYM, NOUT, FAST, GS>, grid, dim3(kMmaWarps * 32), cfg.dyn_smem, st, ip,
+                      kmap, vmap, ksmap, vsmap, kzmap, vzmap);
+}
+
+static bool i4_eligible(const AttnParams& p, bool asym) {
+    return p.a.format == KVQ_FMT_INT4 && !getenv("KVQ_INT4_OLD_KERNEL") && i4_config_for(p, asym) != nullptr;
+}
+
+static int dispatch_i4(const AttnParams& p, bool asym, cudaStream_t st) {
+    return i4_dispatch(p, asym, [&](auto tag) { return launch_i4(tag, p, st); });
 }
 
 template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
@@ -579,6 +721,7 @@ static int launch_mma(MmaTag<FMT, ASYM, OUTL, FAST, GS> tag, const AttnParams& p
 }
 
 static int dispatch_mma(const AttnParams& p, bool asym, cudaStream_t st) {
+    if (i4_eligible(p, asym)) return dispatch_i4(p, asym, st);
     return mma_dispatch(p, asym, [&](auto tag) { return launch_mma(tag, p, st); });
 }
 
@@ -617,7 +760,7 @@ static int pick_splits_internal(const AttnParams& p, bool asym, bool mma) {
     const long long rows = (long long)p.a.B * p.a.Hkv * p.rep_chunks;
     const int sms = device_sm_count();
     if (mma) {
-        const MmaConfig* cfg = mma_config_for(p, asym);
+        const MmaConfig* cfg = i4_eligible(p, asym) ? i4_config_for(p, asym) : mma_config_for(p, asym);
         if (!cfg) return 1;
         return pick_splits_waves(rows, p.a.max_ctx, sms * cfg->ctas_per_sm, kMmaWarps * kTS);
     }
@@ -834,7 +977,9 @@ extern "C" int kvq_debug_error_flag(int reset) {
         int z = 0;
         if (cudaMemcpyToSymbol(kvq::g_kvq_error_flag, &z, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;
     }
-    return v;
+    const int qf = kvq::quantize_error_flag(reset), kf = kvq::kivi_error_flag(reset);
+    if (qf < 0 || kf < 0) return KVQ_ECUDA;
+    return (v ? 1 : 0) | (qf ? 2 : 0) | (kf ? 4 : 0);
 }
 
 extern "C" int kvq_lse_combine(const KvqCombineArgs* args, kvq_stream_t stream) {

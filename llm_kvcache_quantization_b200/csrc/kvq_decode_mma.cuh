@@ -100,6 +100,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `hint_ns` before it reports "not yet"
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
     for (int i = 0; i < kWaitLimit; ++i)
         if (mbar_try_wait(bar, parity)) return true;

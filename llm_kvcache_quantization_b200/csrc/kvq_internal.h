@@ -20,6 +20,11 @@ inline int check_launch() { return check_cuda(cudaGetLastError()); }
 
 int device_sm_count();
 
+// Device-side error flags of the other translation units (each owns its __device__ word): value, optionally
+// cleared; negative = KVQ_ECUDA.  kvq_debug_error_flag combines them.
+int quantize_error_flag(int reset);
+int kivi_error_flag(int reset);
+
 // Launch with programmatic dependent launch: the grid may start while the previous kernel in the
 // stream is still running; the kernel itself calls pdl_wait() before it touches anything that
 // kernel writes.  KVQ_NO_PDL=1 falls back to ordinary stream order.

@@ -23,6 +23,9 @@
 
 namespace kvq {
 
+__device__ int g_kivi_error_flag = 0;   // 1: an append met a slot at or beyond max_slots
+
+
 // monotone float <-> int mapping so that integer atomicMin / atomicMax order floats
 __device__ __forceinline__ int f2ord(float f) {
     const int b = __float_as_int(f);
@@ -105,7 +108,13 @@ __global__ void __launch_bounds__(256) kivi_quantize_kernel(const KiviParams p) 
     const int t = (int)(r % a.T); r /= a.T;
     const int h = (int)(r % a.H);
     const int b = (int)(r / a.H);
-    const long long pos = (a.write_pos_dev ? (long long)(*a.write_pos_dev) : a.write_pos) + t;
+    long long pos = (a.write_pos_dev ? (long long)(*a.write_pos_dev) : a.write_pos) + t;
+    // a slot beyond the destination buffers: store nothing for this token, raise the flag, keep the lane for the shuffles
+    const bool in_range = a.max_slots <= 0 || (pos >= 0 && pos < a.max_slots);
+    if (!in_range) {
+        if (live) g_kivi_error_flag = 1;
+        pos = 0;
+    }
     const __half* src = (const __half*)(side ? a.v_src : a.k_src) + (long long)b * a.src_stride_b +
                         (long long)h * a.src_stride_h + (long long)t * a.src_stride_t + 8 * c;
     const uint4 raw = *(const uint4*)src;
@@ -139,7 +148,7 @@ __global__ void __launch_bounds__(256) kivi_quantize_kernel(const KiviParams p) 
         kivi_scale_zp(mn, mx, p.qmin, p.qspan, s, zp);
 #pragma unroll
         for (int j = 0; j < 8; ++j) code[j] = kivi_code(x[j], s, zp, lo, hi);
-        if (live && c == 0) {
+        if (live && in_range && c == 0) {
             const long long o = (long long)b * a.vs_stride_b + (long long)h * a.vs_stride_h + pos;
             a.v_scale[o] = s;
             a.v_zp[o] = zp;
@@ -149,7 +158,7 @@ __global__ void __launch_bounds__(256) kivi_quantize_kernel(const KiviParams p) 
             }
         }
     }
-    if (!live) return;
+    if (!live || !in_range) return;
     char* row = (char*)(side ? a.v_payload : a.k_payload) + (long long)b * a.pay_stride_b + (long long)h * a.pay_stride_h +
                 pos * a.pay_stride_s;
     if (BITS == 8) {
@@ -235,6 +244,16 @@ static int kivi_check(const KvqKiviArgs& a, KiviParams& p) {
     return KVQ_OK;
 }
 
+int kivi_error_flag(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_kivi_error_flag, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;
+    if (reset && v) {
+        const int z = 0;
+        if (cudaMemcpyToSymbol(g_kivi_error_flag, &z, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;
+    }
+    return v;
+}
+
 }  // namespace kvq
 
 extern "C" int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream) {
@@ -245,7 +264,8 @@ extern "C" int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream) {
     if (rc) return rc;
     const KvqKiviArgs& a = *args;
     if (a.B == 0 || a.T == 0) return KVQ_OK;
-    if (!a.k_src || !a.v_src || a.write_pos < 0) return KVQ_EINVAL;
+    if (!a.k_src || !a.v_src || a.write_pos < 0 || a.max_slots < 0) return KVQ_EINVAL;
+    if (a.max_slots > 0 && !a.write_pos_dev && a.write_pos + a.T > a.max_slots) return KVQ_ELIMIT;
     if ((a.v_scale_h != nullptr) != (a.v_zp_h != nullptr)) return KVQ_EINVAL;
     if (((uintptr_t)a.k_src & 15) || ((uintptr_t)a.v_src & 15) || (a.src_stride_b & 7) || (a.src_stride_h & 7) ||
         (a.src_stride_t & 7))

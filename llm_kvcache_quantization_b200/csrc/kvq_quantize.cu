@@ -28,6 +28,9 @@
 
 namespace kvq {
 
+__device__ int g_quantize_error_flag = 0;   // 1: an append met a slot at or beyond max_slots
+
+
 constexpr int kMaxGroup = 256;
 
 struct QuantParams {
@@ -134,6 +137,13 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
     const int b = (int)(r / a.Hkv);
     long long pos = a.write_pos_dev ? (long long)(*a.write_pos_dev) : a.write_pos;
     pos += t;
+    // a slot beyond the destination buffers (a graph replayed once too often, a stale device counter): nothing of
+    // this token is stored, the flag is raised, and the lane keeps running so that group shuffles stay complete
+    const bool in_range = a.max_slots <= 0 || (pos >= 0 && pos < a.max_slots);
+    if (!in_range) {
+        g_quantize_error_flag = 1;
+        pos = 0;
+    }
 
     const __half* src = (const __half*)sd.src + b * sd.src_stride_b + h * sd.src_stride_h +
                         t * sd.src_stride_t + cb;
@@ -145,6 +155,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
 
     if (FMT == KVQ_FMT_FP16) {
         __half* dst = (__half*)pay + cb;
+        if (!in_range) return;
         if (rope) {
             for (int i = 0; i < cw; ++i) dst[i] = rope_one(src - cb, rcos, rsin, a.rotary_dim, cb + i);
         } else if (CH) {
@@ -199,7 +210,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
 
     // outlier channels of this head that fall in this work item: copy raw, treat as 0
     const int16_t* oidx = a.n_out ? a.outlier_idx + h * a.n_out : nullptr;
-    if (oidx && sd.side) {
+    if (oidx && sd.side && in_range) {
         __half* side = (__half*)sd.side + b * sd.side_stride_b + h * sd.side_stride_h + pos * sd.side_stride_s;
         for (int j = 0; j < a.n_out; ++j) {
             int ch = oidx[j] - cb;
@@ -315,6 +326,7 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
     // stored (kernel-facing) scale is fp16; one lane of the group writes it
     __half s16 = __float2half_rn(s32);
     if (FMT == KVQ_FMT_INT8 && POLICY != KVQ_SCALE_ASYM_MINMAX) s32 = h2f(s16);  // INT8 divides by the fp16 scale
+    if (!in_range) return;                               // every shuffle of the group is behind us
     if (LPG == 1 || (c % LPG) == 0) {
         ((__half*)sd.scale)[sc_off] = s16;
         if (sd.scale_f32) sd.scale_f32[sc_off] = s32;
@@ -417,6 +429,16 @@ static bool side_ok(const KvqAppendSide& s, const KvqAppendArgs& a) {
     return true;
 }
 
+int quantize_error_flag(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_quantize_error_flag, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;
+    if (reset && v) {
+        const int z = 0;
+        if (cudaMemcpyToSymbol(g_quantize_error_flag, &z, sizeof(int)) != cudaSuccess) return KVQ_ECUDA;
+    }
+    return v;
+}
+
 }  // namespace kvq
 
 extern "C" int kvq_quantize_append(const KvqAppendArgs* args, kvq_stream_t stream) {
@@ -431,7 +453,8 @@ extern "C" int kvq_quantize_append(const KvqAppendArgs* args, kvq_stream_t strea
     if (a.policy < 0 || a.policy > 2) return KVQ_EINVAL;
     if (a.n_out < 0 || (a.n_out > 0 && !a.outlier_idx)) return KVQ_EINVAL;
     if (a.n_out > 0 && a.policy == KVQ_SCALE_ASYM_MINMAX) return KVQ_EUNSUPPORTED;
-    if (a.write_pos < 0) return KVQ_EINVAL;
+    if (a.write_pos < 0 || a.max_slots < 0) return KVQ_EINVAL;
+    if (a.max_slots > 0 && !a.write_pos_dev && a.write_pos + a.T > a.max_slots) return KVQ_ELIMIT;
     QuantParams p;
     p.a = a;
     p.a.group_size = gs;

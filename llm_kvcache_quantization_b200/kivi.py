@@ -117,6 +117,7 @@ class KIVIStyleKVCache:
         a.B, a.H, a.T, a.D = kc.shape[0], kc.shape[1], T, D
         a.k_payload, a.v_payload = kc.data_ptr(), vc.data_ptr()
         a.pay_stride_b, a.pay_stride_h, a.pay_stride_s = kc.stride(0), kc.stride(1), kc.stride(2)
+        a.max_slots = min(kc.shape[2], vc.shape[2], self._v_scale[layer_id].shape[-1])   # appends beyond it store nothing
         a.k_scale, a.k_zp = self._k_scale[layer_id].data_ptr(), self._k_zp[layer_id].data_ptr()
         vs = self._v_scale[layer_id]
         a.v_scale, a.v_zp = vs.data_ptr(), self._v_zp[layer_id].data_ptr()

@@ -137,13 +137,16 @@ def quantize_append(fmt: int, policy: int, k_new: torch.Tensor, v_new: torch.Ten
             raise ValueError("outlier_idx must be a contiguous int16 [Hkv, n_out] tensor")
         a.n_out = outlier_idx.shape[1]
         a.outlier_idx = outlier_idx.data_ptr()
+    # the kernel itself refuses slots at or beyond the smallest destination buffer (a device-side position that ran
+    # past the capacity stores nothing and raises bit 1 of kvq_debug_error_flag)
+    cap = k_payload.shape[2] if v_payload is None or v_new is None else min(k_payload.shape[2], v_payload.shape[2])
+    a.max_slots = cap
     if isinstance(write_pos, torch.Tensor):
         if write_pos.dtype != torch.int32 or not write_pos.is_cuda:
             raise ValueError("device write_pos must be an int32 CUDA tensor")
         a.write_pos_dev = write_pos.data_ptr()
     else:
         a.write_pos = int(write_pos)
-        cap = k_payload.shape[2]
         if a.write_pos < 0 or a.write_pos + T > cap:
             raise ValueError(f"append of {T} tokens at {a.write_pos} exceeds capacity {cap}")
     a.k = _append_side(k_new, k_payload, k_scale, k_zp, k_scale_f32, k_side, k_static, k_rescue_thr)
@@ -251,9 +254,13 @@ def decode_attn(fmt: int, q: torch.Tensor, k_payload: torch.Tensor, v_payload: t
         a.inv_tau = inv_tau.data_ptr()
     a.sm_scale = float(sm_scale)
     a.stages = int(stages)
-    if fast_dequant is None:       # KVQ_INT4_FAST=1: factored-scale INT4 path instead of bit-faithful dequantisation
-        fast_dequant = os.environ.get("KVQ_INT4_FAST", "0") == "1"
-    a.fast_dequant = 1 if fast_dequant else 0
+    # packed INT4, groups of >= 32 channels: 0 = library default (factored scales), 1 = factored scales, 2 = bit-faithful
+    # fp16 dequantisation; KVQ_INT4_FAST=1 / 0 picks one for calls that do not say
+    if fast_dequant is None:
+        env = os.environ.get("KVQ_INT4_FAST")
+        a.fast_dequant = 0 if env is None else (1 if env == "1" else 2)
+    else:
+        a.fast_dequant = 1 if fast_dequant else 2
     if q_chan_scale is not None:       # fp32 [B, Hkv, D]: per-channel factor applied to the query inside the kernel
         if q_chan_scale.dtype != torch.float32 or tuple(q_chan_scale.shape) != (B, Hkv, D) or q_chan_scale.stride(-1) != 1:
             raise ValueError("q_chan_scale must be an fp32 [B, Hkv, D] tensor, contiguous in head_dim")

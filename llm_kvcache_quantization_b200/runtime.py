@@ -146,6 +146,8 @@ class GraphedKVStackStep:
     def capture(self) -> None:
         """Warm up once eagerly on a side stream (first-use set-up, workspace growth), rewind the
         device counters, then capture the step."""
+        if self._len + 1 > self.capacity:              # the warm-up below appends at slot `_len`
+            raise ValueError(f"cache capacity {self.capacity} exhausted: nothing left to capture a step into")
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
@@ -295,6 +297,8 @@ class GraphedModelStep:
 
     def capture(self, first_token: torch.Tensor) -> None:
         """`first_token` [B,1]: the token the prompt's last logits chose."""
+        if self._len + 1 > self.capacity:              # the warm-up below appends at slot `_len`
+            raise ValueError(f"cache capacity {self.capacity} exhausted: nothing left to capture a step into")
         self.cache.use_device_positions(self.pos, self.ctx, self.capacity)
         keep = first_token.to(self.device).clone()
         with torch.no_grad():

@@ -31,7 +31,7 @@ def test_header_symbols_all_exported(lib):
 
 
 def test_abi_version_and_strerror(lib):
-    assert lib.kvq_abi_version() == 3
+    assert lib.kvq_abi_version() == 4 == _lib.ABI_VERSION
     assert lib.kvq_strerror(0) == b"ok"
     assert b"invalid" in lib.kvq_strerror(-1)
 
@@ -56,9 +56,30 @@ def test_struct_sizes_match_header(lib):
     assert ctypes.sizeof(_lib.KvqCacheSide) == 13 * 8
     assert ctypes.sizeof(_lib.KvqCombineArgs) == 4 * 4 + 10 * 8
     assert ctypes.sizeof(_lib.KvqDequantArgs) == 8 * 4 + 8 + 2 * 13 * 8 + 5 * 8
-    assert ctypes.sizeof(_lib.KvqKiviArgs) == 6 * 4 + 25 * 8
+    assert ctypes.sizeof(_lib.KvqKiviArgs) == 6 * 4 + 26 * 8
     assert ctypes.sizeof(_lib.KvqAbsmaxArgs) == 5 * 4 + 4 + 8 + 3 * 8 + 8
     assert ctypes.sizeof(_lib.KvqExchangeArgs) == 4 * 4 + 2 * 8 + 2 * 4 + 8 + 2 * 4 + 7 * 8
+
+
+def test_binding_structs_match_the_compiled_header(lib):
+    for i, st in enumerate(_lib.STRUCTS):
+        assert lib.kvq_struct_size(i) == ctypes.sizeof(st), st.__name__
+    assert lib.kvq_struct_size(len(_lib.STRUCTS)) == 0
+
+
+def test_append_beyond_max_slots_is_refused_on_the_host(lib):
+    a = _lib.KvqAppendArgs()
+    a.format, a.policy = _lib.FMT_INT8, _lib.SCALE_DYNAMIC_PCT
+    a.B, a.Hkv, a.T, a.D, a.group_size = 1, 2, 4, 128, 32
+    a.write_pos, a.max_slots = 30, 32             # slots 30..33 of a 32-slot cache
+    assert lib.kvq_quantize_append(ctypes.byref(a), None) == _lib.KVQ_ELIMIT
+    a.max_slots = -1
+    assert lib.kvq_quantize_append(ctypes.byref(a), None) == _lib.KVQ_EINVAL
+    k = _lib.KvqKiviArgs()
+    k.bits, k.B, k.H, k.T, k.D = 4, 1, 2, 4, 128
+    k.k_src = k.v_src = 16
+    k.write_pos, k.max_slots = 30, 32
+    assert lib.kvq_kivi_append(ctypes.byref(k), None) in (_lib.KVQ_ELIMIT, _lib.KVQ_EINVAL)
 
 
 def test_exchange_buffer_layout(lib):
