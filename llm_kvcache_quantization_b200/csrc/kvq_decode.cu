@@ -501,25 +501,23 @@ static int stages_from_env(int dflt) {
     return (v >= 2 && v <= 8) ? v : dflt;
 }
 
-template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
+template <int FMT, bool ASYM, bool OUTL, int GS>
 struct MmaTag {};
 
-template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
-static const MmaConfig& mma_config(MmaTag<FMT, ASYM, OUTL, FAST, GS>) {
+template <int FMT, bool ASYM, bool OUTL, int GS>
+static const MmaConfig& mma_config(MmaTag<FMT, ASYM, OUTL, GS>) {
     static MmaConfig cfg = [] {
         MmaConfig c;
-        // measured on B200: int8 and the outlier variants run best with 2 stages (one more resident
-        // CTA per SM), packed int4 without outliers with 3
-        c.nstage = stages_from_env((FMT == KVQ_FMT_INT4 && !OUTL) ? 3 : 2);
+        c.nstage = stages_from_env(2);       // measured on B200: 2 stages (one more resident CTA per SM) beat 3
         c.stage_bytes = mma_stage_bytes(FMT, ASYM, OUTL, GS);
         c.dyn_smem = (size_t)kMmaWarps * c.nstage * c.stage_bytes + 1024;
         c.ctas_per_sm = 1;
-        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST, GS>,
+        c.rc = check_cuda(cudaFuncSetAttribute(decode_split_mma_kernel<FMT, ASYM, OUTL, GS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.dyn_smem));
         if (c.rc == KVQ_OK) {
             int n = 0;
             c.rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-                &n, decode_split_mma_kernel<FMT, ASYM, OUTL, FAST, GS>, kMmaWarps * 32, c.dyn_smem));
+                &n, decode_split_mma_kernel<FMT, ASYM, OUTL, GS>, kMmaWarps * 32, c.dyn_smem));
             if (n > 0) c.ctas_per_sm = n;
         }
         return c;
@@ -527,35 +525,20 @@ static const MmaConfig& mma_config(MmaTag<FMT, ASYM, OUTL, FAST, GS>) {
     return cfg;
 }
 
-static bool i4_use_fast(const KvqAttnArgs& a);
-static bool use_fast(const AttnParams& p) { return p.a.format == KVQ_FMT_INT4 && i4_use_fast(p.a); }
-
-// Calls f(MmaTag<...>{}) for the instantiation that serves these arguments.
+// Calls f(MmaTag<...>{}) for the INT8 / fp16 instantiation that serves these arguments.
 template <class F>
 static int mma_dispatch(const AttnParams& p, bool asym, F&& f) {
-    const bool outl = p.a.n_out > 0, fast = use_fast(p);
+    const bool outl = p.a.n_out > 0;
     const int fmt = p.a.format, gs = p.a.group_size;
-#define KVQ_MMA_CASE(FMT_, ASYM_, OUTL_, FAST_, GS_)                                              \
-    if (fmt == FMT_ && asym == ASYM_ && outl == OUTL_ && fast == FAST_ && gs == GS_)              \
-        return f(MmaTag<FMT_, ASYM_, OUTL_, FAST_, GS_>{});
-#define KVQ_MMA_GS(FMT_, ASYM_, FAST_)                                                            \
-    KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 32)                                                   \
-    KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 64)                                                   \
-    KVQ_MMA_CASE(FMT_, ASYM_, false, FAST_, 128)
-    KVQ_MMA_CASE(KVQ_FMT_FP16, false, false, false, 128)
-    KVQ_MMA_GS(KVQ_FMT_INT8, false, false)
-    KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, false, 16)
-    KVQ_MMA_CASE(KVQ_FMT_INT8, false, true, false, 32)
-    KVQ_MMA_CASE(KVQ_FMT_INT8, true, false, false, 128)
-    KVQ_MMA_GS(KVQ_FMT_INT4, false, true)
-    KVQ_MMA_GS(KVQ_FMT_INT4, true, true)
-    KVQ_MMA_CASE(KVQ_FMT_INT4, false, true, true, 32)
-    KVQ_MMA_GS(KVQ_FMT_INT4, false, false)
-    KVQ_MMA_GS(KVQ_FMT_INT4, true, false)
-    KVQ_MMA_CASE(KVQ_FMT_INT4, false, false, false, 16)
-    KVQ_MMA_CASE(KVQ_FMT_INT4, true, false, false, 16)
-    KVQ_MMA_CASE(KVQ_FMT_INT4, false, true, false, 32)
-#undef KVQ_MMA_GS
+#define KVQ_MMA_CASE(FMT_, ASYM_, OUTL_, GS_)                                                     \
+    if (fmt == FMT_ && asym == ASYM_ && outl == OUTL_ && gs == GS_) return f(MmaTag<FMT_, ASYM_, OUTL_, GS_>{});
+    KVQ_MMA_CASE(KVQ_FMT_FP16, false, false, 128)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, 16)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, 32)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, 64)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, false, false, 128)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, false, true, 32)
+    KVQ_MMA_CASE(KVQ_FMT_INT8, true, false, 128)
 #undef KVQ_MMA_CASE
     return KVQ_EUNSUPPORTED;
 }
@@ -687,36 +670,29 @@ static int launch_i4(I4Tag<ASYM, NOUT, FAST, GS> tag, const AttnParams& p, cudaS
 }
 
 static bool i4_eligible(const AttnParams& p, bool asym) {
-    return p.a.format == KVQ_FMT_INT4 && !getenv("KVQ_INT4_OLD_KERNEL") && i4_config_for(p, asym) != nullptr;
+    return p.a.format == KVQ_FMT_INT4 && i4_config_for(p, asym) != nullptr;
 }
 
 static int dispatch_i4(const AttnParams& p, bool asym, cudaStream_t st) {
     return i4_dispatch(p, asym, [&](auto tag) { return launch_i4(tag, p, st); });
 }
 
-template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
-static int launch_mma(MmaTag<FMT, ASYM, OUTL, FAST, GS> tag, const AttnParams& p, cudaStream_t st) {
-    constexpr int RB = FMT == KVQ_FMT_FP16 ? 256 : FMT == KVQ_FMT_INT8 ? 128 : 64;
+template <int FMT, bool ASYM, bool OUTL, int GS>
+static int launch_mma(MmaTag<FMT, ASYM, OUTL, GS> tag, const AttnParams& p, cudaStream_t st) {
+    constexpr int RB = FMT == KVQ_FMT_FP16 ? 256 : 128;
     const MmaConfig& cfg = mma_config(tag);
     if (cfg.rc) return cfg.rc;
     MmaParams mp;
     mp.p = p;
     mp.nstage = cfg.nstage;
     mp.warp_smem_bytes = cfg.nstage * cfg.stage_bytes;
-    // Packed INT4 rows are 64 bytes.  When the tokens of a (b, h) row are contiguous, pairs of tokens are fetched as
-    // 128-byte rows.  The pair view covers floor(max_ctx / 2) pairs, so that nothing beyond token max_ctx - 1 is ever
-    // read: with an odd max_ctx the last token must belong to the combine stage (tail_tokens), which kvq_decode_attn
-    // arranges for whole calls; a split-only call without it keeps the 64-byte rows.
-    mp.wide_rows = FMT == KVQ_FMT_INT4 && wide_rows_ok(p.a);
     CUtensorMap kmap, vmap;
-    int rc, ext = p.a.max_ctx;
-    if (mp.wide_rows) ext = p.a.max_ctx / 2;
-    rc = make_payload_map(&kmap, p.a.k, mp.wide_rows ? 2 * RB : RB, ext, p.a.Hkv, p.a.B, mp.wide_rows != 0);
+    int rc = make_payload_map(&kmap, p.a.k, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;
-    rc = make_payload_map(&vmap, p.a.v, mp.wide_rows ? 2 * RB : RB, ext, p.a.Hkv, p.a.B, mp.wide_rows != 0);
+    rc = make_payload_map(&vmap, p.a.v, RB, p.a.max_ctx, p.a.Hkv, p.a.B);
     if (rc) return rc;
     dim3 grid(p.splits, p.a.Hkv * p.rep_chunks, p.a.B);
-    return launch_pdl(decode_split_mma_kernel<FMT, ASYM, OUTL, FAST, GS>, grid, dim3(kMmaWarps * 32), cfg.dyn_smem, st, mp,
+    return launch_pdl(decode_split_mma_kernel<FMT, ASYM, OUTL, GS>, grid, dim3(kMmaWarps * 32), cfg.dyn_smem, st, mp,
                       kmap, vmap);
 }
 

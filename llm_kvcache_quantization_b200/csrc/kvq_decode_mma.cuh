@@ -1,9 +1,9 @@
-// Tensor-core split-K decode-attention kernel for sm_100a.
+// Tensor-core split-K decode-attention kernel for sm_100a: INT8 and unquantised fp16 caches.
+// (The nibble-packed INT4 cache has its own kernel, kvq_decode_int4.cuh, which shares the helpers below.)
 //
-// Shapes: head_dim 128; INT8 or nibble-packed INT4 payload with one fp16 scale per group of
-// 16 / 32 / 64 / 128 channels per token, optional fp16 zero-points, optional fp16 outlier
-// side channels; or an unquantised fp16 cache.  <= 8 query heads per KV head per CTA.
-// Everything else goes to the generic kernel.
+// Shapes: head_dim 128; INT8 payload with one fp16 scale per group of 16 / 32 / 64 / 128 channels per
+// token, optional fp16 zero-points (one group per token), optional fp16 outlier side channels; or an
+// unquantised fp16 cache.  <= 8 query heads per KV head per CTA.  Everything else goes to the generic kernel.
 //
 // Structure
 //  * grid = (KV split, kv head [x head chunk], batch row); 4 warps per CTA.  Every warp
@@ -48,10 +48,6 @@
 #ifndef KVQ_ABLATE
 #define KVQ_ABLATE 0
 #endif
-// resident CTAs per SM the packed-INT4 instantiations are compiled for (register cap = 65536 / (128 * this))
-#ifndef KVQ_INT4_MIN_CTAS
-#define KVQ_INT4_MIN_CTAS 4
-#endif
 
 namespace kvq {
 
@@ -65,7 +61,6 @@ struct MmaParams {
     AttnParams p;
     int nstage;
     int warp_smem_bytes;     // nstage * bytes of one stage: the private ring of one warp
-    int wide_rows;           // packed INT4 only: the payload maps are built over 128-byte rows of TWO tokens
 };
 
 // Bytes of one pipeline stage: K tile, V tile (each TS rows), then 2 (4 with zero-points)
@@ -271,30 +266,20 @@ __device__ __forceinline__ uint32_t apply_scale(uint32_t c, uint32_t s2, uint32_
 //   [TS*RB, 2*TS*RB)      V payload tile   (TMA, swizzled)
 //   then K scales [TS][4] fp16, V scales, (K zero-points, V zero-points)   256 B each
 //
-// FAST (packed INT4 only) applies the scales OUTSIDE the integer products instead of per element:
-//   q.K   one fp32 accumulator per quantisation group (2 mma each over exact integer codes), then
-//         logit = sum_g s[token][g] * S_g  (+ z[token][g] * sum_{d in g} q_d with zero-points);
-//   P.V   the scale of (token, group) is folded into P before the product, P'_g = RN16(P * s_g)
-//         (+ sum_token z[token][g] * p with zero-points, added to every channel of the group).
-// This removes 3 of every 4 fp16 instructions of the dequantisation; products of integer codes are
-// exact, so the result differs from the bit-faithful path only by the reference's own fp16 rounding
-// of code * scale (<= 2^-11 relative per element).  FAST = false is the bit-faithful path and the default;
-// FAST is opt-in (KvqAttnArgs.fast_dequant).
 // GS = quantisation group size (16 / 32 / 64 / 128 channels), NG = 128 / GS scales per token.
-template <int FMT, bool ASYM, bool OUTL, bool FAST, int GS>
-__global__ void __launch_bounds__(kMmaWarps * 32, (FMT == KVQ_FMT_INT4) ? KVQ_INT4_MIN_CTAS : 1)
+template <int FMT, bool ASYM, bool OUTL, int GS>
+__global__ void __launch_bounds__(kMmaWarps * 32, 1)
 decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
     constexpr bool F16 = FMT == KVQ_FMT_FP16;                 // unquantised cache: no scales, no dequantisation
-    constexpr int RB = F16 ? 256 : (FMT == KVQ_FMT_INT8) ? 128 : 64;   // payload bytes per token row
+    constexpr int RB = F16 ? 256 : 128;                       // payload bytes per token row
     constexpr int D = 128;
     constexpr int NG = 128 / GS;                              // scale groups per token
     constexpr int SCB = kTS * NG * 2;                         // bytes of one scale tile
     constexpr int STAGE_BYTES = mma_stage_bytes(FMT, ASYM, OUTL, GS);
     static_assert(GS == 16 || GS == 32 || GS == 64 || GS == 128, "group size");
-    static_assert(!FAST || GS >= 32, "the factored path needs whole 32-channel chunks inside one group");
+    static_assert(FMT == KVQ_FMT_FP16 || FMT == KVQ_FMT_INT8, "packed INT4 is served by kvq_decode_int4.cuh");
     static_assert(!(ASYM && OUTL), "outlier side buffer is defined for symmetric formats");
-    static_assert(!FAST || FMT == KVQ_FMT_INT4, "the factored-scale path exists for packed INT4");
     static_assert(!F16 || (!ASYM && !OUTL && GS == 128), "the fp16 cache has neither scales nor side channels");
     const AttnParams& p = mp.p;
     const KvqAttnArgs& a = p.a;
@@ -305,7 +290,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     const int h0 = kvh * p.n_rep + rc * kHeadsPerCta;
     const int nh = min(kHeadsPerCta, p.n_rep - rc * kHeadsPerCta);
     const int nstage = mp.nstage;
-    const bool wide = FMT == KVQ_FMT_INT4 && mp.wide_rows != 0;
 
     extern __shared__ unsigned char smem_dyn[];
     // stage buffers, 1024-byte aligned by hand: the TMA swizzle pattern is a function of the
@@ -333,13 +317,8 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     split_range(ctx, p.splits, split, kTS, s0, s1);
 
     // ---- Q fragments: thread (g = head, t) holds q[head g][32t .. 32t+32) in the channel
-    // order of the K fragments (INT8: natural; INT4: nibble order d1,d5 | d0,d4 | d3,d7 | d2,d6).
+    // order of the K fragments.
     uint32_t qf[16];
-    // FAST with zero-points: qs[e][G] = sum over the channels of group G of q[head 2t+e] (fp32);
-    // oz[G][e] = zero-point part of the output of that head, shared by every channel of the group
-    float qs[2][NG], oz[NG][2];
-#pragma unroll
-    for (int G = 0; G < NG; ++G) { qs[0][G] = qs[1][G] = 0.f; oz[G][0] = oz[G][1] = 0.f; }
     if (F16) {
         // natural B-fragment order: k-chunk j <-> channels 16j + {2t, 2t+1} and 16j + 8 + {2t, 2t+1}
         const bool hv = g < nh;
@@ -358,13 +337,12 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     } else {
         const bool hv = g < nh;
         const __half* qp = (const __half*)a.q + (long long)b * a.q_stride_b + (long long)(h0 + (hv ? g : 0)) * a.q_stride_h +
-                           (FAST ? 8 * t : 32 * t);
+                           32 * t;
         __half qv[32];
         const __half tau = (a.inv_tau && hv) ? __float2half_rn(a.inv_tau[h0 + g]) : __float2half(1.0f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            // FAST: channels 32 i + 8 t .. + 7 (8 channels of every group); else 32 t + 8 i .. + 7
-            uint4 v = *(const uint4*)(qp + (FAST ? 32 : 8) * i);
+            uint4 v = *(const uint4*)(qp + 8 * i);               // channels 32 t + 8 i .. + 7
             *(uint4*)(qv + 8 * i) = v;
         }
 #pragma unroll
@@ -373,41 +351,18 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             if (a.inv_tau) qv[i] = __hmul(qv[i], tau);
         }
         if (a.q_chan_scale) {
-            // per-channel factor of this kv head; element i of the slice is channel 32 (i / 8) + 8 t + i % 8 in the
-            // factored layout, 32 t + i otherwise
+            // per-channel factor of this kv head; element i of the slice is channel 32 t + i
             const float* cs = a.q_chan_scale + (long long)b * a.qcs_stride_b + (long long)kvh * a.qcs_stride_h;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                const int ch = FAST ? 32 * (i >> 3) + 8 * t + (i & 7) : 32 * t + i;
+                const int ch = 32 * t + i;
                 qv[i] = __float2half_rn(__half2float(qv[i]) * cs[ch]);
             }
         }
-        if (FAST && ASYM) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {                       // 32-channel chunk c lies in group (32 c) / GS
-                float acc = 0.f;                                // this thread: 8 channels of chunk c of head g
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc += __half2float(qv[8 * c + i]);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);    // every lane of the quad: whole chunk of head g
-                qs[0][(32 * c) / GS] += __shfl_sync(0xffffffffu, acc, 4 * (2 * t));
-                qs[1][(32 * c) / GS] += __shfl_sync(0xffffffffu, acc, 4 * (2 * t + 1));
-            }
-        }
-        if (FMT == KVQ_FMT_INT8) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {                       // k-chunk j <-> channels 4j..4j+3
-                qf[2 * j] = h2_as_u32(__halves2half2(qv[4 * j], qv[4 * j + 1]));
-                qf[2 * j + 1] = h2_as_u32(__halves2half2(qv[4 * j + 2], qv[4 * j + 3]));
-            }
-        } else {
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {                       // register w <-> channels 8w..8w+7
-                qf[4 * w + 0] = h2_as_u32(__halves2half2(qv[8 * w + 1], qv[8 * w + 5]));
-                qf[4 * w + 1] = h2_as_u32(__halves2half2(qv[8 * w + 0], qv[8 * w + 4]));
-                qf[4 * w + 2] = h2_as_u32(__halves2half2(qv[8 * w + 3], qv[8 * w + 7]));
-                qf[4 * w + 3] = h2_as_u32(__halves2half2(qv[8 * w + 2], qv[8 * w + 6]));
-            }
+        for (int j = 0; j < 8; ++j) {                           // k-chunk j <-> channels 4j..4j+3
+            qf[2 * j] = h2_as_u32(__halves2half2(qv[4 * j], qv[4 * j + 1]));
+            qf[2 * j + 1] = h2_as_u32(__halves2half2(qv[4 * j + 2], qv[4 * j + 3]));
         }
     }
 
@@ -467,9 +422,8 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                 tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
                 tma_load_4d(sb + kTS * RB + kTS * 128, &vmap, bar, 128, tok0, kvh, b);
             } else {
-                const int row0 = wide ? (tok0 >> 1) : tok0;
-                tma_load_4d(sb, &kmap, bar, 0, row0, kvh, b);
-                tma_load_4d(sb + kTS * RB, &vmap, bar, 0, row0, kvh, b);
+                tma_load_4d(sb, &kmap, bar, 0, tok0, kvh, b);
+                tma_load_4d(sb + kTS * RB, &vmap, bar, 0, tok0, kvh, b);
             }
         }
         // scale-like tiles: TS tokens x NG fp16 = 4*NG chunks of 16 bytes per tile; 2 (or 4) tiles.
@@ -500,20 +454,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
         }
         cp_async_mbar_arrive(bar);
     };
-
-    // byte offsets (inside a 64-byte-row tile) of this lane's ldmatrix row for sub-tile `sub`, group pair `gp`:
-    // matrix (lane>>3): bit 0 = token half, bit 1 = second 16-byte chunk (= group) of the pair
-    uint32_t ldsm_off[2][2];
-    // row-wise 16-byte loads of the bit-faithful q.K product: chunk t of rows 16 sub + g and 16 sub + g + 8
-    uint32_t krow_off[2][2];
-#pragma unroll
-    for (int sub = 0; sub < 2; ++sub)
-#pragma unroll
-        for (int gp = 0; gp < 2; ++gp) {
-            const int lrow = 16 * sub + ((lane >> 3) & 1) * 8 + (lane & 7);
-            ldsm_off[sub][gp] = int4_tile_off(wide, lrow, 2 * gp + (lane >> 4));
-            krow_off[sub][gp] = int4_tile_off(wide, 16 * sub + g + 8 * gp, t);
-        }
 
     bool failed = false;
     const int prolog = min(nstage - 1, n_my);
@@ -549,55 +489,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
 #pragma unroll
                 for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
         }
-        if (FAST && !NO_QK) {
-#pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                float sg[NG][4];                                 // per-group integer dot products
-#pragma unroll
-                for (int G = 0; G < NG; ++G)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) sg[G][j] = 0.f;
-#pragma unroll
-                for (int gp = 0; gp < 2; ++gp) {
-                    uint32_t r[4];                               // rows g | g+8 of chunk 2gp, then of chunk 2gp+1
-                    ldmatrix_x4(kb + ldsm_off[sub][gp], r);
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int c = 2 * gp + e;                // 32-channel chunk; its group:
-                        const int G = (32 * c) / GS;
-                        const uint32_t w0 = r[2 * e], w1 = r[2 * e + 1];
-                        mma16816(sg[G], nib_lo_to_h2(w0), nib_lo_to_h2(w1), nib_hi_to_h2(w0), nib_hi_to_h2(w1),
-                                 qf[4 * c], qf[4 * c + 1]);
-                        const uint32_t x0 = w0 >> 8, x1 = w1 >> 8;
-                        mma16816(sg[G], nib_lo_to_h2(x0), nib_lo_to_h2(x1), nib_hi_to_h2(x0), nib_hi_to_h2(x1),
-                                 qf[4 * c + 2], qf[4 * c + 3]);
-                    }
-                }
-                const int r0 = 16 * sub + g, r1 = r0 + 8;
-                float sa[NG], sb2[NG];                           // K scales of rows r0, r1
-                load_row_floats<NG>(ksb + r0 * 2 * NG, sa);
-                load_row_floats<NG>(ksb + r1 * 2 * NG, sb2);
-                sacc[sub][0] = sacc[sub][1] = sacc[sub][2] = sacc[sub][3] = 0.f;
-#pragma unroll
-                for (int G = 0; G < NG; ++G) {
-                    sacc[sub][0] = fmaf(sa[G], sg[G][0], sacc[sub][0]);
-                    sacc[sub][1] = fmaf(sa[G], sg[G][1], sacc[sub][1]);
-                    sacc[sub][2] = fmaf(sb2[G], sg[G][2], sacc[sub][2]);
-                    sacc[sub][3] = fmaf(sb2[G], sg[G][3], sacc[sub][3]);
-                }
-                if (ASYM) {
-                    load_row_floats<NG>(kzb + r0 * 2 * NG, sa);
-                    load_row_floats<NG>(kzb + r1 * 2 * NG, sb2);
-#pragma unroll
-                    for (int G = 0; G < NG; ++G)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            sacc[sub][e] = fmaf(sa[G], qs[e][G], sacc[sub][e]);
-                            sacc[sub][2 + e] = fmaf(sb2[G], qs[e][G], sacc[sub][2 + e]);
-                        }
-                }
-            }
-        }
         if (F16 && !NO_QK) {
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
@@ -615,7 +506,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             }
         }
 #pragma unroll
-        for (int sub = 0; sub < ((FAST || F16 || NO_QK) ? 0 : 2); ++sub) {
+        for (int sub = 0; sub < ((F16 || NO_QK) ? 0 : 2); ++sub) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) sacc[sub][j] = 0.f;
             const int r0 = 16 * sub + g, r1 = r0 + 8;
@@ -649,48 +540,27 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
                     }
                 }
             }
-            if (FMT == KVQ_FMT_INT8) {
-                uint32_t w[2][8];
+            uint32_t w[2][8];
 #pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {
-                    const int r = rr ? r1 : r0;
-                    uint32_t x[4], y[4];
-                    lds128(kb + r * 128 + (((2 * t) ^ (r & 7)) << 4), x);
-                    lds128(kb + r * 128 + (((2 * t + 1) ^ (r & 7)) << 4), y);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        w[rr][i] = x[i] ^ 0x80808080u;
-                        w[rr][4 + i] = y[i] ^ 0x80808080u;
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int hh = j >> 2;                           // channels 4j.. lie in half j / 4 of the slice
-                    uint32_t a0 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5140u), s2[0][hh], z2[0][hh]);
-                    uint32_t a1 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5140u), s2[1][hh], z2[1][hh]);
-                    uint32_t a2 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5342u), s2[0][hh], z2[0][hh]);
-                    uint32_t a3 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5342u), s2[1][hh], z2[1][hh]);
-                    mma16816(sacc[sub], a0, a1, a2, a3, qf[2 * j], qf[2 * j + 1]);
-                }
-            } else {
-                uint32_t w[2][4];
-                lds128(kb + krow_off[sub][0], w[0]);
-                lds128(kb + krow_off[sub][1], w[1]);
+            for (int rr = 0; rr < 2; ++rr) {
+                const int r = rr ? r1 : r0;
+                uint32_t x[4], y[4];
+                lds128(kb + r * 128 + (((2 * t) ^ (r & 7)) << 4), x);
+                lds128(kb + r * 128 + (((2 * t + 1) ^ (r & 7)) << 4), y);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int hh = i >> 1;                           // channels 8i.. lie in half i / 2 of the slice
-                    uint32_t lo0 = apply_scale<ASYM>(nib_lo_to_h2(w[0][i]), s2[0][hh], z2[0][hh]);
-                    uint32_t lo1 = apply_scale<ASYM>(nib_lo_to_h2(w[1][i]), s2[1][hh], z2[1][hh]);
-                    uint32_t hi0 = apply_scale<ASYM>(nib_hi_to_h2(w[0][i]), s2[0][hh], z2[0][hh]);
-                    uint32_t hi1 = apply_scale<ASYM>(nib_hi_to_h2(w[1][i]), s2[1][hh], z2[1][hh]);
-                    mma16816(sacc[sub], lo0, lo1, hi0, hi1, qf[4 * i], qf[4 * i + 1]);
-                    const uint32_t w0 = w[0][i] >> 8, w1 = w[1][i] >> 8;
-                    lo0 = apply_scale<ASYM>(nib_lo_to_h2(w0), s2[0][hh], z2[0][hh]);
-                    lo1 = apply_scale<ASYM>(nib_lo_to_h2(w1), s2[1][hh], z2[1][hh]);
-                    hi0 = apply_scale<ASYM>(nib_hi_to_h2(w0), s2[0][hh], z2[0][hh]);
-                    hi1 = apply_scale<ASYM>(nib_hi_to_h2(w1), s2[1][hh], z2[1][hh]);
-                    mma16816(sacc[sub], lo0, lo1, hi0, hi1, qf[4 * i + 2], qf[4 * i + 3]);
+                    w[rr][i] = x[i] ^ 0x80808080u;
+                    w[rr][4 + i] = y[i] ^ 0x80808080u;
                 }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int hh = j >> 2;                           // channels 4j.. lie in half j / 4 of the slice
+                uint32_t a0 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5140u), s2[0][hh], z2[0][hh]);
+                uint32_t a1 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5140u), s2[1][hh], z2[1][hh]);
+                uint32_t a2 = apply_scale<ASYM>(i8pair_to_h2(w[0][j], 0x5342u), s2[0][hh], z2[0][hh]);
+                uint32_t a3 = apply_scale<ASYM>(i8pair_to_h2(w[1][j], 0x5342u), s2[1][hh], z2[1][hh]);
+                mma16816(sacc[sub], a0, a1, a2, a3, qf[2 * j], qf[2 * j + 1]);
             }
         }
 
@@ -743,7 +613,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             mneg[e] = -m_new;
         }
         float psum[2] = {0.f, 0.f};
-        float pf[2][4];                                              // fp32 probabilities (FAST + zero-points)
         uint32_t pb[2][2];                                           // P^T B fragments per sub-tile
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
@@ -758,7 +627,6 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             }
             psum[0] += p0 + p2;
             psum[1] += p1 + p3;
-            pf[sub][0] = p0; pf[sub][1] = p1; pf[sub][2] = p2; pf[sub][3] = p3;
             if (OUTL) {
                 const int r0 = 16 * sub + g, r1 = r0 + 8;
                 const bool ok0 = !partial || tok0 + r0 < s1, ok1 = !partial || tok0 + r1 < s1;
@@ -786,64 +654,9 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             for (int i = 0; i < 8; ++i) {
                 o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1];
             }
-            if (FAST && ASYM) {
-#pragma unroll
-                for (int G = 0; G < NG; ++G) { oz[G][0] *= corr[0]; oz[G][1] *= corr[1]; }
-            }
         }
 
         // ================= P.V =================
-        if (FAST && !NO_PV) {
-#pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                // fold the V scale of (token, group) into P: B fragments per group
-                uint32_t px[NG], py[NG];
-                {
-                    const int ta = 16 * sub + 2 * t;
-                    uint32_t mxm = 0xffffffffu, mym = 0xffffffffu;
-                    if (partial) {   // scales past the range may be anything (even NaN): force P' to 0 there
-                        const int tg = tok0 + ta;
-                        mxm = (tg < s1 ? 0x0000ffffu : 0u) | (tg + 1 < s1 ? 0xffff0000u : 0u);
-                        mym = (tg + 8 < s1 ? 0x0000ffffu : 0u) | (tg + 9 < s1 ? 0xffff0000u : 0u);
-                    }
-                    load_scale_pairs<NG>(vsb + ta * 2 * NG, px, mxm);
-                    load_scale_pairs<NG>(vsb + (ta + 8) * 2 * NG, py, mym);
-#pragma unroll
-                    for (int G = 0; G < NG; ++G) {
-                        px[G] = hmul2_u(pb[sub][0], px[G]);
-                        py[G] = hmul2_u(pb[sub][1], py[G]);
-                    }
-                }
-#pragma unroll
-                for (int gp = 0; gp < 2; ++gp) {
-                    uint32_t r[4];
-                    ldmatrix_x4_trans(vb + ldsm_off[sub][gp], r);
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int c = 2 * gp + e;                // 32-channel chunk c, group (32 c) / GS
-                        const int G = (32 * c) / GS;
-                        const uint32_t X = r[2 * e], Y = r[2 * e + 1];
-                        mma16816(o[2 * c], nib_lo_to_h2(X), nib_hi_to_h2(X), nib_lo_to_h2(Y), nib_hi_to_h2(Y), px[G], py[G]);
-                        const uint32_t X8 = X >> 8, Y8 = Y >> 8;
-                        mma16816(o[2 * c + 1], nib_lo_to_h2(X8), nib_hi_to_h2(X8), nib_lo_to_h2(Y8), nib_hi_to_h2(Y8),
-                                 px[G], py[G]);
-                    }
-                }
-                if (ASYM) {
-                    const int r0 = 16 * sub + g, r1 = r0 + 8;
-                    const bool ok0 = !partial || tok0 + r0 < s1, ok1 = !partial || tok0 + r1 < s1;
-                    float y[NG], z[NG];
-                    load_row_floats<NG>(vzb + r0 * 2 * NG, y);
-                    load_row_floats<NG>(vzb + r1 * 2 * NG, z);
-#pragma unroll
-                    for (int G = 0; G < NG; ++G) {
-                        const float yv = ok0 ? y[G] : 0.f, zv = ok1 ? z[G] : 0.f;
-                        oz[G][0] = fmaf(pf[sub][0], yv, fmaf(pf[sub][2], zv, oz[G][0]));
-                        oz[G][1] = fmaf(pf[sub][1], yv, fmaf(pf[sub][3], zv, oz[G][1]));
-                    }
-                }
-            }
-        }
         if (F16 && !NO_PV) {
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
@@ -865,7 +678,7 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             }
         }
 #pragma unroll
-        for (int sub = 0; sub < ((FAST || F16 || NO_PV) ? 0 : 2); ++sub) {
+        for (int sub = 0; sub < ((F16 || NO_PV) ? 0 : 2); ++sub) {
             // scales of tokens (2t, 2t+1) and (2t+8, 2t+9), paired per group
             uint32_t sx[NG], sy[NG], zx[NG], zy[NG];
             {
@@ -890,52 +703,19 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
             // ldmatrix source row for this lane: matrix (lane>>3): bit0 = token half, bit1 = chunk + 1
             const int lrow = 16 * sub + ((lane >> 3) & 1) * 8 + (lane & 7);
             const int lchunk = lane >> 4;
-            if (FMT == KVQ_FMT_INT8) {
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    uint32_t r[4];
-                    ldmatrix_x4_trans(vb + lrow * 128 + (((i + lchunk) ^ (lrow & 7)) << 4), r);
+            for (int i = 0; i < 8; i += 2) {
+                uint32_t r[4];
+                ldmatrix_x4_trans(vb + lrow * 128 + (((i + lchunk) ^ (lrow & 7)) << 4), r);
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const uint32_t X = r[2 * e] ^ 0x80808080u, Y = r[2 * e + 1] ^ 0x80808080u;
-                        const int grp = (16 * (i + e)) / GS;             // channels 16(i+e) .. +15
-                        uint32_t a0 = apply_scale<ASYM>(i8pair_to_h2(X, 0x5240u), sx[grp], zx[grp]);
-                        uint32_t a1 = apply_scale<ASYM>(i8pair_to_h2(X, 0x5341u), sx[grp], zx[grp]);
-                        uint32_t a2 = apply_scale<ASYM>(i8pair_to_h2(Y, 0x5240u), sy[grp], zy[grp]);
-                        uint32_t a3 = apply_scale<ASYM>(i8pair_to_h2(Y, 0x5341u), sy[grp], zy[grp]);
-                        mma16816(o[i + e], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; i += 2) {
-                    uint32_t r[4];
-                    ldmatrix_x4_trans(vb + ldsm_off[sub][i >> 1], r);
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const uint32_t X = r[2 * e], Y = r[2 * e + 1];
-                        const int c = i + e;                             // 32-channel chunk; this thread's 4 channels
-                        // 32c + 4g .. +3 lie in group 2c + (g >> 2) when GS == 16, else in (32 c) / GS
-                        uint32_t ux, uy, vx, vy;
-                        if (GS == 16) {
-                            const bool up = (g >> 2) != 0;
-                            ux = up ? sx[(2 * c + 1) % NG] : sx[(2 * c) % NG]; uy = up ? sy[(2 * c + 1) % NG] : sy[(2 * c) % NG];
-                            vx = up ? zx[(2 * c + 1) % NG] : zx[(2 * c) % NG]; vy = up ? zy[(2 * c + 1) % NG] : zy[(2 * c) % NG];
-                        } else {
-                            ux = sx[(32 * c) / GS]; uy = sy[(32 * c) / GS]; vx = zx[(32 * c) / GS]; vy = zy[(32 * c) / GS];
-                        }
-                        uint32_t a0 = apply_scale<ASYM>(nib_lo_to_h2(X), ux, vx);
-                        uint32_t a1 = apply_scale<ASYM>(nib_hi_to_h2(X), ux, vx);
-                        uint32_t a2 = apply_scale<ASYM>(nib_lo_to_h2(Y), uy, vy);
-                        uint32_t a3 = apply_scale<ASYM>(nib_hi_to_h2(Y), uy, vy);
-                        mma16816(o[2 * c], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
-                        const uint32_t X8 = X >> 8, Y8 = Y >> 8;
-                        a0 = apply_scale<ASYM>(nib_lo_to_h2(X8), ux, vx);
-                        a1 = apply_scale<ASYM>(nib_hi_to_h2(X8), ux, vx);
-                        a2 = apply_scale<ASYM>(nib_lo_to_h2(Y8), uy, vy);
-                        a3 = apply_scale<ASYM>(nib_hi_to_h2(Y8), uy, vy);
-                        mma16816(o[2 * c + 1], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
-                    }
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t X = r[2 * e] ^ 0x80808080u, Y = r[2 * e + 1] ^ 0x80808080u;
+                    const int grp = (16 * (i + e)) / GS;             // channels 16(i+e) .. +15
+                    uint32_t a0 = apply_scale<ASYM>(i8pair_to_h2(X, 0x5240u), sx[grp], zx[grp]);
+                    uint32_t a1 = apply_scale<ASYM>(i8pair_to_h2(X, 0x5341u), sx[grp], zx[grp]);
+                    uint32_t a2 = apply_scale<ASYM>(i8pair_to_h2(Y, 0x5240u), sy[grp], zy[grp]);
+                    uint32_t a3 = apply_scale<ASYM>(i8pair_to_h2(Y, 0x5341u), sy[grp], zy[grp]);
+                    mma16816(o[i + e], a0, a1, a2, a3, pb[sub][0], pb[sub][1]);
                 }
             }
         }
@@ -961,37 +741,12 @@ decode_split_mma_kernel(const MmaParams mp, const __grid_constant__ CUtensorMap 
     for (int i = 0; i < 8; ++i) {
         int d0, d1;                                               // channels of fragment rows g, g+8
         if (F16) { d0 = 16 * i + g; d1 = d0 + 8; }
-        else if (FMT == KVQ_FMT_INT8) { d0 = 16 * i + 2 * g; d1 = d0 + 1; }
-        else { const int base = 32 * (i >> 1) + 4 * g + 2 * (i & 1); d0 = base + 1; d1 = base; }
+        else { d0 = 16 * i + 2 * g; d1 = d0 + 1; }
         float* ra = red_acc + (size_t)warp * kHeadsPerCta * D;
         ra[(2 * t) * D + d0] = o[i][0];
         ra[(2 * t + 1) * D + d0] = o[i][1];
         ra[(2 * t) * D + d1] = o[i][2];
         ra[(2 * t + 1) * D + d1] = o[i][3];
-    }
-    if (FAST && ASYM) {
-        // oz[G][e]: sum over this warp's tokens of p * zero-point for group G, head 2t+e; add it to the
-        // 16 channels [16g, 16g+16) (all in group g/2) of both heads
-#pragma unroll
-        for (int G = 0; G < NG; ++G)
-#pragma unroll
-            for (int e = 0; e < 2; ++e)
-#pragma unroll
-                for (int off = 4; off <= 16; off <<= 1) oz[G][e] += __shfl_xor_sync(0xffffffffu, oz[G][e], off);
-        __syncwarp();
-        const int Gme = (16 * g) / GS;                 // group of this lane's channels [16g, 16g+16)
-        float add0 = oz[0][0], add1 = oz[0][1];
-#pragma unroll
-        for (int G = 1; G < NG; ++G)
-            if (G == Gme) { add0 = oz[G][0]; add1 = oz[G][1]; }
-        float* ra = red_acc + (size_t)warp * kHeadsPerCta * D;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int c = 16 * g + ((i + 4 * (g >> 1) + t) & 15);   // rotated: the 32 lanes hit 32 distinct banks
-            ra[(2 * t) * D + c] += add0;
-            ra[(2 * t + 1) * D + c] += add1;
-        }
-        __syncwarp();
     }
     if (OUTL) {
 #pragma unroll
