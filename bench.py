@@ -1,18 +1,26 @@
 #!/usr/bin/env python3
 """Benchmark of the quantized-KV decode path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c4]
 
-One "step" = one decode step over the whole KV stack of the workload: for every
-layer, quantize-on-append of the new token (one launch for K and V) followed by
-the fused decode attention (split-K kernel + combine) over the cached context.
-Default workload is configuration 2 of the benchmark definition (Qwen2.5-1.5B geometry, 28
-layers, batch 16, context 8192, INT4 asymmetric group-32 with fp16 scale and
-zero-point).  With N > 1 the batch is sharded by sequence: every rank owns its own
-batch of sequences and its own cache, no collective on the data path (weak scaling).
-The single-sequence workload c5 with N > 1 shards the KV sequence instead: every rank
-scans its contiguous chunk, the packed partials cross NVLink in one NCCL all-gather per
-layer and are merged on every rank (strong scaling: the total work is fixed).
+One "step" = one decode step over the whole KV stack of a workload: for every layer, quantize-on-append
+of the new token (one launch for K and V) followed by the fused decode attention (split-K scan + combine)
+over the cached context, captured as one CUDA graph.
+
+Headline workload = configuration 4 of the benchmark definition, the largest one that fits a single GPU
+(Qwen2.5-7B geometry, 28 layers, batch 64, context 32768, INT8 group-32: 64 GB of cache).  The other
+configurations (c1, c2, c3, c5 and the KIVI-format variant of c2) are measured in the same run and
+reported under `extra.workloads`, each with its own step time, scan roofline, end-to-end number and
+clocks; packed-INT4 workloads report both dequantisation arithmetics.
+
+With N > 1 (one process per GPU) the FIXED batch of 64 sequences of configuration 4 is sharded by sequence
+(`parallel.batch_shard`: 64 / N rows per GPU, no collective on the data path; strong scaling), and the
+single-sequence configuration 5 is sharded by KV-sequence chunks with its partials exchanged once per layer
+(`extra.sequence_sharded`: the library's fused combine / peer-store / merge kernel, and the NCCL all-gather form).
+
+Every timed region is a repetition of blocks of exactly K steps (barrier + device synchronisation on both
+sides of a block, CUDA events, maximum over ranks) until at least `--min-seconds` have been timed; the
+median over blocks is reported, the minimum beside it.
 
 Prints ONE JSON line (rank 0).
 """
@@ -420,63 +428,146 @@ def time_graph(g, iters, dist=None):
     return e0.elapsed_time(e1)
 
 
+# --------------------------------------------------------------------------- timing
+def timed_blocks(run_block, steps, min_seconds, dist=None, dev=None, max_blocks=2000):
+    """Repeats `run_block(steps)` (which returns the elapsed milliseconds of exactly `steps` steps, measured between
+    its own synchronisation points) until at least `min_seconds` have been timed.  Returns ms per step of every block.
+    With several ranks every block's time is the maximum over ranks, so that all ranks time the same number of blocks."""
+    per_step, total = [], 0.0
+    while True:
+        ms = run_block(steps)
+        if dist is not None:
+            ms, = allreduce_max([ms], dev, dist)
+        per_step.append(ms / steps)
+        total += ms
+        if total >= min_seconds * 1e3 or len(per_step) >= max_blocks:
+            return per_step
+
+
+def block_stats(per_step):
+    return {"median": statistics.median(per_step), "min": min(per_step), "blocks": len(per_step)}
+
+
+def allreduce_max(vals, dev, dist):
+    import torch
+    if dist is None:
+        return [float(v) for v in vals]
+    t = torch.tensor(list(vals), dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
+
+
 # --------------------------------------------------------------------------- CPU baseline / reference arm
-def cpu_sample(wl, seed=1234, target_s=12.0, max_rows=4):
-    """Times the CPU oracle (C restatement, OpenMP, all host threads) on a bounded sample of
-    the workload: ONE layer, `rows` batch rows at the full context, quantize-on-append of the
-    new token plus decode attention.  Returns (seconds per sample pass, rows, threads)."""
+def cpu_inputs(wl, rows, layers, seed=1234):
+    """Host-side inputs of the CPU oracle for `layers` layers x `rows` batch rows at the full context: random
+    payload bytes, fp16 scales (zero-points, side values) and queries of the workload's shapes and dtypes.  The
+    oracle's run time does not depend on the values, so nothing is quantized here; generated ONCE, outside any
+    timed pass."""
+    import numpy as np
+    Hq, Hkv, S, kind, n_out = wl["Hq"], wl["Hkv"], wl["S"], wl["kind"], wl["n_out"]
+    rng = np.random.default_rng(seed)
+    n = S + 1
+    per_layer = []
+    for _ in range(layers):
+        d = {}
+        if kind == "fp16":
+            d["fmt"] = 0
+            d["k"] = rng.standard_normal((rows, Hkv, n, D), dtype=np.float32).astype(np.float16)
+            d["v"] = rng.standard_normal((rows, Hkv, n, D), dtype=np.float32).astype(np.float16)
+            d["ks"] = d["vs"] = None
+        else:
+            int8 = kind.startswith("int8")
+            d["fmt"] = 1 if int8 else 2
+            dp = D if int8 else D // 2
+            d["k"] = rng.integers(-127, 128, (rows, Hkv, n, dp), dtype=np.int8)
+            d["v"] = rng.integers(-127, 128, (rows, Hkv, n, dp), dtype=np.int8)
+            d["ks"] = rng.uniform(0.01, 0.1, (rows, Hkv, n, G)).astype(np.float16)
+            d["vs"] = rng.uniform(0.01, 0.1, (rows, Hkv, n, G)).astype(np.float16)
+            if kind in ("int4_asym", "kivi4"):
+                d["kz"] = rng.uniform(-0.5, 0.5, (rows, Hkv, n, G)).astype(np.float16)
+                d["vz"] = rng.uniform(-0.5, 0.5, (rows, Hkv, n, G)).astype(np.float16)
+            if kind == "int4_outlier":
+                d["outlier_idx"] = np.stack([np.sort(rng.permutation(D)[:n_out]) for _ in range(Hkv)]).astype(np.int16)
+                d["kside"] = rng.standard_normal((rows, Hkv, n, n_out), dtype=np.float32).astype(np.float16)
+                d["vside"] = rng.standard_normal((rows, Hkv, n, n_out), dtype=np.float32).astype(np.float16)
+        d["q"] = rng.standard_normal((rows, Hq, D), dtype=np.float32).astype(np.float16)
+        d["k_new"] = rng.standard_normal((rows, Hkv, 1, D), dtype=np.float32).astype(np.float16)
+        d["v_new"] = rng.standard_normal((rows, Hkv, 1, D), dtype=np.float32).astype(np.float16)
+        per_layer.append(d)
+    tau = rng.uniform(0.8, 1.2, Hq).astype(np.float32)
+    return per_layer, tau
+
+
+def cpu_pass(wl, per_layer, tau):
+    """One pass of the CPU oracle (C restatement, OpenMP) over the given layers: quantize-on-append of the new token
+    and decode attention over the full context.  Returns the seconds it took."""
     import numpy as np
     from oracle import c_oracle as CO
-    from oracle import kvq_oracle as O
-
-    Hq, Hkv, S, kind, n_out = wl["Hq"], wl["Hkv"], wl["S"], wl["kind"], wl["n_out"]
-    rows = min(max_rows, wl["B"])
-    rng = np.random.default_rng(seed)
-    k = rng.standard_normal((rows, Hkv, S + 1, D), dtype=np.float32).astype(np.float16)
-    v = rng.standard_normal((rows, Hkv, S + 1, D), dtype=np.float32).astype(np.float16)
-    q = rng.standard_normal((rows, Hq, D), dtype=np.float32).astype(np.float16)
-    tau = rng.uniform(0.8, 1.2, Hq).astype(np.float32)
-    ctx = np.full(rows, S + 1, np.int32)
+    kind = wl["kind"]
+    rows = per_layer[0]["q"].shape[0]
+    ctx = np.full(rows, wl["S"] + 1, np.int32)
     sm = 1.0 / np.sqrt(D)
-    extra = {}
-    if kind == "int4_asym":
-        pk, sk, zk = CO.quant_int4_asym(k, GS)
-        pv, sv, zv = CO.quant_int4_asym(v, GS)
-        fmt, extra = 2, dict(kz=zk, vz=zv)
-        append = lambda: (CO.quant_int4_asym(k[:, :, -1:], GS), CO.quant_int4_asym(v[:, :, -1:], GS))
-    elif kind.startswith("int8"):
-        tab = np.full((Hkv, G), 4.5 / 127, np.float16)
-        pk, sk = CO.quant_int8_static(k, tab, GS)
-        pv, sv = CO.quant_int8_static(v, tab, GS)
-        fmt = 1
-        append = lambda: (CO.quant_int8_static(k[:, :, -1:], tab, GS), CO.quant_int8_static(v[:, :, -1:], tab, GS))
-    else:
-        idx = np.stack([np.sort(rng.permutation(D)[:n_out]) for _ in range(Hkv)]).astype(np.int16)
-        tab = np.full((Hkv, G), 4.5 / 7, np.float32)
-        bk, sidek = O.split_outliers(k, idx)
-        bv, sidev = O.split_outliers(v, idx)
-        pk, sk = CO.quant_int4_static(bk, tab, GS)
-        pv, sv = CO.quant_int4_static(bv, tab, GS)
-        fmt, extra = 2, dict(kside=sidek, vside=sidev, outlier_idx=idx)
-        append = lambda: (CO.quant_int4_static(bk[:, :, -1:], tab, GS), CO.quant_int4_static(bv[:, :, -1:], tab, GS))
-
-    def one_pass():
-        append()
-        return CO.decode_attn(fmt, q, pk, pv, sk, sv, ctx, sm, inv_tau=tau, **extra)
-
-    one_pass()
+    tab8 = np.full((wl["Hkv"], G), 4.5 / 127, np.float16)
+    tab4 = np.full((wl["Hkv"], G), 4.5 / 7, np.float32)
     t0 = time.perf_counter()
-    n = 0
-    while True:
-        one_pass()
-        n += 1
-        el = time.perf_counter() - t0
-        if el >= target_s or n >= 50:
+    for d in per_layer:
+        if kind.startswith("int8"):
+            CO.quant_int8_static(d["k_new"], tab8, GS); CO.quant_int8_static(d["v_new"], tab8, GS)
+        elif kind in ("int4_asym", "kivi4"):
+            CO.quant_int4_asym(d["k_new"], GS); CO.quant_int4_asym(d["v_new"], GS)
+        elif kind == "int4_outlier":
+            CO.quant_int4_static(d["k_new"], tab4, GS); CO.quant_int4_static(d["v_new"], tab4, GS)
+        extra = {k: d[k] for k in ("kz", "vz", "kside", "vside", "outlier_idx") if k in d}
+        CO.decode_attn(d["fmt"], d["q"], d["k"], d["v"], d["ks"], d["vs"], ctx, sm, inv_tau=tau, **extra)
+    return time.perf_counter() - t0
+
+
+def cpu_plan(wl):
+    """How much of the workload one CPU pass covers: whole layers with all batch rows; as many layers as keep the
+    host arrays under ~3 GB (every layer of a small stack, one layer of the 64 GB one).  Returns (layers, factor):
+    step time = pass time x factor."""
+    per_layer_bytes = wl["B"] * wl["Hkv"] * (wl["S"] + 1) * bytes_per_token_head(wl["kind"], wl["n_out"])
+    layers = max(1, min(wl["layers"], int(3e9 // max(per_layer_bytes, 1))))
+    return layers, wl["layers"] / layers
+
+
+def cpu_baseline(wl, passes=3, budget_s=25.0):
+    """`cpu_baseline` object of the JSON line: the CPU oracle on whole layers of this workload (all batch rows, full
+    context), inputs built once, `passes` timed passes (fewer if the budget runs out), scaled by layers only."""
+    from oracle import c_oracle as CO
+    layers, factor = cpu_plan(wl)
+    per_layer, tau = cpu_inputs(wl, wl["B"], layers)
+    cpu_pass(wl, per_layer[:1], tau)                                   # load the library, touch the pages
+    times, t_start = [], time.perf_counter()
+    for _ in range(passes):
+        times.append(cpu_pass(wl, per_layer, tau))
+        if time.perf_counter() - t_start > budget_s:
             break
-    return el / n, rows, CO.num_threads()
+    step_s = statistics.median(times) * factor
+    return {"value": wl["B"] / step_s, "unit": "tokens/s", "cores": CO.num_threads(), "kind": "port",
+            "ms_per_step": step_s * 1e3,
+            "sample": (f"C restatement of the reference's torch decode path (OpenMP): {layers} of {wl['layers']} layers, "
+                       f"all {wl['B']} sequences at the full context, quantize-append + decode attention, "
+                       f"{len(times)} passes of {statistics.median(times) * 1e3:.0f} ms, inputs built once outside them; "
+                       + ("the whole step, no extrapolation" if layers == wl["layers"]
+                          else f"step = pass x {factor:g} (layers only)"))}
 
 
-def run_reference_arm(args, wl):
+def workload_config(wl, name, n_gpus=1):
+    """The `config` object; identical for both arms of a run (repo and reference)."""
+    big = wl["layers"] * wl["B"] * wl["Hkv"] * wl["S"] * bytes_per_token_head(wl["kind"], wl["n_out"]) > 126e6
+    par = ("single GPU" if n_gpus == 1 else
+           f"one long sequence sharded by KV chunks x{n_gpus}" if wl["B"] == 1 else
+           f"fixed batch of {wl['B']} sharded by sequence x{n_gpus}")
+    return {"workload": wl["desc"], "name": name, "layers": wl["layers"], "batch": wl["B"], "context": wl["S"],
+            "group_size": GS, "parallelism": par,
+            "l2": "inputs larger than L2 (the KV stack cycles through all layers)" if big
+            else "L2 flushed between timed iterations by a 256 MB write"}
+
+
+def run_reference_arm(args, name, wl):
+    """`--impl reference`: the reference's CPU path (C restatement of its torch dequantize-then-attention decode, all
+    host threads) on the repo arm's workload.  Rank 0 alone runs it; every step is one pass over whole layers."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -484,57 +575,248 @@ def run_reference_arm(args, wl):
         # the multi-process launcher pins every rank to one OpenMP thread; this arm runs on rank 0 alone and
         # uses the host's cores (the setting is read when the OpenMP runtime of the C oracle starts)
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
-    per_pass, rows, threads = cpu_sample(wl, target_s=2.0)          # warm-up + calibration
-    times = []
+    from oracle import c_oracle as CO
+    layers, factor = cpu_plan(wl)
+    per_layer, tau = cpu_inputs(wl, wl["B"], layers)
+    cpu_pass(wl, per_layer[:1], tau)
     for _ in range(max(args.warmup, 0)):
-        cpu_sample(wl, target_s=0.0)
-    for _ in range(args.steps):
-        t, rows, threads = cpu_sample(wl, target_s=0.0)
-        times.append(t)
-    per_pass = statistics.mean(times) if times else per_pass
-    # extrapolate the sample (1 layer x rows sequences) linearly to the full step
-    step_s = per_pass * wl["layers"] * (wl["B"] / rows)
-    value = wl["B"] * args.gpus / step_s if False else wl["B"] / step_s
-    sample = (f"1 of {wl['layers']} layers x {rows} of {wl['B']} sequences at full context, "
-              f"quantize-append + decode attention; extrapolated linearly to the full step")
+        cpu_pass(wl, per_layer, tau)
+    times = [cpu_pass(wl, per_layer, tau) for _ in range(max(args.steps, 1))]
+    step_s = statistics.mean(times) * factor
+    value = wl["B"] / step_s
+    sample = (f"{layers} of {wl['layers']} layers, all {wl['B']} sequences at the full context per step, quantize-append "
+              f"+ decode attention, inputs built once outside the timed passes; "
+              + ("the whole decode step, no extrapolation" if layers == wl["layers"]
+                 else f"ms_per_step = pass x {factor:g} (layers only; the 64 GB stack does not fit the host arrays)"))
     line = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic", "config": workload_config(wl, args.workload),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": workload_config(wl, name, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": CO.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "pass_ms": [t * 1e3 for t in times],
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(wl, name):
-    return {"workload": wl["desc"], "name": name, "layers": wl["layers"], "batch_per_gpu": wl["B"],
-            "context": wl["S"], "group_size": GS, "l2": "inputs larger than L2 (KV stack cycles through all layers)"
-            if wl["layers"] * wl["B"] * wl["Hkv"] * wl["S"] * bytes_per_token_head(wl["kind"], wl["n_out"]) > 126e6
-            else "L2 flushed between timed iterations by a 256 MB write"}
+# --------------------------------------------------------------------------- one workload on this rank's GPU
+def hbm_peak():
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        return float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback"
 
+
+PROFILE_OF = {"int8_dyn": "profiles/decode_split_mma_int8_c4.md", "int8_static": "profiles/decode_split_mma_int8_c4.md",
+              "int4_asym": "profiles/decode_split_int4_c2.md", "int4_outlier": "profiles/decode_split_int4_c3_c5.md",
+              "fp16": "profiles/decode_split_mma_fp16_c2shape.md", "kivi4": "profiles/decode_split_int4_c2.md"}
+
+
+def parity_check(wl, cache, q, inv_tau, out0, rows):
+    """Layer 0 of the step that was just timed against the CPU oracle on the batch rows `rows` (context S + 1)."""
+    import numpy as np
+    import torch
+    from oracle import c_oracle as CO
+    S, kind = wl["S"], wl["kind"]
+    b = cache._bufs[0]
+    idx = torch.as_tensor(rows, device=q.device)
+
+    def host(name):
+        t = b.get(name)
+        return None if t is None else t[idx, :, :S + 1].contiguous().cpu().numpy()
+    fmt = 0 if kind == "fp16" else 1 if kind.startswith("int8") else 2
+    extra = {}
+    if kind == "int4_asym":
+        extra = dict(kz=host("kz"), vz=host("vz"))
+    elif kind == "int4_outlier":
+        extra = dict(kside=host("kside"), vside=host("vside"), outlier_idx=cache.outlier_idx[0].cpu().numpy())
+    ref = CO.decode_attn(fmt, q[0][idx].cpu().numpy(), host("k"), host("v"), host("ks"), host("vs"),
+                         np.full(len(rows), S + 1, np.int32), 1.0 / np.sqrt(D), inv_tau=inv_tau[0].cpu().numpy(),
+                         **extra).astype(np.float32)
+    got = out0[idx].float().cpu().numpy()
+    err = np.abs(got - ref)
+    ok = bool(np.isfinite(got).all() and (err <= 2e-3 + 1e-2 * np.abs(ref)).all())
+    return {"max_abs": float(err.max()), "ok": ok, "rows": [int(r) for r in rows], "layer": 0,
+            "tolerance": "|a-b| <= 2e-3 + 1e-2 |b| against the CPU restatement of the reference's torch path"}
+
+
+def measure_workload(name, wl, args, dev, dist, rank, world, *, e2e=True, cpu=False, parity=True):
+    """Builds this rank's share of the workload and measures it: the decode step (graph), the split-K scan alone
+    (graph; both dequantisation arithmetics for packed INT4), the host-buffer end-to-end step, clocks, parity."""
+    import torch
+    from llm_kvcache_quantization_b200 import ops
+    from llm_kvcache_quantization_b200.parallel import batch_shard
+    wl = dict(wl)
+    B_total = wl["B"]
+    if world > 1:
+        lo, hi = batch_shard(B_total, rank, world)
+        wl["B"] = hi - lo
+    L, B, Hq, Hkv, S, kind, n_out = (wl[k] for k in ("layers", "B", "Hq", "Hkv", "S", "kind", "n_out"))
+    res = {"name": name, "config": workload_config(dict(wl, B=B_total), name, world), "batch_per_gpu": B}
+    free, _ = torch.cuda.mem_get_info()
+    need = L * B * Hkv * (S + 64) * bytes_per_token_head(kind, n_out) * (1.1 if kind != "kivi4" else 1.6) + (3 << 30)
+    short, = allreduce_max([1.0 if free < need else 0.0], dev, dist)      # every rank takes the same branch
+    if short:
+        res["skipped"] = f"needs {need / 2**30:.0f} GiB of device memory, {free / 2**30:.0f} GiB free"
+        return res
+    cache, q, k_new, v_new, inv_tau = build_workload(wl, dev, seed=1234 + rank, extra_slots=64)
+    out = torch.empty(L, B, Hq, D, dtype=torch.float16, device=dev)
+    small = L * B * Hkv * S * bytes_per_token_head(kind, n_out) <= 126e6
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
+
+    step, splits_fn = make_step(wl, cache, q, k_new, v_new, inv_tau, out)
+    g_step = capture(step)
+    splits = splits_fn()
+    int4 = kind in ("int4_asym", "int4_outlier")
+    scans = {}
+    for arm, env in (("default", None), ("bit_faithful", "0")) if int4 else (("default", None),):
+        old = os.environ.get("KVQ_INT4_FAST")
+        if env is not None:
+            os.environ["KVQ_INT4_FAST"] = env
+        try:
+            fn, _ = make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=1, with_append=False)
+            scans[arm] = capture(fn)
+        finally:
+            if env is not None:
+                if old is None:
+                    os.environ.pop("KVQ_INT4_FAST", None)
+                else:
+                    os.environ["KVQ_INT4_FAST"] = old
+
+    def run_block(graph):
+        def block(steps):
+            if flush is None:
+                return time_graph(graph, steps, dist)
+            tot = 0.0
+            for _ in range(steps):
+                flush.fill_(1)
+                tot += time_graph(graph, 1, dist)
+            return tot
+        return block
+
+    for gph in [g_step] + list(scans.values()):
+        run_block(gph)(args.warmup)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    step_ms = timed_blocks(run_block(g_step), args.steps, args.min_seconds, dist, dev)
+    scan_ms = {arm: timed_blocks(run_block(gph), args.steps, args.min_seconds, dist, dev) for arm, gph in scans.items()}
+    clocks = sampler.stop()
+    clocks["window"] = "the timed regions of the decode step and of the split-K scans"
+    n_steps_timed = len(step_ms) * args.steps
+    med, mn = allreduce_max([statistics.median(step_ms), min(step_ms)], dev, dist)
+    res.update(ms_per_step=med, ms_per_step_min=mn, blocks=len(step_ms), us_per_layer=med * 1e3 / L,
+               value=B_total / (med * 1e-3), unit="tokens/s", splits=splits, clocks=clocks,
+               gpu_launches=n_steps_timed * L * 3,
+               step=f"CUDA graph of {L}x(quantize-append || split-K scan of the old tokens, then combine incl. the new token)")
+
+    peak, peak_src = hbm_peak()
+    alg_bytes = B * Hkv * (S + 1) * bytes_per_token_head(kind, n_out)
+
+    def roof(ms_list, what):
+        m, lo_ = allreduce_max([statistics.median(ms_list), min(ms_list)], dev, dist)
+        us = m * 1e3 / L
+        ach = alg_bytes / (us * 1e-6) / 1e9
+        return {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                "traffic": alg_bytes * NCU_TRAFFIC_RATIO.get(kind, 1.0),
+                "traffic_source": f"algorithmic bytes x {NCU_TRAFFIC_RATIO.get(kind, 1.0)}: a stored constant, the ratio "
+                                  f"dram bytes / algorithmic bytes of one ncu capture of this kernel ({PROFILE_OF.get(kind)}), "
+                                  "not a measurement of this run",
+                "peak_source": peak_src, "kernel": what, "us_per_launch": us, "us_per_launch_min": lo_ * 1e3 / L,
+                "algorithmic_bytes_per_launch": alg_bytes, "frac_of_8TBps": ach / 8000.0,
+                "timed": f"{len(ms_list)} blocks of {args.steps} graph replays of the {L} scans, CUDA events, per GPU"}
+    res["roofline"] = roof(scan_ms["default"], "decode split-K scan" + (" (packed INT4, factored scales: library default)" if int4 else ""))
+    if "bit_faithful" in scan_ms:
+        res["roofline_bit_faithful"] = roof(scan_ms["bit_faithful"],
+                                            "decode split-K scan (packed INT4, fp16 dequantisation bit for bit as the reference's torch path)")
+
+    if parity and kind != "kivi4":
+        g_step.replay()
+        torch.cuda.synchronize()
+        rows = sorted({0, B - 1})
+        try:
+            res["parity_check"] = parity_check(wl, cache, q, inv_tau, out[0], rows)
+        except Exception as e:      # the oracle library is test infrastructure: its absence must not hide the numbers
+            res["parity_check"] = {"ok": None, "error": repr(e)[:200]}
+
+    # end to end through the public API with HOST buffers: every step uploads this token's q / k / v
+    # for all layers from pinned memory, replays the captured whole-stack step (append + attention per
+    # layer, device-side position counter, the cache grows by one token) and downloads the outputs
+    if e2e and kind != "kivi4":
+        from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
+        stepper = GraphedKVStackStep(cache, Hq, 1.0 / D ** 0.5, inv_tau=inv_tau)
+        stepper.capture()
+        stepper.host_q.copy_(q.cpu()); stepper.host_k.copy_(k_new.cpu()); stepper.host_v.copy_(v_new.cpu())
+        room = stepper.capacity - stepper._len - 1
+        for _ in range(3):
+            stepper.step(stepper.host_q, stepper.host_k, stepper.host_v)
+        room -= 3
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def e2e_block(steps):
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(steps):
+                r = stepper.step(stepper.host_q, stepper.host_k, stepper.host_v)
+            e1.record()
+            torch.cuda.synchronize()
+            assert bool(torch.isfinite(r.float()).all())
+            return e0.elapsed_time(e1)
+        # the cache grows by one token per step: as many blocks as the reserved slots allow, at least one
+        nb = max(1, min(int(room // max(args.steps, 1)), 200))
+        ems, tot = [], 0.0
+        for _ in range(nb):
+            ms, = allreduce_max([e2e_block(args.steps)], dev, dist)
+            ems.append(ms / args.steps)
+            tot += ms
+            if tot >= args.min_seconds * 1e3:
+                break
+        em, = allreduce_max([statistics.median(ems)], dev, dist)
+        res["e2e"] = {"value": B_total / (em * 1e-3), "unit": "tokens/s",
+                      "h2d_bytes_per_step": stepper.h2d_bytes_per_step * world,
+                      "d2h_bytes_per_step": stepper.d2h_bytes_per_step * world, "ms_per_step": em, "blocks": len(ems),
+                      "api": "GraphedKVStackStep.step(host_q, host_k, host_v) -> host_out: one CUDA graph launch holding the "
+                             "pinned H2D copies of q/k/v, append + attention for every layer, and the pinned D2H of the "
+                             "outputs; stream sync"}
+        del stepper
+
+    if args.aux and kind not in ("fp16", "kivi4") and world == 1:
+        res["aux"] = time_aux(wl, cache, dev)
+    if args.model_step and world == 1 and (Hq, Hkv) in MODEL_GEOMETRY:
+        try:
+            res["model_step"] = time_model_step(wl, cache, dev, steps=max(3, min(args.steps, 10)))
+        except Exception as e:
+            res["model_step"] = {"error": repr(e)[:300]}
+    if cpu and rank == 0 and kind not in ("fp16", "kivi4"):
+        try:
+            res["cpu_baseline"] = cpu_baseline(dict(wl, B=B_total))
+        except Exception as e:
+            res["cpu_baseline"] = {"error": repr(e)[:300]}
+    del g_step, scans, cache, q, k_new, v_new, out, flush
+    ops.release_workspaces()
+    torch.cuda.empty_cache()
+    return res
 
 
 # --------------------------------------------------------------------------- sequence sharding (one long sequence)
-def run_sequence_sharded(args, wl, dev, dist, rank, world):
+def run_sequence_sharded(args, wl, dev, dist, rank, world, collective):
     """KV-sequence sharding of a single long sequence over `world` GPUs: rank r owns a contiguous
     chunk of tokens, the owner of position S appends the new token, every rank runs the fused
-    decode over its chunk into a packed normalised partial, ONE NCCL all-gather per layer moves the
-    partials, and every rank merges them.  The whole step (kernels and collectives) is one CUDA graph."""
+    decode over its chunk into a packed normalised partial, the partials cross NVLink once per layer
+    (the library's fused combine / peer-store / merge kernel, or ONE NCCL all-gather), and every rank merges
+    them.  The whole step (kernels and collectives) is one CUDA graph.  Returns the result object (rank 0)."""
     import torch
     from llm_kvcache_quantization_b200 import ops, _lib, parallel as P
 
     L, B, Hq, Hkv, S, kind, n_out = (wl[k] for k in ("layers", "B", "Hq", "Hkv", "S", "kind", "n_out"))
-    sh = P.SequenceSharding(world=world, max_seq_len=S + 1)
-    lo, hi = sh.token_range(rank)
+    sh = P.SequenceSharding(world=world, max_seq_len=S + 1, align=128)
     n_old = sh.local_len(rank, S)                    # cached tokens of this rank before the step
     owner = sh.owner_of(S) == rank                   # this rank stores the new token
     n_att = n_old + (1 if owner else 0)
     local = dict(wl, S=n_old)
-    # same seed on every rank for q / k_new / v_new would need a shared generator; the inputs of a step are
-    # replicated in a real deployment, here rank 0's are broadcast
+    # the inputs of a step are replicated in a real deployment; here rank 0's are broadcast
     cache, q, k_new, v_new, inv_tau = build_workload(local, dev, seed=1234 + rank, extra_slots=8)
     for t in (q, k_new, v_new, inv_tau):
         dist.broadcast(t, src=0)
@@ -543,7 +825,7 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
     send = torch.empty(B, Hq, D + 2, dtype=torch.float32, device=dev)
     recv = torch.empty(world, B, Hq, D + 2, dtype=torch.float32, device=dev)
     P.check_partial_shapes(send.shape)
-    fused = args.collective == "fused"
+    fused = collective == "fused"
     xchg = P.PeerExchange(B, Hq, D, slots=L) if fused else None
     layers = []
     for l in range(L):
@@ -576,7 +858,7 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
                                  v_side=tens["vside"][:, :, :n_att])
                 ops.decode_attn(fmt, q[l], tens["k"][:, :, :n_att], tens["v"][:, :, :n_att], tens["ks"][:, :, :n_att],
                                 tens["vs"][:, :, :n_att], None, 1.0 / D ** 0.5, head_dim=D, inv_tau=inv_tau[l],
-                                out=out[l], stages=1, **extra)
+                                out=out[l], stages=1, tail_tokens=1, **extra)
                 continue
             do_append = None
             if owner:
@@ -596,130 +878,73 @@ def run_sequence_sharded(args, wl, dev, dist, rank, world):
     splits = ops.last_splits()
     g_scan = capture(lambda: step(scan_only=True))
     time_graph(g_step, args.warmup, dist)
-    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
-    sampler.start()
-    ms = time_graph(g_step, args.steps, dist)
-    time_graph(g_scan, 3, dist)
-    ms_scan = time_graph(g_scan, args.steps, dist)
-    t_end = time.time() + 0.4                   # keep the scans running while the clock sampler is still on
-    while time.time() < t_end:
-        for _ in range(5):
-            g_scan.replay()
-        torch.cuda.synchronize()
-    clocks = sampler.stop()
-    clocks["window"] = "timed region + 0.4 s of split-K scans"
-
-    # end to end with host buffers: upload q / k / v of the token, replay, download the merged output
-    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k_new, v_new))
-    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-
-    def host_step():
-        q.copy_(hq, non_blocking=True); k_new.copy_(hk, non_blocking=True); v_new.copy_(hv, non_blocking=True)
-        g_step.replay()
-        hout.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-    for _ in range(3):
-        host_step()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dist.barrier(); torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        host_step()
-    e1.record(); torch.cuda.synchronize()
-    t = torch.tensor([ms, ms_scan, e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_scan, ems = (float(x) for x in t)
-    ms_per_step = ms / args.steps
-
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    else:
-        peak, peak_src = 6650.0, "fallback"
+    time_graph(g_scan, args.warmup, dist)
+    step_ms = timed_blocks(lambda n: time_graph(g_step, n, dist), args.steps, args.min_seconds, dist, dev)
+    scan_ms = timed_blocks(lambda n: time_graph(g_scan, n, dist), args.steps, args.min_seconds, dist, dev)
+    ms, ms_min, sc = allreduce_max([statistics.median(step_ms), min(step_ms), statistics.median(scan_ms)], dev, dist)
+    peak, peak_src = hbm_peak()
     alg_bytes = B * Hkv * sh.chunk * bytes_per_token_head(kind, n_out)       # the largest shard
-    scan_us = ms_scan / (args.steps * L) * 1e3
+    scan_us = sc * 1e3 / L
     achieved = alg_bytes / (scan_us * 1e-6) / 1e9
-    if rank == 0:
-        line = {
-            "metric": "decode_tokens_per_s", "value": B / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": dict(workload_config(wl, args.workload), parallelism=f"sequence-sharded x{world}",
-                           chunk_tokens=sh.chunk, splits=splits,
-                           collective=("fused kernel: combine + peer stores of [B,Hq,D+2] fp32 over NVLink + merge, "
-                                       "one launch per layer" if fused else
-                                       "one NCCL all-gather of [B,Hq,D+2] fp32 per layer"),
-                           step=(f"CUDA graph of {L}x(append on the owner, split-K scan, fused combine/exchange/merge)"
-                                 if fused else
-                                 f"CUDA graph (kernels + NCCL all-gather) of {L}x(append on the owner, split-K scan, "
-                                 "combine, all-gather, merge)"),
-                           exchange_status=(int(xchg.status.item()) if fused else None)),
-            "us_per_layer": ms_per_step * 1e3 / L,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": alg_bytes * NCU_TRAFFIC_RATIO.get(kind, 1.0),
-                         "traffic_source": "ncu capture of the same kernel (profiles/), scaled by token-heads",
-                         "peak_source": peak_src, "kernel": "decode split-K scan (largest shard, per GPU)",
-                         "us_per_launch": scan_us, "algorithmic_bytes_per_launch": alg_bytes,
-                         "frac_of_8TBps": achieved / 8000.0},
-            "cpu_baseline": None,
-            "e2e": {"value": B / (ems / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": (q.numel() + k_new.numel() + v_new.numel()) * 2,
-                    "d2h_bytes_per_step": out.numel() * 2, "ms_per_step": ems / args.steps,
-                    "api": "pinned H2D of q/k/v on every rank, one CUDA graph (sharded_decode per layer), pinned D2H"},
-            "gpu_launches": args.steps * L * (3 if fused else 4), "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
-    # Tearing the process group down while captured graphs still hold its collectives did not return in a
-    # two-GPU run: drain, agree that every rank is done, drop the graphs, and leave without the teardown.
-    torch.cuda.synchronize()
-    dist.barrier()
-    del g_step, g_scan
-    torch.cuda.synchronize()
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+    status = int(xchg.status.item()) if fused else None
+    res = {"collective": ("fused kernel: combine + peer stores of [B,Hq,D+2] fp32 over NVLink + merge, one launch per layer"
+                          if fused else "one NCCL all-gather of [B,Hq,D+2] fp32 per layer, then the merge kernel"),
+           "ms_per_step": ms, "ms_per_step_min": ms_min, "blocks": len(step_ms), "us_per_layer": ms * 1e3 / L,
+           "tokens_per_s": B / (ms * 1e-3), "chunk_tokens": sh.chunk, "splits": splits, "exchange_status": status,
+           "scan_us_per_layer": scan_us, "scan_frac_of_measured_hbm": achieved / peak, "peak_source": peak_src,
+           "gpu_launches": len(step_ms) * args.steps * L * (3 if fused else 4)}
+    del g_step, g_scan, xchg, cache
+    ops.release_workspaces()
+    torch.cuda.empty_cache()
+    return res
 
 
 # --------------------------------------------------------------------------- main
+EXTRA_WORKLOADS = ("c1", "c2", "c3", "c5", "c2_kivi4")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS),
+                    help="headline workload (default: configuration 4, the largest that fits one GPU)")
+    ap.add_argument("--min-seconds", type=float, default=0.5, help="minimum length of every timed region")
+    ap.add_argument("--no-extras", action="store_true", help="measure the headline workload only")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
     ap.add_argument("--aux", action="store_true",
-                    help="also time the neighbouring kernels at this workload's shape: bulk prefill quantize-append "
+                    help="also time the neighbouring kernels at the headline shape: bulk prefill quantize-append "
                          "(T = context) and the dequantising get_kv, one layer each")
     ap.add_argument("--model-step", action="store_true",
-                    help="also time one decode step of a random-init Qwen2 model of the workload's geometry through "
+                    help="also time one decode step of a random-init Qwen2 model of the headline geometry through "
                          "the patched attention forward over the same synthetic cache (weights, MLP, eager Python "
                          "included); reported under model_step")
-    ap.add_argument("--collective", default="fused", choices=("fused", "nccl"),
-                    help="sequence-sharded mode: the library's fused combine/peer-store/merge kernel, or "
-                         "combine + NCCL all-gather + merge")
+    ap.add_argument("--collective", default="both", choices=("both", "fused", "nccl"),
+                    help="sequence-sharded sub-result: the library's fused combine/peer-store/merge kernel, "
+                         "combine + NCCL all-gather + merge, or both")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.layers > 0:
         wl["layers"] = args.layers
         wl["desc"] += f" [layers overridden to {args.layers}]"
+        args.no_extras = True
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":
-        run_reference_arm(args, wl)
+        run_reference_arm(args, args.workload, wl)
         return
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    # the fused exchange uses plain peer stores; symmetric-memory buffers are not bound to an NVLink multicast object
-    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    # the fused exchange uses plain peer stores; symmetric-memory buffers are never bound to an NVLink multicast object
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
     import torch
-    import llm_kvcache_quantization_b200 as kvq
-    from llm_kvcache_quantization_b200 import ops
+    import llm_kvcache_quantization_b200 as kvq  # noqa: F401
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist = None
@@ -730,141 +955,87 @@ def main():
         # a collective that a peer never joins ends with an error after two minutes instead of waiting forever
         dist_mod.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
         dist = dist_mod
+    t_start = time.time()
 
-    if world > 1 and wl["B"] == 1:
-        run_sequence_sharded(args, wl, dev, dist, rank, world)
-        return
+    head = measure_workload(args.workload, wl, args, dev, dist, rank, world, e2e=not args.no_e2e,
+                            cpu=not args.no_cpu_baseline and world == 1)
+    if "skipped" in head and args.workload == "c4":
+        # a GPU with less free memory than the 64 GB stack needs: fall back to the next largest configuration
+        note = head["skipped"]
+        args.workload, wl = "c3", dict(WORKLOADS["c3"])
+        head = measure_workload("c3", wl, args, dev, dist, rank, world, e2e=not args.no_e2e,
+                                cpu=not args.no_cpu_baseline and world == 1)
+        head["headline_fallback"] = f"configuration 4 skipped ({note})"
 
-    L, B, Hq, Hkv, S = wl["layers"], wl["B"], wl["Hq"], wl["Hkv"], wl["S"]
-    e2e_slots = args.steps + args.warmup + 8 + (64 if args.model_step else 0)
-    cache, q, k_new, v_new, inv_tau = build_workload(wl, dev, seed=1234 + rank, extra_slots=e2e_slots)
-    out = torch.empty(L, B, Hq, D, dtype=torch.float16, device=dev)
-    small = L * B * Hkv * S * bytes_per_token_head(wl["kind"], wl["n_out"]) <= 126e6
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
-
-    step, splits_fn = make_step(wl, cache, q, k_new, v_new, inv_tau, out)
-    g_step = capture(step)
-    splits = splits_fn()
-    split_only, _ = make_step(wl, cache, q, k_new, v_new, inv_tau, out, stages=1, with_append=False)
-    g_split = capture(split_only)
-
-    def timed(graph, iters):
-        if flush is None:
-            return time_graph(graph, iters, dist)
-        tot = 0.0
-        for _ in range(iters):
-            flush.fill_(1)
-            tot += time_graph(graph, 1, dist)
-        return tot
-
-    timed(g_step, args.warmup)
-    sampler = ClockSampler(local)
-    sampler.start()
-    ms = timed(g_step, args.steps)
-    # dominant kernel alone (split-K scan), same clocks window
-    timed(g_split, 3)
-    ms_split = timed(g_split, args.steps)
-    # the timed region lasts a few milliseconds - shorter than the sampling period of nvidia-smi - so the same
-    # step keeps running for another 0.4 s (untimed) while the clock sampler is still on
-    t_end = time.time() + 0.4
-    while time.time() < t_end:
-        for _ in range(20):
-            g_step.replay()
-        torch.cuda.synchronize()
-    clocks = sampler.stop()
-    clocks["window"] = "timed region + 0.4 s of the same step"
-    if dist is not None:
-        t = torch.tensor([ms, ms_split], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_split = float(t[0]), float(t[1])
-    ms_per_step = ms / args.steps
-    value = world * B / (ms_per_step * 1e-3)
-
-    # roofline of the dominant kernel
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    else:
-        peak, peak_src = 6650.0, "fallback"
-    alg_bytes = B * Hkv * (S + 1) * bytes_per_token_head(wl["kind"], wl["n_out"])
-    split_us = ms_split / (args.steps * L) * 1e3
-    achieved = alg_bytes / (split_us * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": alg_bytes * NCU_TRAFFIC_RATIO.get(wl["kind"], 1.0),
-                "traffic_source": "ncu capture of the same kernel on this shape (profiles/), scaled by token-heads",
-                "peak_source": peak_src, "kernel": "decode split-K scan",
-                "us_per_launch": split_us, "algorithmic_bytes_per_launch": alg_bytes,
-                "frac_of_8TBps": achieved / 8000.0}
-
-    # end to end through the public API with HOST buffers: every step uploads this token's q / k / v
-    # for all layers from pinned memory, replays the captured whole-stack step (append + attention per
-    # layer, device-side position counter, the cache grows by one token) and downloads the outputs
-    e2e = None
-    if not args.no_e2e and wl["kind"] != "kivi4":      # the host-buffer stepper serves the group-wise caches
-        from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
-        stepper = GraphedKVStackStep(cache, Hq, 1.0 / D ** 0.5, inv_tau=inv_tau)
-        stepper.capture()
-        stepper.host_q.copy_(q.cpu()); stepper.host_k.copy_(k_new.cpu()); stepper.host_v.copy_(v_new.cpu())
-        for _ in range(3):
-            stepper.step(stepper.host_q, stepper.host_k, stepper.host_v)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(args.steps):
-            res = stepper.step(stepper.host_q, stepper.host_k, stepper.host_v)
-        e1.record()
-        torch.cuda.synchronize()
-        ems = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([ems], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ems = float(t[0])
-        assert bool(torch.isfinite(res.float()).all())
-        e2e = {"value": world * B / (ems / args.steps * 1e-3), "unit": "tokens/s",
-               "h2d_bytes_per_step": stepper.h2d_bytes_per_step, "d2h_bytes_per_step": stepper.d2h_bytes_per_step,
-               "ms_per_step": ems / args.steps,
-               "api": "GraphedKVStackStep.step(host_q, host_k, host_v) -> host_out: one CUDA graph launch holding the "
-                      "pinned H2D copies of q/k/v (first layers, then the rest beside their kernels), append + attention "
-                      "for every layer, and the pinned D2H of the outputs (all but the last layers beside the last "
-                      "layers' kernels, then the tail); stream sync"}
-
-    aux = None
-    if args.aux and wl["kind"] not in ("fp16", "kivi4"):
-        aux = time_aux(wl, cache, dev)
-
-    model_step = None
-    if args.model_step and world == 1:
-        model_step = time_model_step(wl, cache, dev, steps=max(3, min(args.steps, 10)))
-
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and wl["kind"] not in ("fp16", "kivi4"):
-        per_pass, rows, threads = cpu_sample(wl, target_s=12.0)
-        step_s = per_pass * L * (B / rows)
-        cpu = {"value": B / step_s, "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": f"1 of {L} layers x {rows} of {B} sequences at full context (C oracle, OpenMP), "
-                         f"{per_pass * 1e3:.1f} ms per pass, extrapolated linearly"}
+    extra = {}
+    if world == 1 and not args.no_extras:
+        if args.workload == "c4" and not args.model_step and (wl["Hq"], wl["Hkv"]) in MODEL_GEOMETRY:
+            pass    # the random-init 7B model step of configuration 4 is opt-in (--model-step): it adds ~1 minute
+        items = []
+        for name in EXTRA_WORKLOADS:
+            if name == args.workload:
+                continue
+            try:
+                r = measure_workload(name, dict(WORKLOADS[name]), args, dev, None, 0, 1, e2e=not args.no_e2e,
+                                     cpu=(name == "c2" and not args.no_cpu_baseline))
+            except Exception as e:
+                r = {"name": name, "error": repr(e)[:300]}
+            items.append(r)
+        extra["workloads"] = items
+    if world > 1 and not args.no_extras:
+        # configuration 5, one sequence of 131072 tokens: KV-sequence sharding over the same N GPUs, and the same step
+        # on one GPU (rank 0, the others wait) for the speed-up
+        c5 = dict(WORKLOADS["c5"])
+        seq = {"config": workload_config(c5, "c5", world)}
+        which = ("fused", "nccl") if args.collective == "both" else (args.collective,)
+        for coll in which:
+            # every rank runs the same calls; a failure on one rank surfaces on all through the collective's timeout
+            try:
+                seq[coll] = run_sequence_sharded(args, c5, dev, dist, rank, world, coll)
+            except Exception as e:
+                import traceback
+                traceback.print_exc()
+                seq[coll] = {"error": repr(e)[:300]}
+        if rank == 0:
+            try:
+                one = measure_workload("c5", c5, args, dev, None, 0, 1, e2e=False, parity=False)
+                seq["single_gpu_us_per_layer"] = one.get("us_per_layer")
+                for coll in which:
+                    if one.get("us_per_layer") and seq[coll].get("us_per_layer"):
+                        seq[coll]["speedup_over_one_gpu"] = one["us_per_layer"] / seq[coll]["us_per_layer"]
+            except Exception as e:
+                import traceback
+                traceback.print_exc()
+                seq["single_gpu_error"] = repr(e)[:300]
+        extra["sequence_sharded"] = seq
 
     if rank == 0:
         line = {
-            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": dict(workload_config(wl, args.workload), parallelism=f"batch-sharded x{world}", splits=splits,
-                           step=f"CUDA graph of {L}x(quantize-append || split-K scan of the old tokens, then combine "
-                                "incl. the new token)"),
-            "us_per_layer": ms_per_step * 1e3 / L,
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": args.steps * L * 3, "clocks": clocks,
+            "metric": "decode_tokens_per_s", "value": head.get("value"), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": head.get("ms_per_step"),
+            "ms_per_step_min": head.get("ms_per_step_min"), "timed_blocks": head.get("blocks"),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": head["config"], "batch_per_gpu": head.get("batch_per_gpu"), "splits": head.get("splits"),
+            "step": head.get("step"), "us_per_layer": head.get("us_per_layer"),
+            "roofline": head.get("roofline"), "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"),
+            "gpu_launches": head.get("gpu_launches"), "clocks": head.get("clocks"),
+            "parity_check": head.get("parity_check"),
         }
-        if aux is not None:
-            line["aux"] = aux
-        if model_step is not None:
-            line["model_step"] = model_step
+        for k in ("roofline_bit_faithful", "aux", "model_step", "headline_fallback", "skipped"):
+            if k in head:
+                line[k] = head[k]
+        if extra:
+            line["extra"] = extra
+        line["bench_seconds"] = time.time() - t_start
         print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.destroy_process_group()
+        # Tearing the process group down while captured graphs still hold its collectives did not return in a
+        # two-GPU run: drain, agree that every rank is done, and leave without the teardown.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
