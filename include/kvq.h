@@ -217,8 +217,12 @@ KVQ_API int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream);
  *  - Limit: B * Hq * splits * (D + 2) * 4 bytes must fit the array.  With `splits == 0` the
  *    library lowers its own split choice until it fits; if even one split does not fit, or an
  *    explicit `splits` is too large, the call returns KVQ_ELIMIT and launches nothing.
+ *    On a 148-SM part the library's own choice stays near 3 MB (<= 8 heads x resident CTAs x 520 bytes), so the
+ *    lowering is a guard for other parts; KVQ_STATIC_WS_LIMIT=<bytes> in the environment (read once) makes the
+ *    entry point use less of the array.
  *  - The first call on each device looks up the array's device address (with that device
- *    current) and caches it; make that first call outside any stream capture.
+ *    current) and caches it; make that first call outside any stream capture.  First calls from several
+ *    host threads at once are fine (they resolve and cache the same address).
  *  - All calls on a device share the one array and it keeps the previous call's partials.
  *    Nothing in it has to start at zero (every slot a call reads it has written first), but two
  *    calls that overlap on the GPU - different streams, or graphs replayed concurrently - race

@@ -3,6 +3,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+
+#include <atomic>
 #include <stdint.h>
 #include <stdlib.h>
 
@@ -857,20 +859,33 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
 static __device__ __align__(256) unsigned char g_static_workspace[KVQ_STATIC_WS_BYTES];
 
 static int static_workspace_ptr(void** out) {
-    static void* cached[64] = {nullptr};
+    // one slot per device; concurrent first calls from several host threads all resolve the same address and
+    // store the same value, so the relaxed atomics only keep the accesses well defined
+    static std::atomic<void*> cached[64];
     int dev = 0;
     int rc = kvq::check_cuda(cudaGetDevice(&dev));
     if (rc) return rc;
     if (dev < 0 || dev >= 64) return KVQ_EUNSUPPORTED;
-    if (!cached[dev]) {
-        void* p = nullptr;
+    void* p = cached[dev].load(std::memory_order_relaxed);
+    if (!p) {
         rc = kvq::check_cuda(cudaGetSymbolAddress(&p, g_static_workspace));
         if (rc) return rc;
         if (!p) return KVQ_ECUDA;
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_relaxed);
     }
-    *out = cached[dev];
+    *out = p;
     return KVQ_OK;
+}
+
+// Bytes of the array a call may use: all of it, or less when KVQ_STATIC_WS_LIMIT (bytes) says so - a host that
+// wants the partials to stay inside a slice of L2, or a test of the shrinking below.
+static size_t static_workspace_limit() {
+    static const size_t lim = [] {
+        const char* e = getenv("KVQ_STATIC_WS_LIMIT");
+        long long v = e ? atoll(e) : 0;
+        return (v > 0 && (size_t)v < (size_t)KVQ_STATIC_WS_BYTES) ? (size_t)v : (size_t)KVQ_STATIC_WS_BYTES;
+    }();
+    return lim;
 }
 
 extern "C" int kvq_decode_attn_static(const KvqAttnArgs* args, kvq_stream_t stream) {
@@ -882,16 +897,16 @@ extern "C" int kvq_decode_attn_static(const KvqAttnArgs* args, kvq_stream_t stre
     if (a.splits <= 0) {
         a.splits = kvq_decode_pick_splits(&a);
         // prefer fewer splits over refusing: shrink until the partials fit the fixed array
-        while (a.splits > 1 && kvq_decode_workspace_bytes(a.B, a.Hq, a.D, a.splits) > KVQ_STATIC_WS_BYTES) --a.splits;
+        while (a.splits > 1 && kvq_decode_workspace_bytes(a.B, a.Hq, a.D, a.splits) > static_workspace_limit()) --a.splits;
     }
     const size_t need = kvq_decode_workspace_bytes(a.B, a.Hq, a.D, a.splits);
     if (need == 0) return KVQ_EINVAL;
-    if (need > KVQ_STATIC_WS_BYTES) return KVQ_ELIMIT;       // B * Hq * splits * (D + 2) * 4 bytes > 8 MiB
+    if (need > static_workspace_limit()) return KVQ_ELIMIT;  // B * Hq * splits * (D + 2) * 4 bytes > 8 MiB (or the env limit)
     void* ws = nullptr;
     int rc = static_workspace_ptr(&ws);
     if (rc) return rc;
     a.workspace = ws;
-    a.workspace_bytes = KVQ_STATIC_WS_BYTES;
+    a.workspace_bytes = static_workspace_limit();
     return kvq_decode_attn(&a, stream);
 }
 
