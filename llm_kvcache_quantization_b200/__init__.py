@@ -10,7 +10,13 @@ Public surface (names follow the reference project):
 All compute runs in libkvq.so (CUDA, sm_100a).  There is no CPU fallback: the
 entry points raise if the library is missing or a tensor is not on a CUDA device.
 """
-from .cache import FP16KVCache, INT4KVCache, INT8KVCache
+import os as _os
+
+# The sequence-sharded exchange kernel moves data with plain peer stores; torch's symmetric-memory buffers must not
+# be bound to an NVLink multicast object.  Set before anything touches symmetric memory.
+_os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+
+from .cache import FP16KVCache, INT4KVCache, INT8KVCache  # noqa: E402
 from .kivi import KIVIStyleKVCache
 from .kernels import (decode_attn_fp16, decode_attn_int4, decode_attn_int4_asym,
                       decode_attn_int4_outlier, decode_attn_int8)

@@ -40,18 +40,27 @@ def _require_cuda(*tensors) -> torch.device:
     return dev
 
 
+_RETIRED = []      # outgrown workspaces: a CUDA graph captured earlier may still hold their addresses
+
+
 def get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Per-(device, stream) scratch buffer for split-K partials; grows, never shrinks."""
+    """Per-(device, stream) scratch buffer for split-K partials; grows, never shrinks.  A buffer that has been handed
+    out is never returned to the allocator while the process lives (unless `release_workspaces` is called): a CUDA
+    graph captured around an earlier call replays with the old address, which must stay ours."""
     key = (device.index, _stream_ptr(device))
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _RETIRED.append(buf)
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _WORKSPACES[key] = buf
     return buf
 
 
 def release_workspaces() -> None:
+    """Drop every scratch buffer.  Only when no captured graph that used them will be replayed again."""
     _WORKSPACES.clear()
+    _RETIRED.clear()
 
 
 _LAST_SPLITS = 0

@@ -129,10 +129,15 @@ class PeerExchange:
 
     def __init__(self, B: int, Hq: int, D: int, slots: int, group=None, device=None, wait_ns: int = 0):
         import os
+        # The exchange kernel uses plain peer stores.  Symmetric-memory buffers must never be bound to an NVLink
+        # multicast object: a rank that leaves while its memory is bound to one disturbs the other ranks' GPUs.
+        # The package sets the switch at import; refuse to go on if something turned it back on.
+        if os.environ.get("TORCH_SYMM_MEM_DISABLE_MULTICAST") != "1":
+            raise RuntimeError("PeerExchange needs TORCH_SYMM_MEM_DISABLE_MULTICAST=1 (set when this package is imported); "
+                               "it was changed afterwards")
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
         from . import ops
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)

@@ -18,6 +18,7 @@ def _free_port():
 
 
 def _worker(rank, world, port, ret):
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"     # plain peer stores only; nothing is bound to a multicast object
     import torch.distributed as dist
     import llm_kvcache_quantization_b200 as kvq
     from llm_kvcache_quantization_b200 import _lib, ops, parallel as P
@@ -62,6 +63,14 @@ def _worker(rank, world, port, ret):
             err = (out.float() - ref.float()).abs()
             ret["max_err"] = float(err.max())
             ret["ok"] = bool((err <= 2e-3 + 1e-2 * ref.float().abs()).all())
+            # and against the oracle itself (the reference's torch path restated), not only the one-GPU kernel
+            from oracle import kvq_oracle as O
+            ft = full.get_decode_tensors(0)
+            want = O.decode_attn_int4_outlier(q.numpy(), *(ft[n].cpu().numpy() for n in ("k", "v", "ks", "vs", "kside", "vside")),
+                                              idx.numpy(), [S + 1], 0.088, inv_tau=tau.numpy()).astype(np.float32)
+            oerr = np.abs(out.float().cpu().numpy() - want)
+            ret["oracle_max_err"] = float(oerr.max())
+            ret["oracle_ok"] = bool((oerr <= 2e-3 + 1e-2 * np.abs(want)).all())
         # the library's own exchange: combine + peer stores over NVLink + merge in one launch.  Five
         # steps reuse both parities of the receive buffer; the query changes every step.
         xchg = P.PeerExchange(B, Hq, D, slots=2)
@@ -106,5 +115,5 @@ def test_sequence_sharded_decode_two_gpus():
     world = 2
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-    assert ret.get("ok") is True, dict(ret)
+    assert ret.get("ok") is True and ret.get("oracle_ok") is True, dict(ret)
     assert ret.get("xchg_ok_0") is True and ret.get("xchg_ok_1") is True, dict(ret)
