@@ -57,6 +57,9 @@ extern "C" {
 
 /* flags for KVQ_SCALE_STATIC */
 #define KVQ_F_ADAPTIVE     1  /* s = max(static*margin, absmax/qmax)  (int8_cache.py:392-402, int4_cache.py:451-455) */
+#define KVQ_F_ADAPT_SKIP_K 16  /* with KVQ_F_ADAPTIVE: the K side keeps its plain static scale (adaptive_static_k=False) */
+#define KVQ_F_ADAPT_SKIP_V 32  /* with KVQ_F_ADAPTIVE: the V side keeps its plain static scale (adaptive_static_v=False);
+                                  the reference applies the rule to K and V independently (int8_cache.py:394, :427) */
 #define KVQ_F_MIXED_RESCUE 2  /* s = max(s, absmax/7)                 (int4_cache.py:456-459)                        */
 #define KVQ_F_RESCUE_THR   4  /* s = dyn >= *thr ? max(s,dyn) : s     (int4_cache.py:360-390)                        */
 #define KVQ_F_UNPACKED     8  /* KVQ_FMT_INT4 only: store one code per byte ([.., D] int8 in [-8, 7]) instead of

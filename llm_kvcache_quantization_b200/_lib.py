@@ -19,7 +19,7 @@ KVQ_ELIMIT = -5
 
 FMT_FP16, FMT_INT8, FMT_INT4 = 0, 1, 2
 SCALE_STATIC, SCALE_DYNAMIC_PCT, SCALE_ASYM_MINMAX = 0, 1, 2
-F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR, F_UNPACKED = 1, 2, 4, 8
+F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR, F_UNPACKED, F_ADAPT_SKIP_K, F_ADAPT_SKIP_V = 1, 2, 4, 8, 16, 32
 
 _i64, _i32, _vp, _f32 = C.c_int64, C.c_int32, C.c_void_p, C.c_float
 

@@ -32,7 +32,8 @@ import torch
 from torch import Tensor
 
 from . import ops, quant
-from ._lib import (FMT_FP16, FMT_INT4, FMT_INT8, F_ADAPTIVE, F_MIXED_RESCUE, F_RESCUE_THR, F_UNPACKED,
+from ._lib import (FMT_FP16, FMT_INT4, FMT_INT8, F_ADAPTIVE, F_ADAPT_SKIP_K, F_ADAPT_SKIP_V, F_MIXED_RESCUE, F_RESCUE_THR,
+                   F_UNPACKED,
                    SCALE_ASYM_MINMAX, SCALE_DYNAMIC_PCT, SCALE_STATIC)
 
 logger = logging.getLogger(__name__)
@@ -457,11 +458,13 @@ class _QuantCache(_CacheBase):
             policy = SCALE_STATIC
             kw.update(k_static=self._static_table("k", layer_id, H, G, k.device),
                       v_static=self._static_table("v", layer_id, H, G, k.device))
-            if self.adaptive_static_scales:
-                if self.adaptive_static_k != self.adaptive_static_v:
-                    raise ValueError("adaptive_static_k and adaptive_static_v must agree in the fused append")
-                if self.adaptive_static_k:
-                    flags |= F_ADAPTIVE
+            if self.adaptive_static_scales and (self.adaptive_static_k or self.adaptive_static_v):
+                # the rule applies to K and V independently (src/cache/int8_cache.py:394, :427)
+                flags |= F_ADAPTIVE
+                if not self.adaptive_static_k:
+                    flags |= F_ADAPT_SKIP_K
+                if not self.adaptive_static_v:
+                    flags |= F_ADAPT_SKIP_V
             flags |= extra_flags
             if flags & F_RESCUE_THR:
                 kw.update(k_rescue_thr=self._rescue_threshold(k, G), v_rescue_thr=self._rescue_threshold(v, G))

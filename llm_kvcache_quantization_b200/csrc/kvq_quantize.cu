@@ -263,7 +263,8 @@ __global__ void __launch_bounds__(128) quantize_append_kernel(const QuantParams 
             const float qmax = (FMT == KVQ_FMT_INT8) ? 127.0f : 7.0f;
             float dyn = __fdiv_rn(fmaxf(amax, 1e-5f), qmax);
             s32 = fmaxf(s32, 1e-5f);
-            if (a.flags & KVQ_F_ADAPTIVE) s32 = fmaxf(__fmul_rn(s32, a.adaptive_margin), dyn);
+            if ((a.flags & KVQ_F_ADAPTIVE) && !(a.flags & (sidx ? KVQ_F_ADAPT_SKIP_V : KVQ_F_ADAPT_SKIP_K)))
+                s32 = fmaxf(__fmul_rn(s32, a.adaptive_margin), dyn);
             if (a.flags & KVQ_F_MIXED_RESCUE) s32 = fmaxf(s32, dyn);
             if (a.flags & KVQ_F_RESCUE_THR) {
                 float thr = *sd.rescue_threshold;

@@ -30,6 +30,14 @@ from .quant import unpack_int4
 
 logger = logging.getLogger(__name__)
 _patched_classes = set()
+_FUSED_DUMP_WRITTEN = set()        # (directory, layer, step) already dumped by this process
+_FUSED_DEBUG_LOGGED = set()        # (layer, implementation) already logged once
+
+
+def _reset_fused_state() -> None:
+    """Forget what was dumped / logged (tests; src/engine/patch_model.py:31-50)."""
+    _FUSED_DUMP_WRITTEN.clear()
+    _FUSED_DEBUG_LOGGED.clear()
 
 FUSED_KV_MODES = frozenset({"fp16", "int8_baseline", "int8_fused", "int8_ours", "int4_baseline", "int4_fused",
                             "int4_ours", "int4_ours_mixed", "kivi_style"})
@@ -257,6 +265,87 @@ def _layer_inv_tau(engine, layer_idx: int, q_heads: int, device):
     return row.to(device=device, dtype=torch.float32).contiguous()
 
 
+
+def _optional_int_env(name: str) -> Optional[int]:
+    raw = os.environ.get(name, "").strip()
+    if not raw:
+        return None
+    try:
+        return int(raw)
+    except ValueError:
+        logger.warning("Ignoring %s=%r: not an integer.", name, raw)
+        return None
+
+
+def _top_values(t: torch.Tensor, k: int = 5):
+    flat = t.detach().float().reshape(-1)
+    k = min(k, flat.numel())
+    vals, idx = torch.topk(flat, k)
+    return [{"index": int(i), "value": float(v)} for v, i in zip(vals, idx)]
+
+
+def _maybe_dump_fused_decode(engine, layer_idx: int, decode_impl: str, q_kernel: torch.Tensor, inv_tau, sm_scale: float,
+                             fused_out: torch.Tensor) -> None:
+    """Audit dump of one fused decode call (src/engine/patch_model.py:380-496, called at :970-982).
+
+    KV_FUSED_DUMP_DIR enables it; KV_FUSED_DUMP_LAYER / KV_FUSED_DUMP_STEP (cache length after the append) select
+    one call.  Writes `<stem>.pt` (query as the kernel saw it, integer codes, fp16 scales, the fused output, and the
+    torch dequantize-then-attention output on the same tensors) and `<stem>.json` (max / mean |difference|, the
+    largest entries of both outputs).  Once per (directory, layer, step) and process."""
+    dump_dir = os.environ.get("KV_FUSED_DUMP_DIR", "").strip()
+    if not dump_dir:
+        return
+    step = int(engine.get_seq_len()) if hasattr(engine, "get_seq_len") else -1
+    want_layer, want_step = _optional_int_env("KV_FUSED_DUMP_LAYER"), _optional_int_env("KV_FUSED_DUMP_STEP")
+    if (want_layer is not None and want_layer != layer_idx) or (want_step is not None and want_step != step):
+        return
+    key = (dump_dir, int(layer_idx), step)
+    if key in _FUSED_DUMP_WRITTEN:
+        return
+    if hasattr(engine, "get_int8_tensors"):
+        k, v, ks, vs = engine.get_int8_tensors(layer_idx)
+    elif hasattr(engine, "get_int4_tensors"):
+        k, v, ks, vs = engine.get_int4_tensors(layer_idx)
+        if getattr(engine, "bit_packed", True):
+            k, v = unpack_int4(k), unpack_int4(v)          # codes in [-8, 7] stored as int8
+    else:
+        logger.debug("Skipping fused decode dump at layer %s: the engine exposes no integer tensors.", layer_idx)
+        return
+    q_eff = q_kernel if inv_tau is None else q_kernel * inv_tau.to(q_kernel.dtype).view(1, -1, 1)
+    ctx = torch.full((q_kernel.shape[0],), int(k.shape[2]), dtype=torch.int32, device=q_kernel.device)
+    ks16, vs16 = ks.to(torch.float16), vs.to(torch.float16)
+    ref_out = _decode_attn_int8_torch_ref(q_eff, k, v, ks16, vs16, ctx, sm_scale)
+    diff = (fused_out.float() - ref_out.float()).abs()
+    os.makedirs(dump_dir, exist_ok=True)
+    stem = f"fused_layer{int(layer_idx):02d}_step{step:05d}_pid{os.getpid()}"
+    tensor_path = os.path.join(dump_dir, stem + ".pt")
+    torch.save({"layer_idx": int(layer_idx), "step": step, "decode_impl": decode_impl, "sm_scale": float(sm_scale),
+                "context_len": int(k.shape[2]), "q": q_eff.detach().cpu(), "k_int8": k.detach().cpu(),
+                "v_int8": v.detach().cpu(), "k_scale": ks16.detach().cpu(), "v_scale": vs16.detach().cpu(),
+                "fused_out": fused_out.detach().cpu(), "ref_out": ref_out.detach().cpu()}, tensor_path)
+    with open(os.path.join(dump_dir, stem + ".json"), "w") as f:
+        json.dump({"layer_idx": int(layer_idx), "step": step, "decode_impl": decode_impl, "sm_scale": float(sm_scale),
+                   "context_len": int(k.shape[2]), "tensor_path": tensor_path, "max_abs_diff": float(diff.max()),
+                   "mean_abs_diff": float(diff.mean()), "logits_topk_fused": _top_values(fused_out),
+                   "logits_topk_ref": _top_values(ref_out)}, f, indent=2)
+    _FUSED_DUMP_WRITTEN.add(key)
+    logger.info("Wrote fused decode dump: layer=%s step=%s -> %s", layer_idx, step, tensor_path)
+
+
+def _maybe_log_fused_debug(engine, layer_idx: int, decode_impl: str, q_kernel: torch.Tensor) -> None:
+    """KV_FUSED_DEBUG=1: one log line per (layer, implementation) with the shapes the kernel got
+    (src/engine/patch_model.py:993-1004)."""
+    if os.environ.get("KV_FUSED_DEBUG", "0") != "1":
+        return
+    key = (int(layer_idx), decode_impl)
+    if key in _FUSED_DEBUG_LOGGED:
+        return
+    _FUSED_DEBUG_LOGGED.add(key)
+    logger.warning("[KV_FUSED_DEBUG] layer=%d impl=%s q=%s dtype=%s cache=%s seq_len=%s", layer_idx, decode_impl,
+                   tuple(q_kernel.shape), q_kernel.dtype, type(engine).__name__,
+                   engine.get_seq_len() if hasattr(engine, "get_seq_len") else "?")
+
+
 def _fused_forward_impl(self, hidden_states, cache_wrapper, attention_mask=None, position_ids=None,
                         position_embeddings=None, cache_position=None, return_cache=False, **kwargs):
     """Decode-only (q_len == 1) attention forward (src/engine/patch_model.py:645-1008)."""
@@ -317,6 +406,9 @@ def _fused_forward_impl(self, hidden_states, cache_wrapper, attention_mask=None,
         warnings.warn(f"Fused decode failed at layer {layer_idx} after the cache append; the cache now holds one "
                       "more token than outputs were produced for.", RuntimeWarning)
         raise
+    if os.environ.get("KV_FUSED_DUMP_DIR") or os.environ.get("KV_FUSED_DEBUG") == "1":
+        _maybe_dump_fused_decode(engine, layer_idx, decode_impl, q_kernel, inv_tau, sm_scale, attn_output)
+        _maybe_log_fused_debug(engine, layer_idx, decode_impl, q_kernel)
     attn_output = attn_output.to(hidden_states.dtype).reshape(bsz, 1, q_heads * head_dim)
     attn_output = self.o_proj(attn_output)
     if return_cache:
@@ -475,15 +567,36 @@ def remove_int8_fused_patch(model=None) -> bool:
 
 # --------------------------------------------------------------------------- decode loop
 @dataclass
+class GenerationOutput:
+    """Result of `generate` (src/engine/generate_loop.py:151-165)."""
+    text: str
+    tokens: List[int]
+    ttft_ms: float
+    tpot_ms: float
+    tok_per_s: float
+    gpu_mem_peak_mb: float
+    prompt_len: int
+    gen_len: int
+    tok_per_s_per_seq: float = 0.0
+    kv_cache_mem_mb: float = 0.0
+    kv_cache_seq_len: int = 0
+
+
+@dataclass
 class GenerationBatchOutput:
-    """Token ids and timing of one `generate_from_ids` call (a subset of the reference's fields,
-    src/engine/generate_loop.py)."""
-    generated_ids: torch.Tensor                 # [B, max_new_tokens]
+    """Result of `generate_from_ids` (src/engine/generate_loop.py:168-182), plus this package's extras."""
+    generated_ids: torch.Tensor                 # [B, gen_len]
     ttft_ms: float = 0.0
     tpot_ms: float = 0.0
     tok_per_s: float = 0.0
+    tok_per_s_per_seq: float = 0.0
+    gpu_mem_peak_mb: float = 0.0
+    prompt_len: int = 0
+    gen_len: int = 0
+    batch: int = 0
     kv_cache_mem_mb: float = 0.0
     kv_cache_seq_len: int = 0
+    # not in the reference's dataclass:
     kv_mode: str = "fp16"
     decode_stats: dict = field(default_factory=dict)
     step_ms: List[float] = field(default_factory=list)
@@ -522,7 +635,8 @@ def load_calibration(calib_file: str, kv_mode: str, device, *, use_static_scales
 
 def build_cache(kv_mode: str, num_layers: int, device, *, group_size=128, clip_percentile=99.9, max_seq_len=None,
                 calib: Optional[dict] = None, decode_attn_impl="triton_fused", use_attn_temperature=True,
-                quant_bits: int = 8, residual_length: int = 0):
+                quant_bits: int = 8, residual_length: int = 0, adaptive_static_scales: bool = False,
+                adaptive_static_margin: float = 1.0, adaptive_static_k: bool = True, adaptive_static_v: bool = True):
     """Cache engine for a kv_mode (src/engine/generate_loop.py:891-938)."""
     if kv_mode not in FUSED_KV_MODES:
         raise ValueError(f"kv_mode={kv_mode!r} is not supported here; choose one of {sorted(FUSED_KV_MODES)}")
@@ -536,7 +650,11 @@ def build_cache(kv_mode: str, num_layers: int, device, *, group_size=128, clip_p
     gs = calib.get("group_size") or group_size
     cp = calib.get("clip_percentile") or clip_percentile
     common = dict(device=device, clip_percentile=cp, group_size=gs, max_seq_len=max_seq_len,
-                  decode_attn_impl=decode_attn_impl, use_attn_temperature=use_attn_temperature)
+                  decode_attn_impl=decode_attn_impl, use_attn_temperature=use_attn_temperature,
+                  # passed to every quantized mode, as the reference does (src/engine/generate_loop.py:913-916, 932-935);
+                  # the caches apply them only when static scales are present
+                  adaptive_static_scales=adaptive_static_scales, adaptive_static_margin=adaptive_static_margin,
+                  adaptive_static_k=adaptive_static_k, adaptive_static_v=adaptive_static_v)
     calibrated = kv_mode in ("int8_ours", "int4_ours", "int4_ours_mixed", "int4_fused")
     if calibrated:
         common.update(static_k_scale=calib.get("static_k_scale"), static_v_scale=calib.get("static_v_scale"),
@@ -548,6 +666,65 @@ def build_cache(kv_mode: str, num_layers: int, device, *, group_size=128, clip_p
         extra = dict(outlier_rescue_ratio=calib.get("outlier_rescue_ratio", 0.0),
                      mixed_rescue=calib.get("mixed_rescue", False) or kv_mode == "int4_ours_mixed")
     return INT4KVCache(num_layers, **common, **extra)
+
+
+
+def _register_prefill_temperature_hooks(model, inv_tau: torch.Tensor):
+    """Per-head temperature during PREFILL: scale the query states by `inv_tau[layer]` whenever more than one
+    position is processed (src/engine/generate_loop.py:276-390, registered at :1210).  The decode step (one
+    position) is left alone - the fused forward applies `inv_tau` itself.  With a `q_norm` module the scale goes on
+    its output (either [B,H,S,D] or [B,S,H,D]; the former wins a tie), otherwise on the `q_proj` output.
+    Returns the hook handles; the caller removes them."""
+    handles = []
+    layers = getattr(getattr(model, "model", None), "layers", None)
+    if layers is None:
+        warnings.warn("Cannot register prefill temperature hooks: model.model.layers not found. "
+                      "Per-head temperature scaling will NOT be applied during prefill.", UserWarning)
+        return handles
+    if not isinstance(inv_tau, torch.Tensor) or inv_tau.ndim != 2:
+        raise ValueError(f"inv_tau must be a 2D tensor [layers, heads], got {type(inv_tau)} "
+                         f"{getattr(inv_tau, 'shape', None)}")
+    cfg_heads = getattr(getattr(model, "config", None), "num_attention_heads", None)
+    for layer_idx, layer in enumerate(layers):
+        attn = getattr(layer, "self_attn", None)
+        if attn is None:
+            continue
+        heads = next((x for x in (getattr(attn, "num_heads", None), getattr(attn, "_kv_num_attention_heads", None),
+                                  cfg_heads) if x is not None), None)
+        head_dim = getattr(attn, "head_dim", None)
+        if heads is None or head_dim is None:
+            continue
+        heads, head_dim = int(heads), int(head_dim)
+        if layer_idx >= inv_tau.shape[0]:
+            raise ValueError(f"inv_tau has {inv_tau.shape[0]} layers but model has layer_idx={layer_idx}.")
+        if inv_tau.shape[1] != heads:
+            raise ValueError(f"inv_tau head count mismatch at layer {layer_idx}: "
+                             f"inv_tau.shape[1]={inv_tau.shape[1]} vs model.num_heads={heads}.")
+        row = inv_tau[layer_idx]
+        if getattr(attn, "q_norm", None) is not None:
+            def after_q_norm(module, inputs, output, row=row, heads=heads):
+                if not isinstance(output, torch.Tensor) or output.ndim != 4:
+                    return output
+                for head_axis, seq_axis in ((1, 2), (2, 1)):
+                    if output.shape[head_axis] == heads:
+                        if output.shape[seq_axis] <= 1:
+                            return output
+                        shape = [1, 1, 1, 1]
+                        shape[head_axis] = heads
+                        return output * row.to(device=output.device, dtype=output.dtype).view(shape)
+                return output
+            handles.append(attn.q_norm.register_forward_hook(after_q_norm))
+        elif getattr(attn, "q_proj", None) is not None:
+            def after_q_proj(module, inputs, output, row=row, heads=heads, head_dim=head_dim):
+                if not isinstance(output, torch.Tensor) or output.ndim != 3:
+                    return output
+                if output.shape[1] <= 1 or output.shape[2] != heads * head_dim:
+                    return output
+                b, s_len, _ = output.shape
+                scaled = output.view(b, s_len, heads, head_dim) * row.to(device=output.device, dtype=output.dtype).view(1, 1, -1, 1)
+                return scaled.view(b, s_len, heads * head_dim)
+            handles.append(attn.q_proj.register_forward_hook(after_q_proj))
+    return handles
 
 
 def _prefill_into_cache(model, cache, input_ids, attention_mask):
@@ -569,12 +746,20 @@ def _prefill_into_cache(model, cache, input_ids, attention_mask):
 @torch.no_grad()
 def generate_from_ids(model, tokenizer, input_ids, attention_mask=None, max_new_tokens=128, kv_mode="fp16",
                       group_size=128, clip_percentile=99.9, seed=1234, calib_file=None, use_attn_temperature=True,
-                      use_static_scales=True, decode_attn_impl="triton_fused", allow_missing_calib=False,
-                      stop_on_eos=True, quant_bits=8, residual_length=0, **_ignored) -> GenerationBatchOutput:
+                      use_static_scales=True, adaptive_static_scales=False, adaptive_static_margin=1.0,
+                      adaptive_static_k=True, adaptive_static_v=True, decode_attn_impl="triton_fused",
+                      allow_missing_calib=False, stop_on_eos=True, quant_bits=8, k_bits=None, v_bits=None,
+                      residual_length=0, policy_json=None) -> GenerationBatchOutput:
     """Greedy generation with a quantized KV cache and the fused decode path
-    (src/engine/generate_loop.py:393-1581, the fused modes and fp16).  Requires CUDA."""
+    (src/engine/generate_loop.py:393-1581, the fused modes and fp16; same parameters).  Requires CUDA.
+    `k_bits` / `v_bits` / `policy_json` belong to the reference's mixed-bit modes, which this package does not
+    build: anything but None raises."""
     if kv_mode not in FUSED_KV_MODES:
         raise ValueError(f"kv_mode={kv_mode!r} is not supported here; choose one of {sorted(FUSED_KV_MODES)}")
+    for name, val in (("k_bits", k_bits), ("v_bits", v_bits), ("policy_json", policy_json)):
+        if val is not None:
+            raise ValueError(f"{name}={val!r} selects a mixed-bit cache (kv_mode int4_mixed_kv / kivi policies), "
+                             "which this package does not provide; leave it None.")
     if decode_attn_impl not in ("triton_fused", "torch_ref"):
         raise ValueError(f"Unknown decode_attn_impl={decode_attn_impl!r}")
     device = next(model.parameters()).device
@@ -601,11 +786,19 @@ def generate_from_ids(model, tokenizer, input_ids, attention_mask=None, max_new_
     cache = build_cache(kv_mode, num_layers, device, group_size=group_size, clip_percentile=clip_percentile,
                         max_seq_len=max_seq, calib=calib, decode_attn_impl=decode_attn_impl,
                         use_attn_temperature=use_attn_temperature, quant_bits=quant_bits,
-                        residual_length=residual_length)
+                        residual_length=residual_length, adaptive_static_scales=adaptive_static_scales,
+                        adaptive_static_margin=adaptive_static_margin, adaptive_static_k=adaptive_static_k,
+                        adaptive_static_v=adaptive_static_v)
     eos = getattr(tokenizer, "eos_token_id", None)
     if isinstance(eos, (list, tuple)):
         eos = eos[0] if eos else None
     apply_int8_fused_patch(model)
+    hook_handles = []
+    inv_tau = (calib or {}).get("inv_tau")
+    if kv_mode in ("int8_ours", "int4_ours", "int4_ours_mixed", "int4_fused") and use_attn_temperature and inv_tau is not None:
+        # fused modes: the prompt is attended with the calibrated per-head temperature as well
+        hook_handles = _register_prefill_temperature_hooks(model, inv_tau)
+    torch.cuda.reset_peak_memory_stats(device)
     try:
         t0 = time.perf_counter()
         logits = _prefill_into_cache(model, cache, input_ids, attention_mask)
@@ -636,10 +829,45 @@ def generate_from_ids(model, tokenizer, input_ids, attention_mask=None, max_new_
             step_ms.append(e0.elapsed_time(e1))
         ids = torch.cat(generated, dim=1)
         tpot = sum(step_ms) / len(step_ms) if step_ms else 0.0
+        tps = (bsz * len(step_ms) / (sum(step_ms) * 1e-3)) if step_ms else 0.0
         return GenerationBatchOutput(
-            generated_ids=ids, ttft_ms=ttft, tpot_ms=tpot,
-            tok_per_s=(bsz * len(step_ms) / (sum(step_ms) * 1e-3)) if step_ms else 0.0,
+            generated_ids=ids, ttft_ms=ttft, tpot_ms=tpot, tok_per_s=tps, tok_per_s_per_seq=tps / max(bsz, 1),
+            gpu_mem_peak_mb=torch.cuda.max_memory_allocated(device) / 2 ** 20, prompt_len=int(prompt_len),
+            gen_len=int(ids.shape[1]), batch=int(bsz),
             kv_cache_mem_mb=cache.get_memory_mb(), kv_cache_seq_len=cache.get_seq_len(), kv_mode=kv_mode,
             decode_stats=cache.get_decode_stats() if hasattr(cache, "get_decode_stats") else {}, step_ms=step_ms)
     finally:
+        for h in hook_handles:
+            h.remove()
         remove_int8_fused_patch(model)
+
+
+@torch.no_grad()
+def generate(model, tokenizer, prompt: str, max_new_tokens=128, kv_mode="fp16", group_size=128, clip_percentile=99.9,
+             seed=1234, calib_file=None, use_attn_temperature=True, use_static_scales=True,
+             adaptive_static_scales=False, adaptive_static_margin=1.0, adaptive_static_k=True, adaptive_static_v=True,
+             decode_attn_impl="triton_fused", allow_missing_calib=False, stop_on_eos=True, quant_bits=8, k_bits=None,
+             v_bits=None, policy_json=None) -> GenerationOutput:
+    """Single-prompt front end of `generate_from_ids` (src/engine/generate_loop.py:1584): tokenize, generate
+    greedily, decode the new tokens."""
+    enc = tokenizer(prompt, return_tensors="pt")
+    device = next(model.parameters()).device
+    ids = enc["input_ids"].to(device)
+    mask = enc.get("attention_mask")
+    out = generate_from_ids(model, tokenizer, ids, attention_mask=None if mask is None else mask.to(device),
+                            max_new_tokens=max_new_tokens, kv_mode=kv_mode, group_size=group_size,
+                            clip_percentile=clip_percentile, seed=seed, calib_file=calib_file,
+                            use_attn_temperature=use_attn_temperature, use_static_scales=use_static_scales,
+                            adaptive_static_scales=adaptive_static_scales, adaptive_static_margin=adaptive_static_margin,
+                            adaptive_static_k=adaptive_static_k, adaptive_static_v=adaptive_static_v,
+                            decode_attn_impl=decode_attn_impl, allow_missing_calib=allow_missing_calib,
+                            stop_on_eos=stop_on_eos, quant_bits=quant_bits, k_bits=k_bits, v_bits=v_bits,
+                            policy_json=policy_json)
+    toks = out.generated_ids[0].tolist()
+    eos = getattr(tokenizer, "eos_token_id", None)
+    if stop_on_eos and eos is not None and eos in toks:
+        toks = toks[:toks.index(eos) + 1]
+    return GenerationOutput(text=tokenizer.decode(toks, skip_special_tokens=True), tokens=toks, ttft_ms=out.ttft_ms,
+                            tpot_ms=out.tpot_ms, tok_per_s=out.tok_per_s, gpu_mem_peak_mb=out.gpu_mem_peak_mb,
+                            prompt_len=out.prompt_len, gen_len=len(toks), tok_per_s_per_seq=out.tok_per_s_per_seq,
+                            kv_cache_mem_mb=out.kv_cache_mem_mb, kv_cache_seq_len=out.kv_cache_seq_len)

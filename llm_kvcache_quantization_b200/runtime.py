@@ -114,8 +114,12 @@ class GraphedKVStackStep:
             policy = _lib.SCALE_STATIC
             app.update(k_static=c._static_table("k", l, self.Hkv, G, self.device),
                        v_static=c._static_table("v", l, self.Hkv, G, self.device))
-            if c.adaptive_static_scales and c.adaptive_static_k:
+            if c.adaptive_static_scales and (c.adaptive_static_k or c.adaptive_static_v):
                 flags |= _lib.F_ADAPTIVE
+                if not c.adaptive_static_k:
+                    flags |= _lib.F_ADAPT_SKIP_K
+                if not c.adaptive_static_v:
+                    flags |= _lib.F_ADAPT_SKIP_V
             if getattr(c, "mixed_rescue", False) or getattr(c, "outlier_rescue_ratio", 0.0) >= 1.0:
                 flags |= _lib.F_MIXED_RESCUE
             elif getattr(c, "outlier_rescue_ratio", 0.0) > 0.0:

@@ -7,7 +7,8 @@ Usage (only where the reference checkout is available):
 
 The reference's own classes and functions are imported unmodified
 (`INT8KVCache`, `INT4KVCache`, `quantize_asymmetric`, `pack_int4`,
-`_decode_attn_int8_torch_ref`, `_apply_rope`, `KIVIStyleKVCache`) and driven on seeded inputs on CPU; inputs and
+`_decode_attn_int8_torch_ref`, `_apply_rope`, `KIVIStyleKVCache`, `apply_int8_fused_patch`,
+`INT8CacheWrapperContainer`, `_register_prefill_temperature_hooks`) and driven on seeded inputs on CPU; inputs and
 outputs are stored as small `.npz` files.  The fixtures travel with the
 repository, the reference does not.
 """
@@ -111,10 +112,102 @@ def make_kivi():
     print("kivi.npz", os.path.getsize(os.path.join(HERE, "kivi.npz")) // 1024, "KiB")
 
 
+ENGINE_GEOMETRY = dict(vocab_size=48, hidden_size=256, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=128, max_position_embeddings=64, rope_theta=10000.0,
+                       tie_word_embeddings=False)
+
+
+def tiny_qwen2(seed=1234):
+    """The seeded random-init Qwen2 of the engine fixture (CPU, fp16): 2 layers, 2 query heads over 1 KV head of
+    128 channels.  Deterministic for a given torch build; the fixture stores a checksum of the weights."""
+    import transformers
+    cfg = transformers.Qwen2Config(**ENGINE_GEOMETRY)
+    torch.manual_seed(seed)
+    model = transformers.Qwen2ForCausalLM(cfg).eval()
+    # spread the logits: the default init (std 0.02) gives near-uniform attention, a weak test of the temperature
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if "q_proj" in name or "k_proj" in name:
+                prm.mul_(6.0)
+    return model.half()
+
+
+def weights_checksum(model):
+    return float(sum(p.detach().double().abs().sum() for p in model.parameters()))
+
+
+def make_engine():
+    """The reference's patched attention forward end to end on CPU (src/engine/patch_model.py:645-1211 through
+    apply_int8_fused_patch + INT8CacheWrapperContainer, caches with decode_attn_impl="torch_ref", prefill with
+    _register_prefill_temperature_hooks, src/engine/generate_loop.py:276-390): prompt of 7 tokens x batch 2, three
+    greedy decode steps, static scales and per-head inverse temperatures of a calibration file's shape.  Stored:
+    the prompt, the calibration, the prefill K/V the reference's model produced, the logits of the prefill and of
+    every decode step, and the final cache tensors.  `generate_from_ids` itself refuses to run without CUDA
+    (src/engine/generate_loop.py:600-603), so the loop is driven here as it drives it."""
+    from src.cache.int8_cache import INT8KVCache
+    from src.cache.int4_cache import INT4KVCache
+    from src.engine.patch_model import (INT8CacheWrapperContainer, apply_int8_fused_patch, remove_int8_fused_patch)
+    from src.engine.generate_loop import _register_prefill_temperature_hooks
+    gen = torch.Generator().manual_seed(20261127)
+    L, Hq, Hkv, D, gs = 2, 2, 1, 128, 32
+    G = D // gs
+    out = {"weights_checksum": np.array(0.0)}
+    prompt = torch.randint(0, ENGINE_GEOMETRY["vocab_size"], (2, 7), generator=gen)
+    out["prompt"] = _np(prompt)
+    inv_tau = torch.empty(L, Hq).uniform_(0.7, 1.3, generator=gen)
+    out["inv_tau"] = _np(inv_tau)
+    for mode in ("int8_ours", "int4_ours", "int4_ours_mixed"):
+        model = tiny_qwen2()
+        out["weights_checksum"] = np.array(weights_checksum(model))
+        qmax = 127.0 if mode.startswith("int8") else 7.0
+        sdt = torch.float16 if mode.startswith("int8") else torch.float32      # generate_loop.py:816-820
+        ks = (torch.empty(L, Hkv, G).uniform_(1.5, 4.0, generator=gen) / qmax).to(sdt)
+        vs = (torch.empty(L, Hkv, G).uniform_(0.05, 0.2, generator=gen) / qmax).to(sdt)
+        out[f"{mode}_k_scale"], out[f"{mode}_v_scale"] = _np(ks.float()), _np(vs.float())
+        common = dict(device="cpu", group_size=gs, decode_attn_impl="torch_ref", static_k_scale=ks, static_v_scale=vs,
+                      inv_tau=inv_tau, use_attn_temperature=True)
+        if mode.startswith("int8"):
+            cache = INT8KVCache(L, **common)
+        else:
+            cache = INT4KVCache(L, mixed_rescue=(mode == "int4_ours_mixed"), **common)
+        handles = _register_prefill_temperature_hooks(model, inv_tau)
+        apply_int8_fused_patch(model)
+        try:
+            with torch.no_grad():
+                o = model(input_ids=prompt, attention_mask=torch.ones_like(prompt), use_cache=True)
+                pk, pv = [], []
+                for i, item in enumerate(o.past_key_values):
+                    k, v = item[0], item[1]
+                    pk.append(k); pv.append(v)
+                    cache.append(i, k, v)
+                out[f"{mode}_prefill_k"] = _np(torch.stack(pk)); out[f"{mode}_prefill_v"] = _np(torch.stack(pv))
+                out[f"{mode}_prefill_logits"] = _np(o.logits[:, -1].float())
+                tok = o.logits[:, -1].argmax(-1, keepdim=True)
+                toks, step_logits = [tok], []
+                container = INT8CacheWrapperContainer(cache, L)
+                for step in range(3):
+                    pos = torch.full((2, 1), prompt.shape[1] + step, dtype=torch.long)
+                    o = model(input_ids=tok, position_ids=pos, past_key_values=container, use_cache=True)
+                    step_logits.append(o.logits[:, -1].float())
+                    tok = o.logits[:, -1].argmax(-1, keepdim=True)
+                    toks.append(tok)
+                out[f"{mode}_tokens"] = _np(torch.cat(toks, 1)); out[f"{mode}_step_logits"] = _np(torch.stack(step_logits))
+                for i in range(L):
+                    t = cache.get_int8_tensors(i) if mode.startswith("int8") else cache.get_int4_tensors(i)
+                    for name, x in zip(("qk", "qv", "sk", "sv"), t):
+                        out[f"{mode}_l{i}_{name}"] = _np(x)
+        finally:
+            for h in handles:
+                h.remove()
+            remove_int8_fused_patch(model)
+    np.savez_compressed(os.path.join(HERE, "engine.npz"), **out)
+    print("engine.npz", os.path.getsize(os.path.join(HERE, "engine.npz")) // 1024, "KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
-    ap.add_argument("--only", default="", help="'rope' / 'kivi' regenerate rope.npz / kivi.npz alone")
+    ap.add_argument("--only", default="", help="'rope' / 'kivi' / 'engine' regenerate rope.npz / kivi.npz / engine.npz alone")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     warnings.simplefilter("ignore")
@@ -123,6 +216,9 @@ def main():
         return
     if args.only == "kivi":
         make_kivi()
+        return
+    if args.only == "engine":
+        make_engine()
         return
 
     from src.cache.int8_cache import INT8KVCache
@@ -260,6 +356,7 @@ def main():
         print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
     make_rope()
     make_kivi()
+    make_engine()
 
 
 if __name__ == "__main__":

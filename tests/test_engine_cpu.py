@@ -173,3 +173,122 @@ def test_save_calibration_writes_the_schema_load_calibration_reads(tmp_path):
     assert tuple(out["static_k_scale"].shape) == (3, 2, 4) and tuple(out["inv_tau"].shape) == (3, 12)
     with __import__("pytest").raises(ValueError):
         C.compute_absmax_per_group(torch.zeros(2, 5, 128), 48)
+
+
+# --------------------------------------------------------------------------- prefill temperature hooks, decode-loop arguments
+class _TinyAttn(torch.nn.Module):
+    def __init__(self, heads, head_dim, with_norm):
+        super().__init__()
+        self.num_heads, self.head_dim = heads, head_dim
+        self.q_proj = torch.nn.Linear(heads * head_dim, heads * head_dim, bias=False)
+        if with_norm:
+            self.q_norm = torch.nn.Identity()
+
+
+class _TinyModel(torch.nn.Module):
+    def __init__(self, layers, heads, head_dim, with_norm=False):
+        super().__init__()
+        self.model = torch.nn.Module()
+        self.model.layers = torch.nn.ModuleList()
+        for _ in range(layers):
+            layer = torch.nn.Module()
+            layer.self_attn = _TinyAttn(heads, head_dim, with_norm)
+            self.model.layers.append(layer)
+
+
+def test_prefill_temperature_hooks_scale_queries_of_prompts_only():
+    """src/engine/generate_loop.py:276-390: per-head scale on q_proj's output when more than one position is
+    processed; a single position (decode) passes through; the handles remove the hooks."""
+    torch.manual_seed(0)
+    heads, hd = 2, 4
+    m = _TinyModel(2, heads, hd)
+    inv_tau = torch.tensor([[0.5, 2.0], [1.5, 0.25]])
+    x_prompt, x_step = torch.randn(3, 5, heads * hd), torch.randn(3, 1, heads * hd)
+    plain = [l.self_attn.q_proj(x_prompt) for l in m.model.layers]
+    plain_step = m.model.layers[0].self_attn.q_proj(x_step)
+    handles = E._register_prefill_temperature_hooks(m, inv_tau)
+    assert len(handles) == 2
+    for l, layer in enumerate(m.model.layers):
+        got = layer.self_attn.q_proj(x_prompt).view(3, 5, heads, hd)
+        assert torch.allclose(got, plain[l].view(3, 5, heads, hd) * inv_tau[l].view(1, 1, -1, 1))
+    assert torch.equal(m.model.layers[0].self_attn.q_proj(x_step), plain_step)
+    for h in handles:
+        h.remove()
+    assert torch.equal(m.model.layers[1].self_attn.q_proj(x_prompt), plain[1])
+    # with a q_norm module the scale goes on ITS output, in either layout
+    n = _TinyModel(1, heads, hd, with_norm=True)
+    handles = E._register_prefill_temperature_hooks(n, inv_tau[:1])
+    qn = n.model.layers[0].self_attn.q_norm
+    bhsd, bshd = torch.randn(2, heads, 6, hd), torch.randn(2, 6, heads, hd)
+    assert torch.allclose(qn(bhsd), bhsd * inv_tau[0].view(1, -1, 1, 1))
+    assert torch.allclose(qn(bshd), bshd * inv_tau[0].view(1, 1, -1, 1))
+    one = torch.randn(2, heads, 1, hd)
+    assert torch.equal(qn(one), one)
+    # shape errors of the calibration tensor
+    with pytest.raises(ValueError, match="2D tensor"):
+        E._register_prefill_temperature_hooks(m, torch.ones(2))
+    with pytest.raises(ValueError, match="head count mismatch"):
+        E._register_prefill_temperature_hooks(m, torch.ones(2, 3))
+    with pytest.raises(ValueError, match="layers but model"):
+        E._register_prefill_temperature_hooks(m, torch.ones(1, 2))
+    with pytest.warns(UserWarning, match="model.model.layers not found"):
+        assert E._register_prefill_temperature_hooks(torch.nn.Linear(2, 2), inv_tau) == []
+
+
+def test_generate_from_ids_refuses_what_it_does_not_build():
+    ids = torch.zeros(1, 3, dtype=torch.long)
+    for kw in (dict(k_bits=4), dict(v_bits=8), dict(policy_json="p.json")):
+        with pytest.raises(ValueError, match="mixed-bit"):
+            E.generate_from_ids(None, None, ids, kv_mode="int8_ours", **kw)
+    with pytest.raises(ValueError, match="not supported"):
+        E.generate_from_ids(None, None, ids, kv_mode="int4_mixed_kv")
+    import inspect
+    names = list(inspect.signature(E.generate_from_ids).parameters)
+    # the reference's parameter list, in its order (src/engine/generate_loop.py:393-418)
+    assert names == ["model", "tokenizer", "input_ids", "attention_mask", "max_new_tokens", "kv_mode", "group_size",
+                     "clip_percentile", "seed", "calib_file", "use_attn_temperature", "use_static_scales",
+                     "adaptive_static_scales", "adaptive_static_margin", "adaptive_static_k", "adaptive_static_v",
+                     "decode_attn_impl", "allow_missing_calib", "stop_on_eos", "quant_bits", "k_bits", "v_bits",
+                     "residual_length", "policy_json"]
+    fields = {f for f in E.GenerationBatchOutput.__dataclass_fields__}
+    assert {"generated_ids", "ttft_ms", "tpot_ms", "tok_per_s", "tok_per_s_per_seq", "gpu_mem_peak_mb", "prompt_len",
+            "gen_len", "batch", "kv_cache_mem_mb", "kv_cache_seq_len"} <= fields
+
+
+def test_fused_decode_dump_writes_tensors_and_summary(tmp_path, monkeypatch):
+    """KV_FUSED_DUMP_DIR / _LAYER / _STEP (src/engine/patch_model.py:380-496): one dump per (directory, layer, step)."""
+    import json
+    import os
+
+    class Eng:
+        def __init__(self):
+            g = torch.Generator().manual_seed(1)
+            self.k = torch.randint(-127, 128, (1, 1, 6, 8), generator=g, dtype=torch.int8)
+            self.v = torch.randint(-127, 128, (1, 1, 6, 8), generator=g, dtype=torch.int8)
+            self.s = torch.full((1, 1, 6, 1), 0.01)
+
+        def get_int8_tensors(self, i):
+            return self.k, self.v, self.s, self.s
+
+        def get_seq_len(self):
+            return 6
+    E._reset_fused_state()
+    eng, q = Eng(), torch.randn(1, 2, 8).half()
+    ctx = torch.full((1,), 6, dtype=torch.int32)
+    fused = E._decode_attn_int8_torch_ref(q, eng.k, eng.v, eng.s.half(), eng.s.half(), ctx, 0.3)
+    monkeypatch.setenv("KV_FUSED_DUMP_DIR", str(tmp_path))
+    monkeypatch.setenv("KV_FUSED_DUMP_LAYER", "1")
+    E._maybe_dump_fused_decode(eng, 0, "triton_fused", q, None, 0.3, fused)          # filtered out: layer 0
+    assert os.listdir(tmp_path) == []
+    E._maybe_dump_fused_decode(eng, 1, "triton_fused", q, None, 0.3, fused)
+    E._maybe_dump_fused_decode(eng, 1, "triton_fused", q, None, 0.3, fused)          # second call: already written
+    files = sorted(os.listdir(tmp_path))
+    assert len(files) == 2 and files[0].startswith("fused_layer01_step00006_pid") and files[0].endswith(".json")
+    summary = json.load(open(os.path.join(tmp_path, files[0])))
+    assert summary["max_abs_diff"] == 0.0 and summary["context_len"] == 6 and len(summary["logits_topk_ref"]) == 5
+    blob = torch.load(os.path.join(tmp_path, files[1]))
+    assert set(blob) >= {"q", "k_int8", "v_int8", "k_scale", "v_scale", "fused_out", "ref_out", "sm_scale"}
+    monkeypatch.setenv("KV_FUSED_DUMP_STEP", "7")
+    E._reset_fused_state()
+    E._maybe_dump_fused_decode(eng, 1, "triton_fused", q, None, 0.3, fused)          # filtered out: step 6
+    assert len(os.listdir(tmp_path)) == 2

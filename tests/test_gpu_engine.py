@@ -1,10 +1,13 @@
 """End-to-end decode of a small random-init Qwen2 model through the patched forward, the cache
 shims and the fused kernels, compared with plain HuggingFace decoding on the same weights."""
+import os
+
 import numpy as np
 import pytest
 import torch
 
 from llm_kvcache_quantization_b200 import engine as E
+from oracle import kvq_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -198,3 +201,86 @@ def test_kivi_style_mode_generates(tiny_model, bits):
     assert torch.equal(out.generated_ids[:, 0], ref[:, 0])          # the first token comes from the fp16 prefill
     if bits == 8:
         assert (out.generated_ids == ref).float().mean() >= 0.6
+
+
+# --------------------------------------------------------------------------- pinned to the reference's patched forward
+def _fixture_model_and_data(golden_dir):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(golden_dir, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    fx = np.load(os.path.join(golden_dir, "engine.npz"))
+    model = mg.tiny_qwen2()
+    if abs(mg.weights_checksum(model) - float(fx["weights_checksum"])) > 1e-6 * float(fx["weights_checksum"]):
+        pytest.skip("this torch build initialises the seeded model differently from the one that made the fixture")
+    return model, fx
+
+
+@pytest.mark.parametrize("mode", ("int8_ours", "int4_ours", "int4_ours_mixed"))
+def test_patched_forward_matches_the_reference_run(golden_dir, mode):
+    """tests/golden/engine.npz holds a run of the REFERENCE's patched forward on CPU (apply_int8_fused_patch +
+    INT8CacheWrapperContainer + caches with decode_attn_impl="torch_ref", prefill temperature hooks, calibration
+    with static scales and inv_tau) on a seeded tiny Qwen2.  Same weights, this package's engine on the GPU:
+      1. the reference's own prefill K/V through this package's cache: cache bytes and scales bit-equal;
+      2. the whole loop on the GPU (its own prefill with the temperature hooks, three decode steps, the reference's
+         tokens fed back): logits within fp16 tolerance of the reference's, and the cache rows it wrote equal to
+         the reference's up to the few codes that sit on a rounding boundary of the CPU / GPU projections."""
+    from llm_kvcache_quantization_b200 import engine as E
+    model, fx = _fixture_model_and_data(golden_dir)
+    L, gs = 2, 32
+    int8 = mode.startswith("int8")
+    sdt = torch.float16 if int8 else torch.float32
+    calib = dict(group_size=gs, clip_percentile=99.9, inv_tau=torch.from_numpy(fx["inv_tau"]).to(DEV),
+                 static_k_scale=torch.from_numpy(fx[f"{mode}_k_scale"]).to(sdt).to(DEV),
+                 static_v_scale=torch.from_numpy(fx[f"{mode}_v_scale"]).to(sdt).to(DEV),
+                 outlier_rescue_ratio=0.0, mixed_rescue=(mode == "int4_ours_mixed"))
+
+    def tensors(cache, l):
+        return cache.get_int8_tensors(l) if int8 else cache.get_int4_tensors(l)
+
+    # 1. quantize-on-append of the reference's prefill tensors
+    c1 = E.build_cache(mode, L, DEV, group_size=gs, calib=calib, max_seq_len=16)
+    for l in range(L):
+        c1.append(l, torch.from_numpy(fx[f"{mode}_prefill_k"][l]).to(DEV), torch.from_numpy(fx[f"{mode}_prefill_v"][l]).to(DEV))
+        for name, got in zip(("qk", "qv", "sk", "sv"), tensors(c1, l)):
+            want = fx[f"{mode}_l{l}_{name}"][:, :, :7]
+            got = got.cpu().numpy()
+            if name in ("sk", "sv"):
+                assert np.array_equal(got.astype(np.float16).view(np.uint16), want.astype(np.float16).view(np.uint16)), (l, name)
+            else:
+                assert np.array_equal(got, want), (l, name)
+
+    # 2. the loop on the GPU
+    model = model.to(DEV)
+    prompt = torch.from_numpy(fx["prompt"]).to(DEV)
+    cache = E.build_cache(mode, L, DEV, group_size=gs, calib=calib, max_seq_len=16)
+    handles = E._register_prefill_temperature_hooks(model, calib["inv_tau"])
+    E.apply_int8_fused_patch(model)
+    try:
+        with torch.no_grad():
+            logits = E._prefill_into_cache(model, cache, prompt, torch.ones_like(prompt))
+            worst = float((logits.float().cpu() - torch.from_numpy(fx[f"{mode}_prefill_logits"])).abs().max())
+            container = E.INT8CacheWrapperContainer(cache, L)
+            toks = torch.from_numpy(fx[f"{mode}_tokens"]).to(DEV)
+            for step in range(3):
+                pos = torch.full((2, 1), 7 + step, dtype=torch.long, device=DEV)
+                out = model(input_ids=toks[:, step:step + 1], position_ids=pos, past_key_values=container, use_cache=True)
+                d = (out.logits[:, -1].float().cpu() - torch.from_numpy(fx[f"{mode}_step_logits"][step])).abs().max()
+                worst = max(worst, float(d))
+    finally:
+        for h in handles:
+            h.remove()
+        E.remove_int8_fused_patch(model)
+    # logits are O(1); the reference ran its projections in fp16 on the CPU, this run on the GPU
+    assert worst <= (3e-2 if int8 else 1e-1), worst
+    off = tot = 0
+    for l in range(L):
+        for name, got in zip(("qk", "qv"), tensors(cache, l)[:2]):
+            want = fx[f"{mode}_l{l}_{name}"]
+            got = got.cpu().numpy()
+            if not int8:                                   # compare codes, not packed bytes
+                got, want = O.unpack_int4(got), O.unpack_int4(want)
+            diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
+            assert diff.max() <= 1, (l, name, int(diff.max()))
+            off += int((diff != 0).sum()); tot += diff.size
+    assert off <= 0.02 * tot, (off, tot)
