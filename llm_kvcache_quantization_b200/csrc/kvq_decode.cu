@@ -556,8 +556,15 @@ static bool wide_rows_possible(const KvqAttnArgs& a) {
     return a.format == KVQ_FMT_INT4 && a.k.pay_stride_s == 64 && a.v.pay_stride_s == 64 && a.max_ctx >= 2 &&
            !getenv("KVQ_INT4_NARROW_ROWS");
 }
+// An odd max_ctx makes the last pair row reach one token slot past max_ctx - 1: fine when that slot belongs to the
+// same (batch, head) row of the cache (its bytes are sanitised like any token beyond a row's context), which the head
+// stride tells.
+static bool wide_rows_room(const KvqAttnArgs& a) {
+    const long long need = ((long long)a.max_ctx + 1) * 64;
+    return a.k.pay_stride_h >= need && a.v.pay_stride_h >= need;
+}
 static bool wide_rows_ok(const KvqAttnArgs& a) {
-    return wide_rows_possible(a) && ((a.max_ctx & 1) == 0 || a.tail_tokens == 1);
+    return wide_rows_possible(a) && ((a.max_ctx & 1) == 0 || a.tail_tokens == 1 || wide_rows_room(a));
 }
 
 // ---------------------------------------------------------------------------
@@ -639,10 +646,10 @@ static int launch_i4(I4Tag<ASYM, NOUT, FAST, GS> tag, const AttnParams& p, cudaS
     Int4Params ip;
     ip.p = p;
     ip.nstage = cfg.nstage;
-    // Pairs of tokens travel as 128-byte rows when the tokens of a (b, h) row are contiguous.  The pair view covers
-    // floor(max_ctx / 2) pairs, so that nothing beyond token max_ctx - 1 is ever read: with an odd max_ctx the last
-    // token must belong to the combine stage (tail_tokens), which kvq_decode_attn arranges for whole calls; a
-    // split-only call without it keeps the 64-byte rows.
+    // Pairs of tokens travel as 128-byte rows when the tokens of a (b, h) row are contiguous.  With an odd max_ctx
+    // the last token either belongs to the combine stage (tail_tokens; the pair view then covers floor(max_ctx / 2)
+    // pairs), or shares its pair row with the next slot of the same cache row (wide_rows_room); a call with neither
+    // keeps the 64-byte rows.
     ip.wide_rows = wide_rows_ok(p.a);
     {
         static const int pf = [] { const char* e = getenv("KVQ_I4_PREFETCH"); int v = e ? atoi(e) : 4; return v < 0 ? 0 : (v > 64 ? 64 : v); }();
@@ -651,7 +658,7 @@ static int launch_i4(I4Tag<ASYM, NOUT, FAST, GS> tag, const AttnParams& p, cudaS
         ip.l2_ahead = ahead;
     }
     const KvqAttnArgs& a = p.a;
-    const int ext = ip.wide_rows ? a.max_ctx / 2 : a.max_ctx;
+    const int ext = ip.wide_rows ? (a.max_ctx + (a.tail_tokens ? 0 : 1)) / 2 : a.max_ctx;
     const int ng = 128 / GS;
     CUtensorMap kmap, vmap, ksmap, vsmap, kzmap, vzmap;
     int rc;
@@ -819,7 +826,8 @@ extern "C" int kvq_decode_attn(const KvqAttnArgs* args, kvq_stream_t stream) {
     const bool mma = mma_eligible(p, asym);
     // whole call over a packed-INT4 cache with an odd token count: hand the last token to the combine stage so that
     // the scan can fetch pairs of tokens as 128-byte rows (see launch_mma)
-    if (mma && a.stages == 0 && a.tail_tokens == 0 && (a.max_ctx & 1) && wide_rows_possible(a)) p.a.tail_tokens = 1;
+    if (mma && a.stages == 0 && a.tail_tokens == 0 && (a.max_ctx & 1) && wide_rows_possible(a) && !wide_rows_room(a))
+        p.a.tail_tokens = 1;
     p.splits = a.splits > 0 ? a.splits : pick_splits_internal(p, asym, mma);
     size_t need = kvq_decode_workspace_bytes(a.B, a.Hq, a.D, p.splits);
     if (!a.workspace || a.workspace_bytes < need || (((uintptr_t)a.workspace) & 15)) return KVQ_EWORKSPACE;
