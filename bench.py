@@ -782,7 +782,8 @@ def measure_workload(name, wl, args, dev, dist, rank, world, *, e2e=True, cpu=Fa
                              "outputs; stream sync"}
         del stepper
 
-    if args.aux and kind not in ("fp16", "kivi4") and world == 1:
+    # the callers either side of the decode path (dequantising read-back, bulk prefill append): always for configuration 2
+    if (args.aux or name == "c2") and kind not in ("fp16", "kivi4") and world == 1:
         res["aux"] = time_aux(wl, cache, dev)
     if args.model_step and world == 1 and (Hq, Hkv) in MODEL_GEOMETRY:
         try:

@@ -389,6 +389,25 @@ KVQ_API int kvq_dequantize(const KvqDequantArgs* args, kvq_stream_t stream);
  */
 KVQ_API int kvq_debug_error_flag(int reset);
 
+/*
+ * Self-test of the quantizer's division: the kernels divide every element by a scale that is fixed per group and do
+ * it as reciprocal + one residual correction instead of an IEEE division; this runs both on the device over a
+ * family of (dividend, divisor) pairs and counts the pairs whose quotients differ as numbers (NaN equals NaN, -0 equals
+ * +0: the integer code that follows has no signed zero).  The
+ * reference divides with torch's IEEE division (src/quant/int8_basic.py:155-161, int4_basic.py:150-156,
+ * asymmetric_quant.py), so the count must be 0.
+ *   mode 0: dividends = all 65 536 fp16 values (zeros, subnormals, infinities and NaNs included) x divisors = every
+ *           `stride`-th of the 2^23 significands in [1, 2), then the same dividends x the binades 2^-17 .. 2^16 with
+ *           a coarse significand sweep, inf and NaN; then every fp32 dividend significand over the constant divisors
+ *           7, 15, 127 and 255 (amax / 7, range / 15, ...).  stride 1 covers every quotient the symmetric quantizers
+ *           can form (no exponent of theirs under- or overflows).
+ *   mode 1: dividends = every `stride`-th fp32 significand in [1, 2) x divisors = all 2^23 significands in [1, 2):
+ *           with stride 1 every pair of fp32 significands, which settles every normal fp32 pair whose quotient and
+ *           residual stay normal (scaling by powers of two is exact) - the asymmetric quantizer's x - zero_point.
+ * Allocates one counter for the duration of the call and synchronises the device.  No reference counterpart.
+ */
+KVQ_API int kvq_selftest_division(int mode, uint32_t stride, uint64_t* mismatches, uint64_t* pairs);
+
 KVQ_API const char* kvq_strerror(int code);
 KVQ_API int  kvq_last_cuda_error(void);     /* cudaError_t of the last KVQ_ECUDA on this thread */
 KVQ_API int  kvq_abi_version(void);

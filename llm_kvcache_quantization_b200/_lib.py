@@ -147,6 +147,7 @@ EXPORTS = (
     ("kvq_group_absmax", C.c_int, (C.POINTER(KvqAbsmaxArgs), _vp)),
     ("kvq_dequantize", C.c_int, (C.POINTER(KvqDequantArgs), _vp)),
     ("kvq_debug_error_flag", C.c_int, (C.c_int,)),
+    ("kvq_selftest_division", C.c_int, (C.c_int, C.c_uint32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64))),
     ("kvq_decode_kernel_kind", C.c_int, (C.POINTER(KvqAttnArgs),)),
     ("kvq_strerror", C.c_char_p, (C.c_int,)),
     ("kvq_last_cuda_error", C.c_int, ()),
