@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define KVQ_ABI_VERSION 4
+#define KVQ_ABI_VERSION 5
 
 #if defined(__GNUC__)
 #define KVQ_API __attribute__((visibility("default")))
@@ -298,10 +298,35 @@ typedef struct KvqKiviArgs {
     int64_t out_stride_b, out_stride_h, out_stride_s;   /* elements, multiples of 8      */
     void* v_scale_h;             /* append, optional: fp16 copies RN16(v_scale), RN16(v_zp), laid out like the fp32  */
     void* v_zp_h;                /* buffers - the per-token tiles the fused decode kernel reads                      */
+    /* append, optional clipping bounds (percentiles below 100, src/quant/asymmetric_quant.py:98-104): the range of a
+     * channel / token is [lo, hi] instead of its minimum and maximum; values outside are clipped by the code range.
+     * Both pointers of a pair or neither.  kvq_sorted_quantile computes them from sorted values.              */
+    const float* k_lo;           /* fp32 [B, H, D] contiguous, used when init_k_params = 1                     */
+    const float* k_hi;
+    const float* v_lo;           /* fp32 [B, H, T] contiguous                                                   */
+    const float* v_hi;
 } KvqKiviArgs;
 
 KVQ_API int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream);
 KVQ_API int kvq_kivi_dequantize(const KvqKiviArgs* args, kvq_stream_t stream);
+
+/*
+ * Two quantiles of every row of a row-sorted matrix, as torch.quantile(x, q, dim=-1) (linear interpolation) gives
+ * them: rank = q * (n - 1) in fp32, w = rank - floor(rank), value = w < 0.5 ? fma(w, hi - lo, lo) :
+ * fma(w - 1, hi - lo, hi).  `sorted` is fp32 [rows, n], contiguous, ascending in every row (the caller sorts: a sort
+ * has no rounding).  Used for the clipping bounds of the KIVI-format cache
+ * (src/quant/asymmetric_quant.py:98-104 calls torch.quantile twice, with q = 1 - p and p).
+ */
+typedef struct KvqQuantileArgs {
+    const float* sorted;
+    int64_t rows;
+    int32_t n;
+    float   q_lo, q_hi;
+    float*  out_lo;              /* fp32 [rows] */
+    float*  out_hi;
+} KvqQuantileArgs;
+
+KVQ_API int kvq_sorted_quantile(const KvqQuantileArgs* args, kvq_stream_t stream);
 
 /*
  * Calibration statistic: out[h, g] = max(out[h, g], max over batch rows, tokens and the channels of group g
@@ -413,7 +438,7 @@ KVQ_API int  kvq_last_cuda_error(void);     /* cudaError_t of the last KVQ_ECUDA
 KVQ_API int  kvq_abi_version(void);
 /* sizeof of an argument struct as this library was compiled, for binders that mirror the structs by hand
  * (ctypes, cgo): 0 KvqAppendSide, 1 KvqAppendArgs, 2 KvqCacheSide, 3 KvqAttnArgs, 4 KvqCombineArgs,
- * 5 KvqDequantArgs, 6 KvqKiviArgs, 7 KvqAbsmaxArgs, 8 KvqExchangeArgs; 0 for any other id.  No reference counterpart. */
+ * 5 KvqDequantArgs, 6 KvqKiviArgs, 7 KvqAbsmaxArgs, 8 KvqExchangeArgs, 9 KvqQuantileArgs; 0 for any other id.  No reference counterpart. */
 KVQ_API size_t kvq_struct_size(int which);
 
 #ifdef __cplusplus

@@ -17,7 +17,7 @@ import os as _os
 _os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
 
 from .cache import FP16KVCache, INT4KVCache, INT8KVCache  # noqa: E402
-from .kivi import KIVIStyleKVCache
+from .kivi import KIVIStyleKVCache, RoleAwareAsymKVCache
 from .kernels import (decode_attn_fp16, decode_attn_int4, decode_attn_int4_asym,
                       decode_attn_int4_outlier, decode_attn_int8)
 from .quant import (dequantize_asymmetric_groupwise, dequantize_symmetric_int4,
@@ -26,7 +26,7 @@ from .quant import (dequantize_asymmetric_groupwise, dequantize_symmetric_int4,
                     quantize_symmetric_int8, quantize_symmetric_int8_with_scale, unpack_int4)
 
 __all__ = [
-    "FP16KVCache", "INT4KVCache", "INT8KVCache", "KIVIStyleKVCache",
+    "FP16KVCache", "INT4KVCache", "INT8KVCache", "KIVIStyleKVCache", "RoleAwareAsymKVCache",
     "decode_attn_fp16", "decode_attn_int4", "decode_attn_int4_asym", "decode_attn_int4_outlier",
     "decode_attn_int8",
     "dequantize_asymmetric_groupwise", "dequantize_symmetric_int4", "dequantize_symmetric_int8",

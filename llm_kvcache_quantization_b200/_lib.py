@@ -113,6 +113,13 @@ class KvqKiviArgs(C.Structure):
         ("write_pos", _i64), ("write_pos_dev", _vp), ("max_slots", _i64),
         ("k_out", _vp), ("v_out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64), ("out_stride_s", _i64),
         ("v_scale_h", _vp), ("v_zp_h", _vp),
+        ("k_lo", _vp), ("k_hi", _vp), ("v_lo", _vp), ("v_hi", _vp),
+    ]
+
+
+class KvqQuantileArgs(C.Structure):
+    _fields_ = [
+        ("sorted", _vp), ("rows", _i64), ("n", _i32), ("q_lo", _f32), ("q_hi", _f32), ("out_lo", _vp), ("out_hi", _vp),
     ]
 
 
@@ -143,6 +150,7 @@ EXPORTS = (
     ("kvq_exchange_bytes", C.c_size_t, (_i32, _i32, _i32, _i32, _i32)),
     ("kvq_combine_exchange", C.c_int, (C.POINTER(KvqExchangeArgs), _vp)),
     ("kvq_kivi_append", C.c_int, (C.POINTER(KvqKiviArgs), _vp)),
+    ("kvq_sorted_quantile", C.c_int, (C.POINTER(KvqQuantileArgs), _vp)),
     ("kvq_kivi_dequantize", C.c_int, (C.POINTER(KvqKiviArgs), _vp)),
     ("kvq_group_absmax", C.c_int, (C.POINTER(KvqAbsmaxArgs), _vp)),
     ("kvq_dequantize", C.c_int, (C.POINTER(KvqDequantArgs), _vp)),
@@ -155,10 +163,10 @@ EXPORTS = (
     ("kvq_struct_size", C.c_size_t, (C.c_int,)),
 )
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 # ids of kvq_struct_size, in the order of include/kvq.h
 STRUCTS = (KvqAppendSide, KvqAppendArgs, KvqCacheSide, KvqAttnArgs, KvqCombineArgs, KvqDequantArgs, KvqKiviArgs,
-           KvqAbsmaxArgs, KvqExchangeArgs)
+           KvqAbsmaxArgs, KvqExchangeArgs, KvqQuantileArgs)
 
 _LIB = None
 

@@ -60,6 +60,7 @@ extern "C" size_t kvq_struct_size(int which) {
         case 6: return sizeof(KvqKiviArgs);
         case 7: return sizeof(KvqAbsmaxArgs);
         case 8: return sizeof(KvqExchangeArgs);
+        case 9: return sizeof(KvqQuantileArgs);
         default: return 0;
     }
 }

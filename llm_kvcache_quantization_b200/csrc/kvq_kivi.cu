@@ -79,8 +79,8 @@ __global__ void kivi_k_finalize_kernel(const KiviParams p) {
     const KvqKiviArgs& a = p.a;
     const long long n = (long long)a.B * a.H * a.D;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const float mn = ord2f(reinterpret_cast<int*>(a.k_zp)[i]);
-        const float mx = ord2f(reinterpret_cast<int*>(a.k_scale)[i]);
+        const float mn = a.k_lo ? a.k_lo[i] : ord2f(reinterpret_cast<int*>(a.k_zp)[i]);
+        const float mx = a.k_lo ? a.k_hi[i] : ord2f(reinterpret_cast<int*>(a.k_scale)[i]);
         float s, zp;
         kivi_scale_zp(mn, mx, p.qmin, p.qspan, s, zp);
         a.k_scale[i] = s;
@@ -144,6 +144,11 @@ __global__ void __launch_bounds__(256) kivi_quantize_kernel(const KiviParams p) 
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
     if (side == 1) {
+        if (a.v_lo) {                                  // clipping bounds of this token instead of its minimum / maximum
+            const long long o = ((long long)b * a.H + h) * a.T + t;
+            mn = a.v_lo[o];
+            mx = a.v_hi[o];
+        }
         float s, zp;
         kivi_scale_zp(mn, mx, p.qmin, p.qspan, s, zp);
 #pragma unroll
@@ -254,7 +259,38 @@ int kivi_error_flag(int reset) {
     return v;
 }
 
+// torch.quantile's linear interpolation on a sorted row: the rank in fp32, one fused multiply-add for either branch
+__device__ __forceinline__ float sorted_quantile(const float* row, int n, float q) {
+    const float pos = __fmul_rn(q, (float)(n - 1));
+    const int lo = (int)floorf(pos);
+    const int hi = min(lo + 1, n - 1);
+    const float w = __fsub_rn(pos, (float)lo);
+    const float x0 = row[lo], x1 = row[hi];
+    const float diff = __fsub_rn(x1, x0);
+    return (w < 0.5f) ? __fmaf_rn(w, diff, x0) : __fmaf_rn(__fsub_rn(w, 1.0f), diff, x1);
+}
+
+__global__ void sorted_quantile_kernel(const KvqQuantileArgs a) {
+    for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r < a.rows; r += (long long)gridDim.x * blockDim.x) {
+        const float* row = a.sorted + r * a.n;
+        a.out_lo[r] = sorted_quantile(row, a.n, a.q_lo);
+        a.out_hi[r] = sorted_quantile(row, a.n, a.q_hi);
+    }
+}
+
 }  // namespace kvq
+
+extern "C" int kvq_sorted_quantile(const KvqQuantileArgs* args, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!args) return KVQ_EINVAL;
+    const KvqQuantileArgs& a = *args;
+    if (a.rows < 0 || a.n <= 0 || !(a.q_lo >= 0.f && a.q_lo <= 1.f) || !(a.q_hi >= 0.f && a.q_hi <= 1.f)) return KVQ_EINVAL;
+    if (a.rows == 0) return KVQ_OK;
+    if (!a.sorted || !a.out_lo || !a.out_hi) return KVQ_EINVAL;
+    const long long blocks = (a.rows + 255) / 256;
+    sorted_quantile_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, (cudaStream_t)stream>>>(a);
+    return check_launch();
+}
 
 extern "C" int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream) {
     using namespace kvq;
@@ -271,12 +307,15 @@ extern "C" int kvq_kivi_append(const KvqKiviArgs* args, kvq_stream_t stream) {
         (a.src_stride_t & 7))
         return KVQ_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
+    if ((a.k_lo != nullptr) != (a.k_hi != nullptr) || (a.v_lo != nullptr) != (a.v_hi != nullptr)) return KVQ_EINVAL;
     if (a.init_k_params) {
         const long long n = (long long)a.B * a.H * a.D;
         const unsigned g = (unsigned)((n + 255) / 256 < 1024 ? (n + 255) / 256 : 1024);
-        kivi_stats_init_kernel<<<g, 256, 0, st>>>(p);
-        dim3 grid((a.T + kKiviStatRows - 1) / kKiviStatRows, a.B * a.H);
-        kivi_k_stats_kernel<<<grid, 128, 0, st>>>(p);
+        if (!a.k_lo) {
+            kivi_stats_init_kernel<<<g, 256, 0, st>>>(p);
+            dim3 grid((a.T + kKiviStatRows - 1) / kKiviStatRows, a.B * a.H);
+            kivi_k_stats_kernel<<<grid, 128, 0, st>>>(p);
+        }
         kivi_k_finalize_kernel<<<g, 256, 0, st>>>(p);
         if ((rc = check_launch()) != 0) return rc;
     }

@@ -40,7 +40,10 @@ def _reset_fused_state() -> None:
     _FUSED_DEBUG_LOGGED.clear()
 
 FUSED_KV_MODES = frozenset({"fp16", "int8_baseline", "int8_fused", "int8_ours", "int4_baseline", "int4_fused",
-                            "int4_ours", "int4_ours_mixed", "kivi_style"})
+                            "int4_ours", "int4_ours_mixed", "kivi_style", "int4_kivi_aligned", "int4_ours_asym",
+                            "int4_ours_asym_ba"})
+# modes stored in the KIVI format (per-channel K, per-token V, asymmetric)
+KIVI_FORMAT_MODES = frozenset({"kivi_style", "int4_kivi_aligned", "int4_ours_asym", "int4_ours_asym_ba"})
 
 
 # --------------------------------------------------------------------------- HF cache shims
@@ -633,6 +636,51 @@ def load_calibration(calib_file: str, kv_mode: str, device, *, use_static_scales
     return out
 
 
+def load_role_aware_calibration(calib_file: Optional[str], kv_mode: str, device) -> dict:
+    """Percentiles and temperature of the KIVI-format modes that read a calibration file
+    (src/engine/generate_loop.py:951-994 for int4_kivi_aligned, :995-1043 for int4_ours_asym / int4_ours_asym_ba):
+    `role_aware` section first, the `k_calibration` / `v_calibration` schema as the fallback (with the reference's
+    warning); inv_tau only for the modes that use it.  A path that does not exist raises, as in the reference."""
+    out = {"k_percentile": 100.0, "v_percentile": 100.0, "inv_tau": None}
+    if calib_file is None:
+        return out
+    if not os.path.exists(calib_file):
+        raise FileNotFoundError(f"{kv_mode}: calib_file={calib_file!r} not found. Use an absolute path or run from "
+                                "the project root.")
+    with open(calib_file, "r") as f:
+        data = json.load(f)
+
+    def tau(raw):
+        return torch.tensor(raw, dtype=torch.float32, device=device)
+
+    if kv_mode == "int4_kivi_aligned":
+        if "k_calibration" in data and "inv_tau" in data["k_calibration"]:
+            out["inv_tau"] = tau(data["k_calibration"]["inv_tau"])
+        elif "inv_tau" in data:
+            out["inv_tau"] = tau(data["inv_tau"])
+        if "v_calibration" in data and "v_percentile" in data["v_calibration"]:
+            out["v_percentile"] = float(data["v_calibration"]["v_percentile"])
+        return out
+    if "role_aware" in data:
+        ra = data["role_aware"]
+        out["k_percentile"] = float(ra.get("k_percentile", 100.0))
+        out["v_percentile"] = float(ra.get("v_percentile", 100.0))
+    elif "k_calibration" in data:
+        warnings.warn(f"RoleAlign mode '{kv_mode}' using k_calibration fallback schema; consider re-generating "
+                      "calibration with role_aware schema.", UserWarning)
+        out["k_percentile"] = float(data["k_calibration"].get("k_percentile", data.get("k_percentile", 100.0)))
+        if "v_calibration" in data:
+            out["v_percentile"] = float(data["v_calibration"].get("v_percentile", 100.0))
+    if kv_mode == "int4_ours_asym_ba":
+        if "role_aware" in data and "inv_tau" in data["role_aware"]:
+            out["inv_tau"] = tau(data["role_aware"]["inv_tau"])
+        elif "k_calibration" in data and "inv_tau" in data["k_calibration"]:
+            out["inv_tau"] = tau(data["k_calibration"]["inv_tau"])
+        elif "inv_tau" in data:
+            out["inv_tau"] = tau(data["inv_tau"])
+    return out
+
+
 def build_cache(kv_mode: str, num_layers: int, device, *, group_size=128, clip_percentile=99.9, max_seq_len=None,
                 calib: Optional[dict] = None, decode_attn_impl="triton_fused", use_attn_temperature=True,
                 quant_bits: int = 8, residual_length: int = 0, adaptive_static_scales: bool = False,
@@ -642,10 +690,26 @@ def build_cache(kv_mode: str, num_layers: int, device, *, group_size=128, clip_p
         raise ValueError(f"kv_mode={kv_mode!r} is not supported here; choose one of {sorted(FUSED_KV_MODES)}")
     if kv_mode == "fp16":
         return FP16KVCache(num_layers, device=device, max_seq_len=max_seq_len)
-    if kv_mode == "kivi_style":        # per-channel K / per-token V asymmetric (src/engine/generate_loop.py:905-921)
+    if kv_mode == "kivi_style":        # per-channel K / per-token V asymmetric (src/engine/generate_loop.py:939-950)
         from .kivi import KIVIStyleKVCache
         return KIVIStyleKVCache(num_layers, device=device, max_seq_len=max_seq_len, quant_bits=quant_bits,
                                 residual_length=residual_length)
+    if kv_mode == "int4_kivi_aligned":  # KIVI INT4 with a calibrated temperature and V percentile (:951-994)
+        from .kivi import KIVIStyleKVCache
+        ra = calib or {}
+        return KIVIStyleKVCache(num_layers, device=device, max_seq_len=max_seq_len, quant_bits=4,
+                                v_percentile=ra.get("v_percentile", 100.0), inv_tau=ra.get("inv_tau"),
+                                use_attn_temperature=use_attn_temperature, residual_length=residual_length)
+    if kv_mode in ("int4_ours_asym", "int4_ours_asym_ba"):   # calibrated percentiles (+ temperature for _ba) (:995-1060)
+        from .kivi import RoleAwareAsymKVCache
+        ra = calib or {}
+        ba = kv_mode == "int4_ours_asym_ba"
+        cache = RoleAwareAsymKVCache(num_layers, device=device, max_seq_len=max_seq_len, quant_bits=4,
+                                     k_percentile=ra.get("k_percentile", 100.0), v_percentile=ra.get("v_percentile", 100.0),
+                                     inv_tau=ra.get("inv_tau"), use_attn_temperature=use_attn_temperature and ba,
+                                     framework="ours_asym_ba" if ba else "ours_asym")
+        cache.decode_attn_impl = decode_attn_impl
+        return cache
     calib = calib or {}
     gs = calib.get("group_size") or group_size
     cp = calib.get("clip_percentile") or clip_percentile
@@ -780,6 +844,8 @@ def generate_from_ids(model, tokenizer, input_ids, attention_mask=None, max_new_
         elif not allow_missing_calib:
             raise FileNotFoundError(f"kv_mode={kv_mode!r} needs a calibration file (got {calib_file!r}); "
                                     "pass allow_missing_calib=True to fall back to dynamic scales.")
+    if kv_mode in ("int4_kivi_aligned", "int4_ours_asym", "int4_ours_asym_ba"):
+        calib = load_role_aware_calibration(calib_file, kv_mode, device)
     num_layers = len(model.model.layers)
     max_pos = getattr(model.config, "max_position_embeddings", None)
     max_seq = prompt_len + max_new_tokens if max_pos is None else min(max_pos, prompt_len + max_new_tokens)

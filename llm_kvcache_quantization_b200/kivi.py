@@ -7,8 +7,12 @@ layer, which derives the per-channel K parameters), `get_kv` (bit-exact dequanti
 over the quantized cache (one fused kernel at head_dim 128; dequantise-then-attend otherwise, which is how
 the reference decodes this cache, `decode_attn_impl = "torch_ref"`).  With `residual_length > 0` the newest
 decode tokens stay in an fp16 window and are quantized as they leave it (:363-405); attention then merges the
-partial over the quantized tokens with the partial over the window.  Clipping percentiles below 100 are not
-offered.
+partial over the quantized tokens with the partial over the window.  Clipping percentiles below 100
+(src/quant/asymmetric_quant.py:98-104: two-sided torch.quantile bounds, over the prompt's tokens for K and over the
+head dimension of each token for V) sort on the device (torch.sort: no rounding) and interpolate in
+kvq_sorted_quantile; the append kernel takes the bounds in place of the minimum and maximum.
+`RoleAwareAsymKVCache` (src/cache/role_aware_asym_cache.py:27-83) is the same cache carrying the metadata of the
+calibrated-percentile family.
 """
 from __future__ import annotations
 
@@ -22,6 +26,24 @@ from . import _lib, ops
 from .cache import _new_stats
 
 
+def _clip_bounds(x: Tensor, percentile: float) -> Tuple[Tensor, Tensor]:
+    """(quantile(1 - p), quantile(p)) over the last axis of an fp32 tensor, the clipping range of the reference's
+    asymmetric quantizer below percentile 100 (src/quant/asymmetric_quant.py:98-104)."""
+    srt = torch.sort(x.contiguous(), dim=-1).values
+    rows, n = srt.numel() // srt.shape[-1], srt.shape[-1]
+    lo = torch.empty(srt.shape[:-1], dtype=torch.float32, device=x.device)
+    hi = torch.empty_like(lo)
+    q = _lib.KvqQuantileArgs()
+    q.sorted, q.rows, q.n = srt.data_ptr(), rows, n
+    q.q_lo = max(0.0, min((100.0 - percentile) / 100.0, 1.0))
+    q.q_hi = max(0.0, min(percentile / 100.0, 1.0))
+    q.out_lo, q.out_hi = lo.data_ptr(), hi.data_ptr()
+    with torch.cuda.device(x.device):
+        rc = _lib.load().kvq_sorted_quantile(C.byref(q), ops._stream_ptr(x.device))
+    _lib.check("kvq_sorted_quantile", rc)
+    return lo, hi
+
+
 class KIVIStyleKVCache:
     def __init__(self, num_layers: int, device: str = "cuda", dtype: torch.dtype = torch.float16,
                  max_seq_len: Optional[int] = None, quant_bits: int = 8, k_percentile: float = 100.0,
@@ -31,14 +53,16 @@ class KIVIStyleKVCache:
             raise ValueError(f"num_layers must be > 0, got {num_layers}")
         if quant_bits not in (4, 8):
             raise ValueError(f"quant_bits must be 4 or 8, got {quant_bits}")
-        if float(k_percentile) != 100.0 or float(v_percentile) != 100.0:
-            raise NotImplementedError("clipping percentiles below 100 are not offered by this cache")
+        for nm, pct in (("k_percentile", k_percentile), ("v_percentile", v_percentile)):
+            if not (50.0 < float(pct) <= 100.0):      # the quantizer's own check (src/quant/asymmetric_quant.py:64-68)
+                raise ValueError(f"percentile must be in (50.0, 100.0], got {pct} for {nm}. "
+                                 "Values <= 50 invert min/max and produce silent errors.")
         self.num_layers = num_layers
         self.device = device
         self.dtype = dtype
         self.max_seq_len = int(max_seq_len) if max_seq_len is not None else None
         self.quant_bits = quant_bits
-        self.k_percentile, self.v_percentile = 100.0, 100.0
+        self.k_percentile, self.v_percentile = float(k_percentile), float(v_percentile)
         self.bit_packed = bool(quant_bits == 4)
         self.decode_attn_impl = "torch_ref"
         self.inv_tau = inv_tau
@@ -181,9 +205,20 @@ class KIVIStyleKVCache:
         a.src_stride_b, a.src_stride_h, a.src_stride_t = k16.stride(0), k16.stride(1), k16.stride(2)
         a.write_pos = old
         dev = k16.device
+        keep = []                                     # bounds tensors stay alive until the launch is enqueued
+        if a.init_k_params and self.k_percentile < 100.0:
+            # per channel over the prompt's tokens: sorted along the token axis
+            lo, hi = _clip_bounds(k16.float().transpose(2, 3), self.k_percentile)           # [B, H, D]
+            a.k_lo, a.k_hi = lo.data_ptr(), hi.data_ptr()
+            keep += [lo, hi]
+        if self.v_percentile < 100.0:
+            lo, hi = _clip_bounds(v16.float(), self.v_percentile)                           # [B, H, T]
+            a.v_lo, a.v_hi = lo.data_ptr(), hi.data_ptr()
+            keep += [lo, hi]
         with torch.cuda.device(dev):
             rc = _lib.load().kvq_kivi_append(C.byref(a), ops._stream_ptr(dev))
         _lib.check("kvq_kivi_append", rc)
+        del keep
         self._k_scale_initialized[layer_id] = True
         self._layer_seq_lens[layer_id] = old + T
         self._seq_len = max(self._layer_seq_lens) + (max(self._residual_lens) if self.residual_length > 0 else 0)
@@ -314,3 +349,20 @@ class KIVIStyleKVCache:
     def __repr__(self) -> str:
         return (f"KIVIStyleKVCache(num_layers={self.num_layers}, quant_bits={self.quant_bits}, "
                 f"seq_len={self._seq_len}, memory={self.get_memory_mb():.1f}MB)")
+
+
+class RoleAwareAsymKVCache(KIVIStyleKVCache):
+    """The KIVI-format cache under the name of the calibrated-percentile family
+    (src/cache/role_aware_asym_cache.py:27-83): same storage and quantization, INT4 by default, plus the
+    `framework` tag and `ba_calibrated` (either percentile differs from 100) that the reference's routing and
+    experiment tracking read."""
+
+    def __init__(self, num_layers: int, device: str = "cuda", dtype: torch.dtype = torch.float16,
+                 max_seq_len: Optional[int] = None, quant_bits: int = 4, k_percentile: float = 100.0,
+                 v_percentile: float = 100.0, inv_tau: Optional[Tensor] = None, use_attn_temperature: bool = False,
+                 framework: str = "ours_asym", residual_length: int = 0):
+        super().__init__(num_layers=num_layers, device=device, dtype=dtype, max_seq_len=max_seq_len,
+                         quant_bits=quant_bits, k_percentile=k_percentile, v_percentile=v_percentile, inv_tau=inv_tau,
+                         use_attn_temperature=use_attn_temperature, residual_length=residual_length)
+        self.framework = framework
+        self.ba_calibrated = (k_percentile != 100.0) or (v_percentile != 100.0)

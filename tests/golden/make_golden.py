@@ -112,6 +112,83 @@ def make_kivi():
     print("kivi.npz", os.path.getsize(os.path.join(HERE, "kivi.npz")) // 1024, "KiB")
 
 
+def make_kivi_percentile():
+    """KIVIStyleKVCache and RoleAwareAsymKVCache (src/cache/role_aware_asym_cache.py) with clipping percentiles
+    below 100 on CPU: K bounds = torch.quantile over the prompt's tokens, V bounds = torch.quantile over the head
+    dimension of every token (src/quant/asymmetric_quant.py:98-106); a prompt, then single-token appends."""
+    from src.cache.kivi_style_cache import KIVIStyleKVCache
+    from src.cache.role_aware_asym_cache import RoleAwareAsymKVCache
+    gen = torch.Generator().manual_seed(20261128)
+    out = {}
+    B, H, P, N, D = 2, 2, 45, 3, 128
+    k = gen_kv(gen, B, H, P + N, D, outlier_ch=2)
+    v = gen_kv(gen, B, H, P + N, D, chan_std=True)
+    out["k"], out["v"], out["prompt"] = _np(k), _np(v), np.array(P)
+    cases = (("kivi", KIVIStyleKVCache, 4, 99.0, 99.9), ("kivi", KIVIStyleKVCache, 8, 97.5, 90.0),
+             ("role", RoleAwareAsymKVCache, 4, 99.5, 98.5))
+    out["cases"] = np.array([[bits, kp, vp] for _, _, bits, kp, vp in cases], dtype=np.float64)
+    for i, (_, cls, bits, kp, vp) in enumerate(cases):
+        c = cls(num_layers=1, device="cpu", quant_bits=bits, k_percentile=kp, v_percentile=vp)
+        c.append(0, k[:, :, :P], v[:, :, :P])
+        for t in range(P, P + N):
+            c.append(0, k[:, :, t:t + 1], v[:, :, t:t + 1])
+        S = P + N
+        out[f"c{i}_k_payload"] = _np(c._k_cache[0][:, :, :S])
+        out[f"c{i}_v_payload"] = _np(c._v_cache[0][:, :, :S])
+        out[f"c{i}_k_scale"], out[f"c{i}_k_zp"] = _np(c._k_scale[0]), _np(c._k_zp[0])
+        out[f"c{i}_v_scale"], out[f"c{i}_v_zp"] = _np(c._v_scale[0][:, :, :S]), _np(c._v_zp[0][:, :, :S])
+        kd, vd = c.get_kv(0)
+        out[f"c{i}_k_deq"], out[f"c{i}_v_deq"] = _np(kd), _np(vd)
+        if cls is RoleAwareAsymKVCache:
+            out["role_framework"] = np.array(c.framework)
+            out["role_ba_calibrated"] = np.array(bool(c.ba_calibrated))
+    np.savez_compressed(os.path.join(HERE, "kivi_pct.npz"), **out)
+    print("kivi_pct.npz", os.path.getsize(os.path.join(HERE, "kivi_pct.npz")) // 1024, "KiB")
+
+
+def make_calibration(reference_root):
+    """Two fixtures of the calibration row:
+    calib_absmax.npz - `compute_absmax_per_group` (scripts/calibrate_behavior.py:228-260) on seeded K tensors, per
+    sample and as the running maximum over samples that the collection loop keeps;
+    calib_schema.json - the schema of the calibration file the reference ships (artifacts/kv_calib_mse_1p5b_int8.json):
+    every key, with the per-layer tables cut to the first two layers, so that the loader is tested on the real layout."""
+    import json
+    import types
+    for name in ("matplotlib", "matplotlib.pyplot", "datasets"):      # plotting / dataset imports of the script's CLI
+        if name not in sys.modules:
+            try:
+                __import__(name)
+            except Exception:
+                sys.modules[name] = types.ModuleType(name)
+    from scripts.calibrate_behavior import compute_absmax_per_group
+    gen = torch.Generator().manual_seed(20261129)
+    H, S, D, n = 2, 67, 128, 2
+    xs = [(torch.randn(H, S, D, generator=gen) * torch.exp(torch.randn(H, 1, D, generator=gen))).half() for _ in range(n)]
+    out = {"x": np.stack([_np(x) for x in xs])}
+    for gs in (16, 32, 128):
+        per = [compute_absmax_per_group(x, gs).float() for x in xs]
+        out[f"g{gs}_per_sample"] = np.stack([_np(p) for p in per])
+        out[f"g{gs}_running_max"] = _np(torch.stack(per).amax(0))
+    np.savez_compressed(os.path.join(HERE, "calib_absmax.npz"), **out)
+    print("calib_absmax.npz", os.path.getsize(os.path.join(HERE, "calib_absmax.npz")) // 1024, "KiB")
+    with open(os.path.join(reference_root, "artifacts", "kv_calib_mse_1p5b_int8.json")) as f:
+        full = json.load(f)
+    keep = 2
+    cut = {}
+    for key, val in full.items():
+        if key in ("k_scale", "v_scale", "inv_tau"):
+            cut[key] = val[:keep]
+        elif key == "selection":
+            cut[key] = {k2: (v2 if not isinstance(v2, (list, dict)) else type(v2)()) for k2, v2 in val.items()}
+        else:
+            cut[key] = val
+    cut["num_layers_in_shipped_file"] = full["num_layers"]
+    cut["shapes_in_shipped_file"] = {k2: list(np.asarray(full[k2]).shape) for k2 in ("k_scale", "v_scale", "inv_tau")}
+    with open(os.path.join(HERE, "calib_schema.json"), "w") as f:
+        json.dump(cut, f)
+    print("calib_schema.json", os.path.getsize(os.path.join(HERE, "calib_schema.json")) // 1024, "KiB")
+
+
 ENGINE_GEOMETRY = dict(vocab_size=48, hidden_size=256, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
                        num_key_value_heads=1, head_dim=128, max_position_embeddings=64, rope_theta=10000.0,
                        tie_word_embeddings=False)
@@ -207,12 +284,18 @@ def make_engine():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
-    ap.add_argument("--only", default="", help="'rope' / 'kivi' / 'engine' regenerate rope.npz / kivi.npz / engine.npz alone")
+    ap.add_argument("--only", default="", help="'rope' / 'kivi' / 'kivi_pct' / 'calib' / 'engine': regenerate that fixture alone")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     warnings.simplefilter("ignore")
     if args.only == "rope":
         make_rope()
+        return
+    if args.only == "kivi_pct":
+        make_kivi_percentile()
+        return
+    if args.only == "calib":
+        make_calibration(args.reference)
         return
     if args.only == "kivi":
         make_kivi()
@@ -356,6 +439,8 @@ def main():
         print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
     make_rope()
     make_kivi()
+    make_kivi_percentile()
+    make_calibration(args.reference)
     make_engine()
 
 

@@ -31,7 +31,7 @@ def test_header_symbols_all_exported(lib):
 
 
 def test_abi_version_and_strerror(lib):
-    assert lib.kvq_abi_version() == 4 == _lib.ABI_VERSION
+    assert lib.kvq_abi_version() == 5 == _lib.ABI_VERSION
     assert lib.kvq_strerror(0) == b"ok"
     assert b"invalid" in lib.kvq_strerror(-1)
 
@@ -56,7 +56,8 @@ def test_struct_sizes_match_header(lib):
     assert ctypes.sizeof(_lib.KvqCacheSide) == 13 * 8
     assert ctypes.sizeof(_lib.KvqCombineArgs) == 4 * 4 + 10 * 8
     assert ctypes.sizeof(_lib.KvqDequantArgs) == 8 * 4 + 8 + 2 * 13 * 8 + 5 * 8
-    assert ctypes.sizeof(_lib.KvqKiviArgs) == 6 * 4 + 26 * 8
+    assert ctypes.sizeof(_lib.KvqKiviArgs) == 6 * 4 + 30 * 8
+    assert ctypes.sizeof(_lib.KvqQuantileArgs) == 8 + 8 + 3 * 4 + 4 + 2 * 8
     assert ctypes.sizeof(_lib.KvqAbsmaxArgs) == 5 * 4 + 4 + 8 + 3 * 8 + 8
     assert ctypes.sizeof(_lib.KvqExchangeArgs) == 4 * 4 + 2 * 8 + 2 * 4 + 8 + 2 * 4 + 7 * 8
 

@@ -292,3 +292,59 @@ def test_fused_decode_dump_writes_tensors_and_summary(tmp_path, monkeypatch):
     E._reset_fused_state()
     E._maybe_dump_fused_decode(eng, 1, "triton_fused", q, None, 0.3, fused)          # filtered out: step 6
     assert len(os.listdir(tmp_path)) == 2
+
+
+def test_role_aware_calibration_schemas(tmp_path):
+    """The calibration reader of the KIVI-format modes (src/engine/generate_loop.py:951-1043): `role_aware` section,
+    the k_calibration / v_calibration fallback with its warning, inv_tau only where the mode uses it, a missing file
+    raises."""
+    import json
+    import warnings as W
+    from llm_kvcache_quantization_b200 import engine as E
+    f1 = tmp_path / "ra.json"
+    f1.write_text(json.dumps({"role_aware": {"k_percentile": 99.5, "v_percentile": 99.9, "inv_tau": [[1.0, 1.1]]}, "inv_tau": [[2.0, 2.0]]}))
+    a = E.load_role_aware_calibration(str(f1), "int4_ours_asym", "cpu")
+    assert (a["k_percentile"], a["v_percentile"], a["inv_tau"]) == (99.5, 99.9, None)
+    b = E.load_role_aware_calibration(str(f1), "int4_ours_asym_ba", "cpu")
+    assert b["inv_tau"].dtype == torch.float32 and b["inv_tau"].tolist() == [[1.0, pytest.approx(1.1)]]
+    f2 = tmp_path / "v3.json"
+    f2.write_text(json.dumps({"k_calibration": {"k_percentile": 99.0, "inv_tau": [[0.9, 0.8]]}, "v_calibration": {"v_percentile": 98.0}}))
+    with pytest.warns(UserWarning, match="k_calibration fallback schema"):
+        c = E.load_role_aware_calibration(str(f2), "int4_ours_asym_ba", "cpu")
+    assert (c["k_percentile"], c["v_percentile"]) == (99.0, 98.0) and c["inv_tau"].shape == (1, 2)
+    with W.catch_warnings():
+        W.simplefilter("error")
+        d = E.load_role_aware_calibration(str(f2), "int4_kivi_aligned", "cpu")
+    assert (d["k_percentile"], d["v_percentile"]) == (100.0, 98.0) and d["inv_tau"].shape == (1, 2)
+    assert E.load_role_aware_calibration(None, "int4_ours_asym", "cpu") == {"k_percentile": 100.0, "v_percentile": 100.0, "inv_tau": None}
+    with pytest.raises(FileNotFoundError):
+        E.load_role_aware_calibration(str(tmp_path / "missing.json"), "int4_ours_asym", "cpu")
+    assert {"int4_kivi_aligned", "int4_ours_asym", "int4_ours_asym_ba"} <= E.FUSED_KV_MODES
+
+
+def test_load_calibration_reads_the_schema_of_the_shipped_file(golden_dir):
+    """tests/golden/calib_schema.json keeps every key of the reference's artifacts/kv_calib_mse_1p5b_int8.json (tables
+    cut to two layers).  The loader takes group size and percentile from the *_k keys, gives fp16 static scales to
+    INT8 modes and fp32 to INT4 modes, warns about version < 2 as the reference does
+    (src/engine/generate_loop.py:764-856)."""
+    import json
+    import os
+    from llm_kvcache_quantization_b200 import engine as E
+    path = os.path.join(golden_dir, "calib_schema.json")
+    raw = json.load(open(path))
+    assert raw["shapes_in_shipped_file"] == {"k_scale": [28, 2, 8], "v_scale": [28, 2, 8], "inv_tau": [28, 12]}
+    with pytest.warns(UserWarning, match="version=1"):
+        c = E.load_calibration(path, "int8_ours", "cpu")
+    assert c["group_size"] == 16 and c["clip_percentile"] == 99.5
+    assert c["static_k_scale"].dtype == torch.float16 and tuple(c["static_k_scale"].shape) == (2, 2, 8)
+    assert tuple(c["static_v_scale"].shape) == (2, 2, 8) and tuple(c["inv_tau"].shape) == (2, 12)
+    assert c["inv_tau"].dtype == torch.float32
+    assert torch.equal(c["static_k_scale"], torch.tensor(raw["k_scale"], dtype=torch.float16))
+    assert torch.equal(c["inv_tau"], torch.tensor(raw["inv_tau"], dtype=torch.float32))
+    assert c["outlier_rescue_ratio"] == 0.0 and c["mixed_rescue"] is False
+    with pytest.warns(UserWarning):
+        c4 = E.load_calibration(path, "int4_ours", "cpu", use_attn_temperature=False)
+    assert c4["static_k_scale"].dtype == torch.float32 and c4["inv_tau"] is None
+    with pytest.warns(UserWarning):
+        c0 = E.load_calibration(path, "int8_ours", "cpu", use_static_scales=False)
+    assert c0["static_k_scale"] is None and c0["static_v_scale"] is None

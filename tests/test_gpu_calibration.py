@@ -58,3 +58,18 @@ def test_calibration_pipeline_round_trip(tmp_path):
     cache.append(0, k, k)
     kd, _ = cache.get_kv(0)
     assert float((kd.float() - k.float()).abs().max()) < 0.05 * float(k.float().abs().max())
+
+
+@pytest.mark.parametrize("gs", (16, 32, 128))
+def test_group_absmax_reproduces_the_reference_function(golden_dir, gs):
+    """Fixture from the reference's own compute_absmax_per_group (scripts/calibrate_behavior.py:228-260), per sample and
+    as the running maximum its collection loop keeps."""
+    import os
+    z = np.load(os.path.join(golden_dir, "calib_absmax.npz"))
+    x = torch.from_numpy(z["x"]).to(DEV)                       # [samples, H, S, D]
+    acc = torch.zeros(x.shape[1], x.shape[3] // gs, device=DEV)
+    for i in range(x.shape[0]):
+        got = C.compute_absmax_per_group(x[i], gs)
+        assert np.array_equal(got.float().cpu().numpy(), z[f"g{gs}_per_sample"][i])
+        ops.group_absmax(x[i][None], gs, out=acc)
+    assert np.array_equal(acc.cpu().numpy(), z[f"g{gs}_running_max"])

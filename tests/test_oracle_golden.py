@@ -170,3 +170,23 @@ def test_kivi_format_matches_reference(golden_dir, bits):
         assert got.dtype == np.float32 and np.array_equal(got, z[f"b{bits}_{name}"]), name
     assert np.array_equal(O.dequant_asym_f32(codes_k, sk, zk, 2).view(np.uint16), z[f"b{bits}_k_deq"].view(np.uint16))
     assert np.array_equal(O.dequant_asym_f32(cv, sv, zv, 3).view(np.uint16), z[f"b{bits}_v_deq"].view(np.uint16))
+
+
+@pytest.mark.parametrize("case", (0, 1, 2))
+def test_kivi_format_with_clipping_percentiles_matches_reference(golden_dir, case):
+    """Clipping percentiles below 100 (two-sided torch.quantile bounds: over the prompt's tokens for K, over the head
+    dimension of each token for V) restated in numpy == the reference's KIVIStyleKVCache / RoleAwareAsymKVCache on
+    CPU, bit for bit."""
+    z = np.load(os.path.join(golden_dir, "kivi_pct.npz"))
+    bits, kp, vp = int(z["cases"][case][0]), float(z["cases"][case][1]), float(z["cases"][case][2])
+    k, v, P = z["k"], z["v"], int(z["prompt"])
+    ck, sk, zk = O.quantize_asym_axis(k[:, :, :P], 2, bits, percentile=kp)
+    codes_k = np.concatenate([ck, O.quantize_asym_with_params(k[:, :, P:], sk, zk, 2, bits)], axis=2)
+    cv, sv, zv = O.quantize_asym_axis(v, 3, bits, percentile=vp)
+    pk, pv = (O.pack_int4(codes_k), O.pack_int4(cv)) if bits == 4 else (codes_k, cv)
+    for got, name in ((sk, "k_scale"), (zk, "k_zp"), (sv, "v_scale"), (zv, "v_zp")):
+        assert got.dtype == np.float32 and np.array_equal(got, z[f"c{case}_{name}"]), name
+    assert np.array_equal(pk, z[f"c{case}_k_payload"]) and np.array_equal(pv, z[f"c{case}_v_payload"])
+    assert np.array_equal(O.dequant_asym_f32(codes_k, sk, zk, 2).view(np.uint16), z[f"c{case}_k_deq"].view(np.uint16))
+    assert np.array_equal(O.dequant_asym_f32(cv, sv, zv, 3).view(np.uint16), z[f"c{case}_v_deq"].view(np.uint16))
+    assert int((np.abs(codes_k.astype(np.int32)) >= (7 if bits == 4 else 127)).sum()) > 0      # clipping happened
