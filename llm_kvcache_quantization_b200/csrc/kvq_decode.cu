@@ -38,29 +38,30 @@ __device__ __forceinline__ float red_sum(const float (*red)[N], int c) {
     return v;
 }
 
+// Merge of the KV splits of one (batch, head) row: warp w takes splits w, w + 8, ... (a lane = EPL channels), eight
+// partials in flight per lane, one pass with a running (max, sum) per warp - no separate pass over the maxima, the
+// row's latency is one or two round trips to L2.  The warps then agree on the maximum through shared memory and leave
+// their sums, scaled to it, in `red` ([warp][channel], column D = the softmax denominator).  Returns the maximum
+// (log2 domain, -inf for an empty row).
 template <int EPL>   // channels per lane = D / 32
 __device__ __forceinline__ float combine_partials(const AttnParams& p, int b, int h, float (*red)[EPL * 32 + 1]) {
     const KvqAttnArgs& a = p.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int D = EPL * 32;
+    constexpr int U = 8;
+    __shared__ float warp_m[kCombineWarps];
     const long long row0 = ((long long)b * a.Hq + h) * p.splits;
     const float2* ml = reinterpret_cast<const float2*>(p.ws_ml) + row0;
-    float M = -INFINITY;
-    for (int s = lane; s < p.splits; s += 32) {
-        const float2 v = ml[s];
-        if (v.y > 0.f) M = fmaxf(M, v.x);
-    }
-    M = warp_max(M);
+    const float* o_base = p.ws_o + row0 * D + lane * EPL;
     float acc[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
-    float L = 0.f;
-    const float* o_base = p.ws_o + row0 * D + lane * EPL;
-    for (int s0 = warp; s0 < p.splits; s0 += 4 * kCombineWarps) {
-        float2 mv[4];
-        float ov[4][EPL];
+    float M = -INFINITY, L = 0.f;
+    for (int s0 = warp; s0 < p.splits; s0 += U * kCombineWarps) {
+        float2 mv[U];
+        float ov[U][EPL];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int s = s0 + kCombineWarps * u;
             mv[u] = s < p.splits ? ml[s] : make_float2(-INFINITY, 0.f);
             if (s < p.splits) {
@@ -71,8 +72,19 @@ __device__ __forceinline__ float combine_partials(const AttnParams& p, int b, in
                 }
             }
         }
+        float Mn = M;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u)
+            if (mv[u].y > 0.f) Mn = fmaxf(Mn, mv[u].x);
+        if (Mn > M) {                                  // uniform over the warp
+            const float c = exp2f(M - Mn);             // exp2f(-inf) = 0 the first time
+            L *= c;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) acc[e] *= c;
+            M = Mn;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
             if (mv[u].y > 0.f) {
                 const float w = exp2f(mv[u].x - M);
                 L += mv[u].y * w;
@@ -81,11 +93,17 @@ __device__ __forceinline__ float combine_partials(const AttnParams& p, int b, in
             }
         }
     }
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) red[warp][lane * EPL + e] = acc[e];
-    if (lane == 0) red[warp][D] = L;
+    if (lane == 0) warp_m[warp] = M;
     __syncthreads();
-    return M;
+    float Mt = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kCombineWarps; ++w) Mt = fmaxf(Mt, warp_m[w]);
+    const float c = (L > 0.f) ? exp2f(M - Mt) : 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) red[warp][lane * EPL + e] = acc[e] * c;
+    if (lane == 0) red[warp][D] = L * c;
+    __syncthreads();
+    return Mt;
 }
 
 // One channel of one cached token, dequantised exactly as the split kernels do (any format; runtime
