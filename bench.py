@@ -67,7 +67,7 @@ G = D // GS
 
 # DRAM traffic / algorithmic bytes of the split-K scan, from the ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same kernel, scaled by token-heads)
-NCU_TRAFFIC_RATIO = {"kivi4": 1.0, "fp16": 1.0, "int4_asym": 1.003, "int8_dyn": 1.004, "int8_static": 1.004, "int4_outlier": 1.028}
+NCU_TRAFFIC_RATIO = {"kivi4": 1.0, "fp16": 1.0, "int4_asym": 1.002, "int8_dyn": 1.004, "int8_static": 1.004, "int4_outlier": 1.022}
 
 
 def bytes_per_token_head(kind: str, n_out: int) -> int:
