@@ -736,7 +736,7 @@ static int dispatch_mma(const AttnParams& p, bool asym, cudaStream_t st) {
 // fewer splits on ties (less workspace traffic, cheaper combine).
 // ---------------------------------------------------------------------------
 static int pick_splits_waves(long long rows, int max_ctx, int slots, int min_tokens) {
-    long long by_len = max_ctx / min_tokens;
+    long long by_len = (max_ctx + min_tokens - 1) / min_tokens;     // a last split may be short
     if (by_len < 1) by_len = 1;
     if (by_len > 256) by_len = 256;
     if (rows >= 8LL * slots) return 1;            // many waves already: the tail is a small fraction
@@ -765,9 +765,10 @@ static int pick_splits_internal(const AttnParams& p, bool asym, bool mma) {
     if (mma) {
         const MmaConfig* cfg = i4_eligible(p, asym) ? i4_config_for(p, asym) : mma_config_for(p, asym);
         if (!cfg) return 1;
-        return pick_splits_waves(rows, p.a.max_ctx, sms * cfg->ctas_per_sm, kMmaWarps * kTS);
+        // the tokens the split kernel scans: a tail token belongs to the combine stage
+        return pick_splits_waves(rows, p.a.max_ctx - (p.a.tail_tokens ? 1 : 0), sms * cfg->ctas_per_sm, kMmaWarps * kTS);
     }
-    return pick_splits_waves(rows, p.a.max_ctx, sms * 8, 256);
+    return pick_splits_waves(rows, p.a.max_ctx - (p.a.tail_tokens ? 1 : 0), sms * 8, 256);
 }
 
 static int fill_params(const KvqAttnArgs& a, AttnParams& p, bool& asym) {
