@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 import torch
 
+import llm_kvcache_quantization_b200 as kvq
 from llm_kvcache_quantization_b200 import engine as E
 from oracle import kvq_oracle as O
 
@@ -201,6 +202,44 @@ def test_kivi_style_mode_generates(tiny_model, bits):
     assert torch.equal(out.generated_ids[:, 0], ref[:, 0])          # the first token comes from the fp16 prefill
     if bits == 8:
         assert (out.generated_ids == ref).float().mean() >= 0.6
+
+
+@pytest.mark.parametrize("mode", ("int4_ours_asym", "int4_ours_asym_ba", "int4_kivi_aligned"))
+def test_role_aware_modes_generate(tiny_model, mode, tmp_path):
+    """The KIVI-format modes that read a calibration file (src/engine/generate_loop.py:951-1060): the percentiles reach
+    the cache, inv_tau only where the mode uses it, generation runs through the fused decode of the KIVI cache and
+    equals a KIVIStyleKVCache run with the same settings."""
+    import json
+    cfg = tiny_model.config
+    L, Hq = cfg.num_hidden_layers, cfg.num_attention_heads
+    tau = [[1.0 + 0.01 * (l + h) for h in range(Hq)] for l in range(L)]
+    f = tmp_path / "ra.json"
+    f.write_text(json.dumps({"role_aware": {"k_percentile": 99.5, "v_percentile": 99.0, "inv_tau": tau},
+                             "k_calibration": {"inv_tau": tau}, "v_calibration": {"v_percentile": 99.0}}))
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, 512, (2, 33), generator=g).to(DEV)
+    seen = {}
+    real = E.build_cache
+
+    def spy(*a, **k):
+        seen["cache"] = real(*a, **k)
+        return seen["cache"]
+    E.build_cache = spy
+    try:
+        out = E.generate_from_ids(tiny_model, _Tok(), ids, max_new_tokens=5, kv_mode=mode, calib_file=str(f), stop_on_eos=False)
+    finally:
+        E.build_cache = real
+    c = seen["cache"]
+    assert out.generated_ids.shape == (2, 5) and out.kv_cache_seq_len == 37
+    assert c.quant_bits == 4 and c.v_percentile == 99.0
+    if mode == "int4_kivi_aligned":
+        assert type(c) is kvq.KIVIStyleKVCache and c.k_percentile == 100.0 and c.inv_tau is not None
+    else:
+        assert type(c) is kvq.RoleAwareAsymKVCache and c.k_percentile == 99.5 and c.ba_calibrated
+        assert c.framework == ("ours_asym_ba" if mode.endswith("_ba") else "ours_asym")
+        assert (c.inv_tau is not None) == mode.endswith("_ba") and c.use_attn_temperature == mode.endswith("_ba")
+    ref, _ = _hf_greedy(tiny_model, ids, 5)
+    assert torch.equal(out.generated_ids[:, 0], ref[:, 0])          # the first token comes from the fp16 prefill
 
 
 # --------------------------------------------------------------------------- pinned to the reference's patched forward
