@@ -131,6 +131,7 @@ decode_split_int4_kernel(const Int4Params ip, const __grid_constant__ CUtensorMa
     __shared__ uint32_t done_cnt[kI4MaxStages];                // warps that finished reading the slot, ever
     __shared__ float red_ml[kMmaWarps][kHeadsPerCta][2];
 
+
     const uint32_t bar0 = smem_u32(&bars[0]);
     const uint32_t done0 = smem_u32(&done_cnt[0]);
     if (threadIdx.x == 0) {
@@ -186,6 +187,7 @@ decode_split_int4_kernel(const Int4Params ip, const __grid_constant__ CUtensorMa
 
     // Called by ALL lanes of one warp: lane 0 arms the barrier and starts the tensor copies.
     auto issue = [&](int k, int st) {        // stage k of the CTA into slot st = k mod nstage
+        if (KVQ_ABLATE & 32) return;         // timing experiment: arithmetic on whatever the slots hold, no copies
         const int tok0 = s0 + k * kI4Tok;
         const uint32_t sb = sbase + st * STAGE_BYTES;
         const uint32_t bar = bar0 + 8 * st;
@@ -363,7 +365,7 @@ decode_split_int4_kernel(const Int4Params ip, const __grid_constant__ CUtensorMa
     int st = 0;
     uint32_t parity = 0u;
     for (int k = 0; k < n_st; ++k) {
-        const bool ok = mbar_wait_bounded(bar0 + 8 * st, parity);
+        const bool ok = (KVQ_ABLATE & 32) ? true : mbar_wait_bounded(bar0 + 8 * st, parity);
         if (!__all_sync(0xffffffffu, ok)) {
             failed = true;
             break;
@@ -417,15 +419,16 @@ decode_split_int4_kernel(const Int4Params ip, const __grid_constant__ CUtensorMa
                         const int c = 2 * gp + e;                // 32-channel chunk; its group:
                         const int G = (32 * c) / GS;
                         const uint32_t w0 = r[2 * e], w1 = r[2 * e + 1];
+                        const uint32_t* qc = qf + 4 * c;
                         if ((32 * c) % GS == 0)
                             mma16816_zero(sg[G], nib_lo_to_h2(w0), nib_lo_to_h2(w1), nib_hi_to_h2(w0), nib_hi_to_h2(w1),
-                                          qf[4 * c], qf[4 * c + 1]);
+                                          qc[0], qc[1]);
                         else
                             mma16816(sg[G], nib_lo_to_h2(w0), nib_lo_to_h2(w1), nib_hi_to_h2(w0), nib_hi_to_h2(w1),
-                                     qf[4 * c], qf[4 * c + 1]);
+                                     qc[0], qc[1]);
                         const uint32_t x0 = w0 >> 8, x1 = w1 >> 8;
                         mma16816(sg[G], nib_lo_to_h2(x0), nib_lo_to_h2(x1), nib_hi_to_h2(x0), nib_hi_to_h2(x1),
-                                 qf[4 * c + 2], qf[4 * c + 3]);
+                                 qc[2], qc[3]);
                     }
                 }
                 float sa[NG], sb2[NG];                           // K scales of rows 16 sub + g, + 8
