@@ -4,8 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c4]
 
 One "step" = one decode step over the whole KV stack of a workload: for every layer, quantize-on-append
-of the new token (one launch for K and V) followed by the fused decode attention (split-K scan + combine)
-over the cached context, captured as one CUDA graph.
+of the new token (one launch for K and V) and the fused decode attention (split-K scan + combine) over the
+cached context, captured as one CUDA graph - with the append either on a second stream beside the scan or in
+stream order, whichever a short trial of both finds faster for the shape (`step`, `step_form_trial_ms`).
 
 Headline workload = configuration 4 of the benchmark definition, the largest one that fits a single GPU
 (Qwen2.5-7B geometry, 28 layers, batch 64, context 32768, INT8 group-32: 64 GB of cache).  The other
@@ -662,9 +663,32 @@ def measure_workload(name, wl, args, dev, dist, rank, world, *, e2e=True, cpu=Fa
     small = L * B * Hkv * S * bytes_per_token_head(kind, n_out) <= 126e6
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
 
-    step, splits_fn = make_step(wl, cache, q, k_new, v_new, inv_tau, out)
-    g_step = capture(step)
-    splits = splits_fn()
+    # Two forms of the same step: the append on a second stream beside the scan of the old tokens (the combine then
+    # attends the new token), or append, scan, combine in stream order.  Which is faster depends on the shape (the
+    # fork and join of the second stream cost about as much as a small append hides): both are captured, timed for a
+    # few steps, and the faster one is measured; every rank takes the same one.
+    forms = {}
+    for form, env in (("append beside the scan", None), ("append in stream order", "1")):
+        old = os.environ.get("KVQ_BENCH_NO_OVERLAP")
+        forced = old is not None
+        if env is not None and not forced:
+            os.environ["KVQ_BENCH_NO_OVERLAP"] = env
+        try:
+            fn, splits_fn = make_step(wl, cache, q, k_new, v_new, inv_tau, out)
+            forms[form] = (capture(fn), splits_fn())
+        finally:
+            if env is not None and not forced:
+                os.environ.pop("KVQ_BENCH_NO_OVERLAP", None)
+        if forced:
+            forms = {("append in stream order" if old == "1" else "append beside the scan"): forms[form]}
+            break
+    trial = {}
+    for form, (gph, _) in forms.items():
+        time_graph(gph, 3, dist)
+        trial[form], = allreduce_max([min(time_graph(gph, max(args.steps, 5), dist) for _ in range(2))], dev, dist)
+    step_form = min(trial, key=trial.get)
+    g_step, splits = forms[step_form]
+    forms.clear()
     int4 = kind in ("int4_asym", "int4_outlier")
     scans = {}
     for arm, env in (("default", None), ("bit_faithful", "0")) if int4 else (("default", None),):
@@ -705,7 +729,10 @@ def measure_workload(name, wl, args, dev, dist, rank, world, *, e2e=True, cpu=Fa
     res.update(ms_per_step=med, ms_per_step_min=mn, blocks=len(step_ms), us_per_layer=med * 1e3 / L,
                value=B_total / (med * 1e-3), unit="tokens/s", splits=splits, clocks=clocks,
                gpu_launches=n_steps_timed * L * 3,
-               step=f"CUDA graph of {L}x(quantize-append || split-K scan of the old tokens, then combine incl. the new token)")
+               step=(f"CUDA graph of {L}x(quantize-append || split-K scan of the old tokens, then combine incl. the new token)"
+                     if step_form == "append beside the scan" else
+                     f"CUDA graph of {L}x(quantize-append, split-K scan, combine) in stream order"),
+               step_form_trial_ms={k: v / max(args.steps, 5) for k, v in trial.items()})
 
     peak, peak_src = hbm_peak()
     alg_bytes = B * Hkv * (S + 1) * bytes_per_token_head(kind, n_out)
@@ -741,7 +768,8 @@ def measure_workload(name, wl, args, dev, dist, rank, world, *, e2e=True, cpu=Fa
     # layer, device-side position counter, the cache grows by one token) and downloads the outputs
     if e2e and kind != "kivi4":
         from llm_kvcache_quantization_b200.runtime import GraphedKVStackStep
-        stepper = GraphedKVStackStep(cache, Hq, 1.0 / D ** 0.5, inv_tau=inv_tau)
+        stepper = GraphedKVStackStep(cache, Hq, 1.0 / D ** 0.5, inv_tau=inv_tau,
+                                     overlap_append=step_form == "append beside the scan")
         stepper.capture()
         stepper.host_q.copy_(q.cpu()); stepper.host_k.copy_(k_new.cpu()); stepper.host_v.copy_(v_new.cpu())
         room = stepper.capacity - stepper._len - 1
@@ -1019,7 +1047,7 @@ def main():
             "gpu_launches": head.get("gpu_launches"), "clocks": head.get("clocks"),
             "parity_check": head.get("parity_check"),
         }
-        for k in ("roofline_bit_faithful", "aux", "model_step", "headline_fallback", "skipped"):
+        for k in ("roofline_bit_faithful", "aux", "model_step", "headline_fallback", "skipped", "step_form_trial_ms"):
             if k in head:
                 line[k] = head[k]
         if extra:
