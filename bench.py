@@ -807,6 +807,30 @@ def measure_workload(name, wl, args, dev, dist, rank, world, *, e2e=True, cpu=Fa
                              "outputs; stream sync"}
         del stepper
 
+    if args.decompose and world == 1 and kind != "kivi4":
+        # where a layer's time goes: graphs of the scan alone, scan + combine, and the two forms of the whole step
+        # (L2 is not flushed between replays here: meaningful for stacks larger than L2 or read as a warm-cache figure)
+        dec = {}
+        for label, kw, env in (("scan", dict(stages=1, with_append=False), None),
+                               ("scan_combine", dict(stages=0, with_append=False), None),
+                               ("step_append_in_order", dict(), "1"), ("step_append_beside", dict(), "0")):
+            old = os.environ.get("KVQ_BENCH_NO_OVERLAP")
+            if env is not None:
+                os.environ["KVQ_BENCH_NO_OVERLAP"] = env
+            try:
+                fn, _ = make_step(wl, cache, q, k_new, v_new, inv_tau, out, **kw)
+                gph = capture(fn)
+            finally:
+                if env is not None:
+                    if old is None:
+                        os.environ.pop("KVQ_BENCH_NO_OVERLAP", None)
+                    else:
+                        os.environ["KVQ_BENCH_NO_OVERLAP"] = old
+            time_graph(gph, 5)
+            dec[label] = min(time_graph(gph, 30) for _ in range(5)) / 30 / L * 1e3
+            del gph
+        res["decomposition_us_per_layer"] = dec
+
     # the callers either side of the decode path (dequantising read-back, bulk prefill append): always for configuration 2
     if (args.aux or name == "c2") and kind not in ("fp16", "kivi4") and world == 1:
         res["aux"] = time_aux(wl, cache, dev)
@@ -942,6 +966,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling captures only)")
+    ap.add_argument("--decompose", action="store_true",
+                    help="also time graphs of the scan alone, scan + combine and both forms of the step (us per layer)")
     ap.add_argument("--aux", action="store_true",
                     help="also time the neighbouring kernels at the headline shape: bulk prefill quantize-append "
                          "(T = context) and the dequantising get_kv, one layer each")
@@ -1047,7 +1073,8 @@ def main():
             "gpu_launches": head.get("gpu_launches"), "clocks": head.get("clocks"),
             "parity_check": head.get("parity_check"),
         }
-        for k in ("roofline_bit_faithful", "aux", "model_step", "headline_fallback", "skipped", "step_form_trial_ms"):
+        for k in ("roofline_bit_faithful", "aux", "model_step", "headline_fallback", "skipped", "step_form_trial_ms",
+                  "decomposition_us_per_layer"):
             if k in head:
                 line[k] = head[k]
         if extra:
