@@ -16,9 +16,11 @@
 // This translation unit must be compiled WITHOUT fast-math: it relies on IEEE
 // fp32 division and fp16 subnormals.
 //
-// Work decomposition: one thread per (side, b, h, t, group).  Append traffic is
-// tiny next to the attention scan (decode: B*Hkv rows of 256 B), so the kernel is
-// launch-latency bound; what matters is that it is ONE launch with no host sync.
+// Two work decompositions of the same arithmetic.  Per-token form: one thread per chunk of a
+// (side, b, h, t) row; decode-time append traffic is tiny next to the attention scan (B*Hkv rows
+// of 256 B), the kernel is launch-latency bound and what matters is that it is ONE launch with no
+// host sync.  Bulk form (prefill, thousands of tokens): laid out for bandwidth and for few
+// instructions per element, bit-identical results (see quantize_bulk_kernel).
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -780,7 +782,7 @@ static int launch(const QuantParams& p, cudaStream_t st) {
     const int gs = a.group_size;
     // a percentile below 100 needs the sorted group unless its rank falls on the two largest values
     const bool dyn_sort = POLICY == KVQ_SCALE_DYNAMIC_PCT && a.quantile < 1.0f && !top2_applies(gs, a.quantile);
-    if (bulk_ok<FMT, POLICY>(p)) {
+    if constexpr (FMT != KVQ_FMT_FP16) if (bulk_ok<FMT, POLICY>(p)) {
         int rc = KVQ_EUNSUPPORTED;
         if (gs == 16) rc = launch_bulk<FMT, POLICY, 8, 2>(p, st);
         if (gs == 32) rc = launch_bulk<FMT, POLICY, 16, 2>(p, st);
