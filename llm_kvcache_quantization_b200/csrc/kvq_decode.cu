@@ -670,7 +670,7 @@ static int launch_i4(I4Tag<ASYM, NOUT, FAST, GS> tag, const AttnParams& p, cudaS
     // keeps the 64-byte rows.
     ip.wide_rows = wide_rows_ok(p.a);
     {
-        static const int pf = [] { const char* e = getenv("KVQ_I4_PREFETCH"); int v = e ? atoi(e) : 4; return v < 0 ? 0 : (v > 64 ? 64 : v); }();
+        static const int pf = [] { const char* e = getenv("KVQ_I4_PREFETCH"); int v = e ? atoi(e) : 1; return v < 0 ? 0 : (v > 64 ? 64 : v); }();
         static const int ahead = [] { const char* e = getenv("KVQ_I4_L2_AHEAD"); int v = e ? atoi(e) : 0; return v < 0 ? 0 : (v > 16 ? 16 : v); }();
         ip.prefetch_stages = pf;
         ip.l2_ahead = ahead;

@@ -232,10 +232,10 @@ decode_split_int4_kernel(const Int4Params ip, const __grid_constant__ CUtensorMa
             cp_async_mbar_arrive(bar);
         }
     };
-    if (warp == 0) {
-        const int first = min(nstage, n_st);
-        for (int k = 0; k < first; ++k) issue(k, k);
-    }
+    // Only the first stage is requested here; the other slots are filled when it has landed (below).  A launch of
+    // this kernel is one wave of CTAs that all start together: with every CTA asking for two stages at once, half of a
+    // short context's bytes queue at the memory in the first microsecond and everybody's first stage arrives late.
+    if (warp == 0 && n_st > 0) issue(0, 0);               // an empty range issues nothing (its start need not even be aligned)
     pdl_launch_dependents();      // the combine kernel may take free SM resources; it waits for this grid itself
 
     // ---- Q fragments: thread (g = head, t) holds 32 channels of q[head g] in the channel order of the K fragments
@@ -369,6 +369,10 @@ decode_split_int4_kernel(const Int4Params ip, const __grid_constant__ CUtensorMa
         if (!__all_sync(0xffffffffu, ok)) {
             failed = true;
             break;
+        }
+        if (k == 0 && warp == 0) {                              // the first stage is here: request the rest of the ring
+            const int first = min(nstage, n_st);
+            for (int kk = 1; kk < first; ++kk) issue(kk, kk);
         }
         const int tok0 = s0 + k * kI4Tok + warp * 32;           // first token of this warp's quarter
         const uint32_t sb = sbase + st * STAGE_BYTES;
