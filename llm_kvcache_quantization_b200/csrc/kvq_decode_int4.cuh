@@ -191,6 +191,10 @@ decode_split_int4_kernel(const Int4Params ip, const __grid_constant__ CUtensorMa
         const int tok0 = s0 + k * kI4Tok;
         const uint32_t sb = sbase + st * STAGE_BYTES;
         const uint32_t bar = bar0 + 8 * st;
+        if ((KVQ_ABLATE & 64) && !OUTL) {    // timing experiment: the slot protocol without the copies (barrier completes at once)
+            if (lane == 0) mbar_expect_tx(bar, 0);
+            return;
+        }
         if (lane == 0) {
             mbar_expect_tx(bar, 2 * TILE + ((KVQ_ABLATE & 16) ? 0 : (ASYM ? 4 : 2) * SCB));
             tma_load_4d(sb, &kmap, bar, 0, wide ? (tok0 >> 1) : tok0, kvh, b);

@@ -45,7 +45,8 @@
 // Profiling builds only (build.py -DKVQ_ABLATE=bits --out ...): leave one phase of the loop out so that its share of
 // the kernel time can be read from CUDA-event timings.  1: no scale / zero-point arithmetic, 2: no softmax
 // (probabilities = logits), 4: no P.V product, 8: no q.K product, 16: scales and zero-points are not fetched, 32 (packed-INT4 kernel): no copies
-// and no waits at all - the arithmetic alone, on whatever the slots hold.  The results of such a build are meaningless.
+// and no waits at all - the arithmetic alone, on whatever the slots hold, 64 (packed-INT4 kernel without outliers): the
+// slot protocol (barriers, release counters) without the copies.  The results of such a build are meaningless.
 #ifndef KVQ_ABLATE
 #define KVQ_ABLATE 0
 #endif
